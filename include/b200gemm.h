@@ -1,0 +1,108 @@
+/*
+ * b200gemm -- C ABI of the B200 (sm_100a) grouped-GEMM / per-block-quantiser library.
+ *
+ * The reference project (DeepLink-org/Triton_Grouped_GEMM) has no C interface: its kernels
+ * are Triton JIT functions launched from Python.  Each entry point below replaces the Triton
+ * launch made by one reference Python function (cited per function, paths relative to the
+ * reference's root); the Python package triton_grouped_gemm_b200 binds them with ctypes.
+ *
+ * Conventions
+ *   - Every pointer is a DEVICE pointer unless the comment says "host".
+ *   - Every call is asynchronous on `stream` (a cudaStream_t passed as void*; NULL = the
+ *     legacy default stream), never synchronises the host, and allocates nothing.
+ *   - Return value: 0 = ok, negative = rejected on the host (B200GEMM_ERR_*);
+ *     b200gemm_last_error() then holds a message (thread local).
+ *   - Errors detected on the device (a bounded wait that ran out) are OR-ed into a
+ *     per-device status word, read with b200gemm_device_status().
+ *   - Group sizes always stay on the device; `sizes_is_i64` selects int64_t / int32_t.
+ *   - dtype codes: 0 = bfloat16, 1 = float16.  fp8 format codes: 0 = e4m3, 1 = e5m2.
+ */
+#ifndef B200GEMM_H_
+#define B200GEMM_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200GEMM_OK 0
+#define B200GEMM_ERR_INVALID_ARGUMENT (-1)
+#define B200GEMM_ERR_UNSUPPORTED (-2)
+#define B200GEMM_ERR_CUDA (-3)
+#define B200GEMM_ERR_DRIVER_ENTRY (-4)
+
+/* bits of the device status word */
+#define B200GEMM_DEV_TIMEOUT_PRODUCER 0x1u
+#define B200GEMM_DEV_TIMEOUT_MMA 0x2u
+#define B200GEMM_DEV_TIMEOUT_EPILOGUE 0x4u
+#define B200GEMM_DEV_TIMEOUT_PROMOTE 0x8u
+#define B200GEMM_DEV_BAD_GROUP_SIZE 0x10u
+
+/* ---- library services (no reference counterpart: the reference reports errors with Python
+ *      assert / ValueError and lets a wedged kernel hang) -------------------------------- */
+int b200gemm_version(void);
+const char* b200gemm_last_error(void);
+/* Copies the current device's status word to *out_status (host pointer); synchronises the
+ * device.  clear != 0 resets it afterwards. */
+int b200gemm_device_status(unsigned* out_status, int clear);
+int b200gemm_sm_count(void);
+/* Tuning override for the 16-bit M-grouped kernels: 0 = pick the tile width (64 / 128 / 256
+ * output columns) from the problem size, otherwise force that width.  Process-wide. */
+int b200gemm_set_block_n(int block_n);
+
+/* ---- BF16 / FP16 grouped GEMMs ------------------------------------------------------- */
+
+/* M-grouped GEMM: C[rows of g, :] = A[rows of g, :] * B_g, fp32 accumulate, one rounding.
+ * Replaces _m_grouped_gemm_launch + m_grouped_gemm_b{K,N}major_kernel + the host metadata
+ * build (gemm/BF16/m_grouped_gemm_TMA.py:73-268, 297-326, 329-432; sm_80 twin
+ * gemm/BF16/m_grouped_gemm.py:43-292).
+ *   A [m_rows, k] row-major, compact (no padding rows); C [m_rows, n] row-major.
+ *   trans_b != 0: B [G, n, k];  trans_b == 0: B [G, k, n].
+ *   sizes [G]: rows per group (sum <= m_rows).  Requires k % 8 == 0, n % 8 == 0,
+ *   16-byte aligned base pointers.  num_sms <= 0 = all SMs. */
+int b200gemm_m_grouped(const void* a, const void* b, void* c, const void* sizes, int sizes_is_i64,
+                       int num_groups, int64_t m_rows, int n, int k, int trans_b, int dtype, int num_sms,
+                       void* stream);
+
+/* Masked M-grouped GEMM: for each g, rows [g*expected_m, g*expected_m + masked_m[g]) of
+ * out = same rows of lhs * rhs[g]^T; other rows of out are left untouched.
+ * Replaces m_grouped_gemm_masked + m_grouped_gemm_masked_kernel
+ * (gemm/BF16/m_grouped_gemm_masked_TMA.py:54-250).  lhs [G*expected_m, k], rhs [G, n, k]
+ * (trans_b != 0) or [G, k, n], out [G*expected_m, n].  masked_m[g] is clamped to
+ * [0, expected_m].  Runs on `stream` (the reference uses a private side stream). */
+int b200gemm_m_grouped_masked(const void* lhs, const void* rhs, void* out, const void* masked_m,
+                              int sizes_is_i64, int num_groups, int expected_m, int n, int k, int trans_b,
+                              int dtype, int num_sms, void* stream);
+
+/* ---- per-block FP8 (e4m3) quantisers: bytes and fp32 scales identical to the reference's
+ *      torch functions ------------------------------------------------------------------ */
+
+/* 1x128 activation quantiser.  Replaces per_token_cast_to_fp8
+ * (gemm/FP8/m_grouped_gemm_channel_expert.py:217-222).  x [rows, k] 16-bit, k % 128 == 0;
+ * q [rows, k] bytes; scales [rows, k/128] fp32. */
+int b200quant_act_1x128(const void* x, void* q, float* scales, int64_t rows, int64_t k, int dtype, void* stream);
+
+/* 128x128 weight quantiser, batched over experts.  Replaces per_block_cast_to_fp8
+ * (gemm/FP8/m_grouped_gemm_channel_expert.py:237-245) applied to each x[e].
+ * x [batch, rows, cols] 16-bit; q same shape, bytes; scales [batch, ceil(rows/128),
+ * ceil(cols/128)] fp32. */
+int b200quant_w_128x128(const void* x, void* q, float* scales, int64_t batch, int rows, int cols, int dtype,
+                        void* stream);
+
+/* Transposing 128x128 quantiser with per-expert expansion.  Replaces
+ * trans_per_block_quant_expand_128x + its Triton kernel
+ * (quant/trans_per_block_quant_expand_128x.py:42-208); results equal the torch function
+ * per_block_trans_quant_expand_torch (same file :253-273).
+ * x [m_rows, n] 16-bit (n % 128 == 0), sizes [G] rows per expert;
+ * q [n, m_expand] bytes, scales [n/128, m_expand/128] fp32, padded_sizes_out [G] int64
+ * (may be NULL).  m_expand = m_rows + 128*G - m_rows % 128 (computed by the caller). */
+int b200quant_trans_expand_128x(const void* x, const void* sizes, int sizes_is_i64, int num_groups, void* q,
+                                float* scales, int64_t* padded_sizes_out, int64_t m_rows, int n, int64_t m_expand,
+                                int dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* B200GEMM_H_ */

@@ -1,0 +1,184 @@
+"""BF16 / FP16 M-grouped and masked M-grouped GEMM on the GPU against the CPU oracle.
+
+Tolerance (from the build target): rdiff = sum|a-b| / sum|b| <= 2e-3 against the oracle's
+fp32-accumulated, once-rounded result; in practice the two differ only by accumulation
+order, so a much tighter bound (2e-4) is asserted as well where noted."""
+
+import pytest
+import torch
+
+import oracle as O
+from triton_grouped_gemm_b200 import _lib
+from triton_grouped_gemm_b200.gemm.BF16.m_grouped_gemm_TMA import _m_grouped_gemm_launch, m_grouped_gemm
+from triton_grouped_gemm_b200.gemm.BF16.m_grouped_gemm_masked_TMA import m_grouped_gemm_masked
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+RDIFF_TOL = 2e-3
+
+
+@pytest.fixture(autouse=True)
+def _reset_tuning():
+    yield
+    _lib.load().b200gemm_set_block_n(0)
+    assert _lib.device_status() == 0
+
+
+def _run(a, b, sizes, trans_b, block_n=0, size_dtype=torch.int64):
+    _lib.load().b200gemm_set_block_n(block_n)
+    n = b.shape[1] if trans_b else b.shape[2]
+    c = torch.full((a.shape[0], n), float("nan"), device=DEV, dtype=a.dtype)
+    _m_grouped_gemm_launch(a.to(DEV), b.to(DEV), c, sizes.to(DEV, size_dtype), trans_b)
+    torch.cuda.synchronize()
+    return c.cpu()
+
+
+def _check(out, ref, rows_written, tol=RDIFF_TOL):
+    assert not torch.isnan(out[:rows_written].float()).any(), "unwritten / NaN outputs inside groups"
+    r = O.rdiff(out[:rows_written].float(), ref[:rows_written].float())
+    assert r <= tol, f"rdiff {r:.3e} > {tol}"
+    # rows past the last group must not have been touched
+    assert torch.isnan(out[rows_written:].float()).all()
+
+
+@pytest.mark.parametrize("block_n", [64, 128, 256])
+@pytest.mark.parametrize("trans_b", [True, False])
+def test_single_tile_known_answer(block_n, trans_b):
+    """One 128-row group, K = 64: A selects one k per row, B holds small integers, so every
+    output is exact and a wrong descriptor / swizzle shows up as a wrong integer."""
+    m, n, k = 128, 256, 64
+    a = torch.zeros(m, k)
+    a[torch.arange(m), torch.arange(m) % k] = 1.0
+    b_nk = ((torch.arange(n)[:, None] * 3 + torch.arange(k)[None, :] * 5) % 97 - 48).float()
+    b = b_nk if trans_b else b_nk.t().contiguous()
+    ref = a @ b_nk.t()
+    out = _run(a.bfloat16(), b.bfloat16()[None].contiguous(), torch.tensor([m]), trans_b, block_n)
+    assert torch.equal(out.float(), ref), f"max abs err {(out.float() - ref).abs().max()}"
+
+
+@pytest.mark.parametrize("name,trans_b", [("small_nt", True), ("small_nn", False), ("small_nt_fp16", True)])
+def test_golden_small(golden_dir, name, trans_b):
+    c = torch.load(golden_dir / "m_grouped.pt", weights_only=False)[name]
+    out = _run(c["a"], c["b"], c["sizes"], trans_b)
+    _check(out, c["out"], int(c["sizes"].sum()), tol=2e-4)
+
+
+def test_config0_golden_and_oracle(golden_dir):
+    g = torch.load(golden_dir / "m_grouped.pt", weights_only=False)["config0"]
+    a, b, sizes = O.config0_inputs(0)
+    out = _run(a, b, sizes, True)
+    _check(out, g["out"], a.shape[0], tol=2e-4)
+    _check(out, O.m_grouped_ref(a, b, sizes, True, fp32_accumulate_explicit=True), a.shape[0], tol=2e-4)
+    # through the registered custom op as a user would call it
+    out2 = m_grouped_gemm(a.to(DEV), b.to(DEV), sizes.to(DEV), True).cpu()
+    assert torch.equal(out2, out)
+    out3 = torch.ops.moe.m_grouped_gemm(a.to(DEV), b.to(DEV), sizes.to(DEV), True, -1).cpu()
+    assert torch.equal(out3, out)
+
+
+CASES = [
+    # sizes, n, k
+    ([128, 256, 384], 256, 128),
+    ([1, 127, 129, 0, 255, 0, 0, 64], 264, 200),   # ragged rows, n and k tails, empty groups
+    ([0, 0, 5], 8, 8),
+    ([300], 1536, 2048),
+    ([5, 1, 1, 1, 700, 3], 72, 1024),
+    ([130] * 40, 512, 320),
+]
+
+
+@pytest.mark.parametrize("block_n", [0, 64, 128, 256])
+@pytest.mark.parametrize("trans_b", [True, False])
+@pytest.mark.parametrize("sizes,n,k", CASES)
+def test_ragged_vs_oracle(sizes, n, k, trans_b, block_n):
+    gen = torch.Generator().manual_seed(n * 31 + k + len(sizes))
+    m = sum(sizes)
+    extra = 7  # rows past the last group: must stay untouched
+    a = (torch.randn(m + extra, k, generator=gen) * 0.5).bfloat16()
+    g = len(sizes)
+    b = (torch.randn(g, n, k, generator=gen) * 0.5).bfloat16()
+    ref = O.m_grouped_ref(a[:m], b, sizes, True, fp32_accumulate_explicit=True)
+    bb = b if trans_b else b.transpose(1, 2).contiguous()
+    out = _run(a, bb, torch.tensor(sizes), trans_b, block_n)
+    _check(out, ref, m, tol=2e-4)
+
+
+@pytest.mark.parametrize("size_dtype", [torch.int32, torch.int64])
+def test_size_dtypes_and_fp16(size_dtype):
+    gen = torch.Generator().manual_seed(5)
+    sizes = [200, 56, 128]
+    a = torch.randn(sum(sizes), 256, generator=gen).half()
+    b = torch.randn(3, 128, 256, generator=gen).half()
+    ref = O.m_grouped_ref(a, b, sizes, True, fp32_accumulate_explicit=True)
+    out = _run(a, b, torch.tensor(sizes), True, size_dtype=size_dtype)
+    _check(out, ref, sum(sizes), tol=2e-4)
+
+
+def test_num_sms_argument():
+    gen = torch.Generator().manual_seed(6)
+    sizes = torch.tensor([256, 256, 100])
+    a = torch.randn(612, 128, generator=gen).bfloat16().to(DEV)
+    b = torch.randn(3, 512, 128, generator=gen).bfloat16().to(DEV)
+    full = m_grouped_gemm(a, b, sizes.to(DEV), True)
+    few = m_grouped_gemm(a, b, sizes.to(DEV), True, 3)
+    one = m_grouped_gemm(a, b, sizes.to(DEV), True, 1)
+    assert torch.equal(full, few) and torch.equal(full, one)
+
+
+@pytest.mark.parametrize("trans_b", [True, False])
+def test_masked_golden(golden_dir, trans_b):
+    c = torch.load(golden_dir / "masked.pt", weights_only=False)
+    e = c["expected_m"]
+    rhs = c["rhs"] if trans_b else c["rhs"].transpose(1, 2).contiguous()
+    out = torch.full(c["full"].shape, 7.0, dtype=torch.bfloat16, device=DEV)
+    assert m_grouped_gemm_masked(c["lhs"].to(DEV), rhs.to(DEV), out, c["masked_m"].to(DEV), e, trans_b) is None
+    torch.cuda.synchronize()
+    out = out.cpu()
+    for g, m in enumerate(c["masked_m"].tolist()):
+        if m:
+            assert O.rdiff(out[g * e:g * e + m].float(), c["full"][g * e:g * e + m].float()) < 2e-4
+        assert torch.all(out[g * e + m:(g + 1) * e] == 7.0), "rows past masked_m were written"
+
+
+@pytest.mark.parametrize("g,e,n,k", [(16, 256, 3072, 512), (5, 128, 64, 64), (4, 384, 200, 136), (3, 100, 128, 64)])
+def test_masked_vs_oracle(g, e, n, k):
+    gen = torch.Generator().manual_seed(g * e + n)
+    lhs = (torch.randn(g * e, k, generator=gen) * 0.5).bfloat16()
+    rhs = (torch.randn(g, n, k, generator=gen) * 0.5).bfloat16()
+    masked = torch.randint(0, e + 1, (g,), generator=gen)
+    masked[0] = e
+    if g > 2:
+        masked[1] = 0
+    init = torch.full((g * e, n), 3.0, dtype=torch.bfloat16)
+    ref = O.m_grouped_masked_ref(lhs, rhs, init, masked, e, fp32_accumulate_explicit=True)
+    out = init.clone().to(DEV)
+    m_grouped_gemm_masked(lhs.to(DEV), rhs.to(DEV), out, masked.to(DEV), e, True)
+    torch.cuda.synchronize()
+    out = out.cpu()
+    assert O.rdiff(out.float(), ref.float()) < 2e-4
+    untouched = torch.ones(g * e, dtype=torch.bool)
+    for i, m in enumerate(masked.tolist()):
+        untouched[i * e:i * e + m] = False
+    assert torch.all(out[untouched] == 3.0)
+
+
+def test_full_size_properties():
+    """Benchmark-size problem (G=128, 655360+ rows, K=2048, N=1536): the oracle is checked on a
+    sample of groups, and the whole result through linearity: C(A, B) + C(A, B) == C(A, 2B)."""
+    sizes = O.routing_sizes(128, 655360, seed=2026)
+    m = int(sizes.sum())
+    gen = torch.Generator(device=DEV).manual_seed(1)
+    a = (torch.randn(m, 2048, device=DEV, generator=gen) * 0.02).bfloat16()
+    b = (torch.randn(128, 1536, 2048, device=DEV, generator=gen) * 0.02).bfloat16()
+    sz = sizes.to(DEV)
+    c1 = m_grouped_gemm(a, b, sz, True)
+    c2 = m_grouped_gemm(a, b * 2, sz, True)
+    assert torch.equal(c1 * 2, c2)  # exact: scaling by 2 commutes with every rounding
+    starts = torch.cumsum(sizes, 0) - sizes
+    for g in (0, 63, 127):
+        s, n_rows = int(starts[g]), min(int(sizes[g]), 256)
+        ref = (a[s:s + n_rows].cpu().float() @ b[g].cpu().float().t()).bfloat16()
+        assert O.rdiff(c1[s:s + n_rows].cpu().float(), ref.float()) < 2e-4
+    # trans_b=False on the same data gives the same result
+    c3 = m_grouped_gemm(a, b.transpose(1, 2).contiguous(), sz, False)
+    assert O.rdiff(c3.float().cpu(), c1.float().cpu()) < 1e-5

@@ -1,0 +1,145 @@
+// Host/device helpers shared by every translation unit of the library: error reporting,
+// the device status word, tensor-map encoding, bounded mbarrier waits and the one-pass
+// group walker that replaces the reference's host-built tile metadata
+// (gemm/BF16/m_grouped_gemm_TMA.py:297-326 in the reference).
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "ptx.cuh"
+
+namespace b200 {
+
+// ------------------------------------------------------------------ status codes (C ABI return values)
+enum : int {
+  kOk = 0,
+  kErrInvalidArgument = -1,
+  kErrUnsupported = -2,
+  kErrCuda = -3,
+  kErrDriverEntry = -4,
+};
+
+// bits of the device status word (b200gemm_device_status)
+enum : unsigned {
+  kDevTimeoutProducer = 1u << 0,
+  kDevTimeoutMma = 1u << 1,
+  kDevTimeoutEpilogue = 1u << 2,
+  kDevTimeoutPromote = 1u << 3,
+  kDevBadGroupSize = 1u << 4,
+};
+
+// implemented in api.cu
+int set_error(int code, const char* fmt, ...);
+int check_cuda(cudaError_t e, const char* what);
+// device address of the per-device status word (set-up on first use, per device)
+unsigned* device_status_ptr();
+int sm_count();
+// cuTensorMapEncodeTiled through cudaGetDriverEntryPoint (no link-time libcuda dependency)
+int encode_tmap(CUtensorMap* out, CUtensorMapDataType dtype, int rank, const void* base, const uint64_t* dims,
+                const uint64_t* strides_bytes /* rank-1 entries */, const uint32_t* box, CUtensorMapSwizzle swz,
+                const char* what);
+
+#define B200_REQUIRE(cond, ...)                                   \
+  do {                                                            \
+    if (!(cond)) return ::b200::set_error(::b200::kErrInvalidArgument, __VA_ARGS__); \
+  } while (0)
+
+#define B200_CUDA(expr)                                          \
+  do {                                                           \
+    int _rc = ::b200::check_cuda((expr), #expr);                 \
+    if (_rc != 0) return _rc;                                    \
+  } while (0)
+
+// ------------------------------------------------------------------ bounded waits
+// Every spin on an mbarrier gives up after kWaitLimitNs; the waiting role then raises the
+// CTA-wide abort flag, records which role timed out in the device status word and leaves
+// its loop, so a protocol error ends in an error code instead of a hung GPU.
+constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
+
+__device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                             unsigned* status, unsigned role_bit) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = global_timer_ns();
+  uint32_t spins = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++spins & 63u) == 0u) {
+      if (*abort_flag) return false;
+      if (global_timer_ns() - t0 > kWaitLimitNs) {
+        *abort_flag = 1;
+        if (status) atomicOr(status, role_bit);
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+// ------------------------------------------------------------------ group walker
+// Tiles are numbered in "padded tile space": group g owns ceil(size_g / kTileRows)
+// consecutive row tiles.  A walker is advanced monotonically to the row tile a role is about
+// to process; all lanes of a warp run it redundantly (uniform loads, no divergence).
+// kind 0: contiguous rows (A is compact, group g starts at sum of earlier sizes)
+// kind 1: masked layout (group g starts at g * stride, only sizes[g] rows are valid)
+struct GroupWalker {
+  const void* sizes;
+  int sizes_i64;
+  int num_groups;
+  int stride;        // masked: rows per group slot; contiguous: unused
+  int tile_rows;
+  int g;             // current group
+  int tile_begin;    // first padded tile of group g
+  int ntiles;        // tiles of group g
+  int size;          // rows of group g
+  long long row_begin;  // first row of group g (contiguous kind)
+
+  __device__ __forceinline__ int load_size(int i) const {
+    long long v = sizes_i64 ? static_cast<const long long*>(sizes)[i]
+                            : static_cast<long long>(static_cast<const int*>(sizes)[i]);
+    if (v < 0) v = 0;
+    if (stride > 0 && v > stride) v = stride;
+    return static_cast<int>(v);
+  }
+
+  __device__ __forceinline__ void init(const void* sizes_, int sizes_i64_, int num_groups_, int stride_,
+                                       int tile_rows_) {
+    sizes = sizes_;
+    sizes_i64 = sizes_i64_;
+    num_groups = num_groups_;
+    stride = stride_;
+    tile_rows = tile_rows_;
+    g = 0;
+    tile_begin = 0;
+    row_begin = 0;
+    size = num_groups > 0 ? load_size(0) : 0;
+    ntiles = (size + tile_rows - 1) / tile_rows;
+  }
+
+  // Move to padded row tile `t` (t must not decrease between calls).  false = past the end.
+  __device__ __forceinline__ bool seek(int t) {
+    while (g < num_groups && t >= tile_begin + ntiles) {
+      tile_begin += ntiles;
+      row_begin += size;
+      ++g;
+      if (g < num_groups) {
+        size = load_size(g);
+        ntiles = (size + tile_rows - 1) / tile_rows;
+      }
+    }
+    return g < num_groups;
+  }
+
+  // first row (in the A / C row space) of padded tile t, and one-past-last valid row of the group
+  __device__ __forceinline__ long long tile_row0(int t) const {
+    long long base = stride > 0 ? static_cast<long long>(g) * stride : row_begin;
+    return base + static_cast<long long>(t - tile_begin) * tile_rows;
+  }
+  __device__ __forceinline__ long long group_row_end() const {
+    long long base = stride > 0 ? static_cast<long long>(g) * stride : row_begin;
+    return base + size;
+  }
+};
+
+}  // namespace b200
