@@ -1,0 +1,513 @@
+#!/usr/bin/env python
+"""Benchmark of the grouped-GEMM hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference] [--workload NAME]
+
+One "step" = one pass of the hot path over one batch: a single M-grouped GEMM launch over all
+experts a rank owns.  Default workload (``bf16_m_grouped_gate_up``): G=128 experts, 655 360
+routed rows (multinomial over softmax(N(0,0.5)) logits, each expert padded to 128 rows),
+K=2048, N=1536, trans_b=True, A and B ~ N(0,1)*0.02 in bf16, synthetic and seeded.  With N>1
+ranks (torchrun, one per GPU) the experts are partitioned G/N per rank and every rank keeps
+655 360 routed rows (weak scaling, no data-path collective; the only collectives are the
+barrier and the max-over-ranks of the timing).
+
+Prints ONE JSON line (rank 0).  ``value`` = device-timed TFLOP/s with inputs resident in HBM;
+``e2e`` = the same metric through the public Python operator with HOST (pinned) inputs and a
+host result, copies inside the timed region.  ``--impl reference`` times the reference's CPU
+path (torch per-group loop, restated in oracle/) on this host's cores on a bounded sample.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+WORKLOADS = {
+    # name: (kind, K, N, trans_b)
+    "bf16_m_grouped_gate_up": ("m_grouped", 2048, 1536, True),
+    "bf16_m_grouped_gate_up_nn": ("m_grouped", 2048, 1536, False),
+    "bf16_m_grouped_down": ("m_grouped", 768, 2048, True),
+    "bf16_k_grouped_wgrad": ("k_grouped", 2048, 768, False),
+    "fp8_block_m_grouped_gate_up": ("fp8_block", 4096, 3072, True),
+    "fp8_block_m_grouped_down": ("fp8_block", 1536, 4096, True),
+    "quant_act_1x128": ("quant_act", 4096, 0, True),
+}
+TOTAL_ROWS = 655360
+NUM_EXPERTS = 128
+ROUTING_SEED = 2026
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            d = json.loads(p.read_text())
+            return {"bf16": float(d["bf16_tflops"]), "bf16_sustained": float(d.get("bf16_tflops_sustained", 0) or 0),
+                    "hbm": float(d["hbm_gbs"]), "source": "measured"}
+        except Exception:
+            pass
+    return {"bf16": 1590.0, "bf16_sustained": 1400.0, "hbm": 6650.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples nvidia-smi SM clocks and throttle reasons while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines = []
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        clocks, maxes, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                clocks.append(float(parts[1]))
+                maxes.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(clocks) if clocks else None,
+                "sm_max_mhz": max(maxes) if maxes else None, "reasons": sorted(reasons), "samples": len(clocks)}
+
+
+def dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return rank, world, local
+
+
+def rank_sizes(world: int, rank: int) -> torch.Tensor:
+    """Row counts of the experts this rank owns.  Every rank keeps TOTAL_ROWS routed rows over
+    its NUM_EXPERTS/world experts (routing seed varies with the rank)."""
+    g_local = NUM_EXPERTS // world
+    gen = torch.Generator().manual_seed(ROUTING_SEED + rank)
+    logits = 0.5 * torch.randn(g_local, generator=gen)
+    draws = torch.multinomial(torch.softmax(logits, dim=0), TOTAL_ROWS, replacement=True, generator=gen)
+    counts = torch.bincount(draws, minlength=g_local)
+    return ((counts + 127) // 128 * 128).to(torch.int64)
+
+
+def make_inputs(kind, k, n, trans_b, sizes, device, seed):
+    gen = torch.Generator(device=device).manual_seed(seed)
+    m = int(sizes.sum())
+    g = sizes.numel()
+
+    def randn(shape, scale, chunk_rows=65536):
+        out = torch.empty(shape, device=device, dtype=torch.bfloat16)
+        flat = out.view(shape[0], -1)
+        for r in range(0, shape[0], chunk_rows):
+            rows = min(chunk_rows, shape[0] - r)
+            flat[r:r + rows] = (torch.randn(rows, flat.shape[1], device=device, generator=gen) * scale).bfloat16()
+        return out
+
+    if kind == "m_grouped":
+        a = randn((m, k), 0.02)
+        b = randn((g, n, k) if trans_b else (g, k, n), 0.02, chunk_rows=8)
+        return {"a": a, "b": b}
+    if kind == "k_grouped":
+        return {"a": randn((m, k), 0.02), "b": randn((m, n), 0.02)}
+    if kind == "fp8_block":
+        return {"x": randn((m, k), 1.0), "w": randn((g, n, k), 0.02, chunk_rows=4)}
+    if kind == "quant_act":
+        return {"x": randn((m, k), 1.0)}
+    raise ValueError(kind)
+
+
+def algorithmic_work(kind, k, n, sizes):
+    rows = int(sizes.sum())
+    if kind in ("m_grouped", "fp8_block"):
+        return 2.0 * rows * n * k, "flop"
+    if kind == "k_grouped":
+        return 2.0 * rows * n * k, "flop"  # M_DIM=k, N_DIM=n, K_total=rows
+    if kind == "quant_act":
+        return rows * k * 3.0 + rows * (k // 128) * 4.0, "byte"
+    raise ValueError(kind)
+
+
+def build_step(kind, k, n, trans_b, sizes_dev, inp):
+    """Returns (fn, launches_per_step).  fn() runs one step on the current stream."""
+    import triton_grouped_gemm_b200 as pkg  # noqa: F401
+
+    if kind == "m_grouped":
+        from triton_grouped_gemm_b200.gemm.BF16.m_grouped_gemm_TMA import _m_grouped_gemm_launch
+
+        a, b = inp["a"], inp["b"]
+        c = torch.empty(a.shape[0], n, device=a.device, dtype=a.dtype)
+        inp["c"] = c
+        return (lambda: _m_grouped_gemm_launch(a, b, c, sizes_dev, trans_b)), 1
+    if kind == "k_grouped":
+        from triton_grouped_gemm_b200.gemm.BF16.k_grouped_gemm_TMA import k_grouped_gemm
+
+        a, b = inp["a"], inp["b"]
+        return (lambda: inp.__setitem__("c", k_grouped_gemm(a, b, sizes_dev))), 1
+    if kind == "fp8_block":
+        from triton_grouped_gemm_b200.gemm.FP8.m_grouped_gemm_block_scaled import m_grouped_fp8_block_scaled
+        from triton_grouped_gemm_b200.quant.per_block_cast import per_block_cast_to_fp8, per_token_cast_to_fp8
+
+        a8, a_s = per_token_cast_to_fp8(inp["x"])
+        b8, b_s = per_block_cast_to_fp8(inp["w"])
+        del inp["x"], inp["w"]
+        out = torch.empty(a8.shape[0], n, device=a8.device, dtype=torch.bfloat16)
+        inp.update(a8=a8, a_s=a_s, b8=b8, b_s=b_s, c=out)
+        return (lambda: m_grouped_fp8_block_scaled((a8, a_s), (b8, b_s), sizes_dev, out=out)), 1
+    if kind == "quant_act":
+        from triton_grouped_gemm_b200.quant.per_block_cast import per_token_cast_to_fp8
+
+        x = inp["x"]
+        return (lambda: inp.__setitem__("c", per_token_cast_to_fp8(x))), 1
+    raise ValueError(kind)
+
+
+def cpu_reference_step(kind, k, n, trans_b, sizes, budget_work, seed=7):
+    """The reference's CPU path on a bounded sample: the first groups of the workload whose
+    algorithmic work adds up to ~budget_work.  Returns (fn, work_of_sample, description)."""
+    import oracle as O
+
+    picked, work = [], 0.0
+    for s in sizes.tolist():
+        if picked and work >= budget_work:
+            break
+        picked.append(int(s))
+        work += algorithmic_work(kind, k, n, torch.tensor([s]))[0]
+    ps = torch.tensor(picked, dtype=torch.int64)
+    gen = torch.Generator().manual_seed(seed)
+    m = int(ps.sum())
+    g = len(picked)
+    if kind == "m_grouped":
+        a = (torch.randn(m, k, generator=gen) * 0.02).bfloat16()
+        b = (torch.randn(g, n, k, generator=gen) * 0.02).bfloat16()
+        if not trans_b:
+            b = b.transpose(1, 2).contiguous()
+        fn = lambda: O.m_grouped_ref(a, b, ps, trans_b)  # noqa: E731
+    elif kind == "k_grouped":
+        a = (torch.randn(m, k, generator=gen) * 0.02).bfloat16()
+        b = (torch.randn(m, n, generator=gen) * 0.02).bfloat16()
+        fn = lambda: O.k_grouped_ref(a, b, ps)  # noqa: E731
+    elif kind == "fp8_block":
+        x = torch.randn(m, k, generator=gen).bfloat16()
+        w = (torch.randn(g, n, k, generator=gen) * 0.02).bfloat16()
+        a8, a_s = O.per_token_cast_to_fp8(x)
+        qs = [O.per_block_cast_to_fp8(w[i]) for i in range(g)]
+        b8 = torch.stack([q for q, _ in qs])
+        b_s = torch.stack([s for _, s in qs])
+        fn = lambda: O.fp8_block_m_grouped_ref(a8, a_s, b8, b_s, ps)  # noqa: E731
+    elif kind == "quant_act":
+        x = torch.randn(m, k, generator=gen).bfloat16()
+        fn = lambda: O.per_token_cast_to_fp8(x)  # noqa: E731
+    else:
+        raise ValueError(kind)
+    desc = f"first {g} of {sizes.numel()} groups ({m} rows) of the workload, torch {torch.__version__} on host cores"
+    return fn, work, desc
+
+
+def unit_of(kind):
+    return ("TFLOP/s", 1e12) if kind != "quant_act" else ("GB/s", 1e9)
+
+
+def run_reference(args):
+    rank, world, _ = dist_env()
+    if rank != 0:
+        return
+    kind, k, n, trans_b = WORKLOADS[args.workload]
+    sizes = rank_sizes(max(args.gpus, 1), 0)
+    unit, div = unit_of(kind)
+    budget = 0.6e12 if unit == "TFLOP/s" else 1.5e9
+    fn, work, desc = cpu_reference_step(kind, k, n, trans_b, sizes, budget)
+    for _ in range(max(args.warmup, 1)):
+        fn()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        fn()
+    dt = (time.perf_counter() - t0) / args.steps
+    value = work / dt / div
+    cores = torch.get_num_threads()
+    line = {
+        "impl": "reference", "metric": metric_name(kind), "value": value, "unit": unit, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": dtype_name(kind), "data": "synthetic",
+        "config": config_of(args.workload, kind, k, n, trans_b, sizes, args.gpus),
+        "cpu_baseline": {"value": value, "unit": unit, "cores": cores, "kind": "port", "sample": desc,
+                         "host_cpus": os.cpu_count()},
+        "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def metric_name(kind):
+    return {"m_grouped": "grouped-GEMM TFLOP/s (BF16 M-grouped)", "k_grouped": "grouped-GEMM TFLOP/s (BF16 K-grouped)",
+            "fp8_block": "grouped-GEMM TFLOP/s (FP8 block-scaled M-grouped)",
+            "quant_act": "per-block quantiser GB/s (1x128 e4m3)"}[kind]
+
+
+def dtype_name(kind):
+    return {"m_grouped": "bf16", "k_grouped": "bf16", "fp8_block": "fp8_e4m3", "quant_act": "bf16->fp8_e4m3"}[kind]
+
+
+def config_of(name, kind, k, n, trans_b, sizes, gpus):
+    return {"workload": name, "groups_per_gpu": int(sizes.numel()), "routed_rows_per_gpu": TOTAL_ROWS,
+            "padded_rows_rank0": int(sizes.sum()), "K": k, "N": n, "trans_b": trans_b,
+            "partition": f"experts split {NUM_EXPERTS}/{gpus} per GPU, no data-path collective",
+            "l2": "inputs (>2.7 GB per step) exceed the 126 MB L2; no explicit flush"}
+
+
+def run_b200(args):
+    rank, world, local = dist_env()
+    if world != max(args.gpus, 1):
+        # launched without torchrun but with --gpus N>1: only rank 0's share can run here
+        if world == 1 and args.gpus > 1:
+            print(json.dumps({"error": "launch with torch.distributed.run for --gpus > 1"}), flush=True)
+            return 2
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device (sm_100a); there is no CPU fallback")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    use_dist = world > 1
+    if use_dist:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=dev)
+    from triton_grouped_gemm_b200 import _lib
+
+    _lib.load()
+    kind, k, n, trans_b = WORKLOADS[args.workload]
+    sizes = rank_sizes(world, rank)
+    sizes_dev = sizes.to(dev)
+    inp = make_inputs(kind, k, n, trans_b, sizes, dev, seed=100 + rank)
+    step, launches = build_step(kind, k, n, trans_b, sizes_dev, inp)
+    work, _ = algorithmic_work(kind, k, n, sizes)
+    unit, div = unit_of(kind)
+
+    def barrier():
+        if use_dist:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.start()
+        time.sleep(0.25)
+    # ---- device-timed region: exactly `steps` steps, one CUDA event pair per step
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    barrier()
+    t_wall = time.perf_counter()
+    for s_ev, e_ev in evs:
+        s_ev.record()
+        step()
+        e_ev.record()
+    barrier()
+    t_wall = time.perf_counter() - t_wall
+    per_step = [s.elapsed_time(e) for s, e in evs]
+    total_ms = evs[0][0].elapsed_time(evs[-1][1])
+    clocks = sampler.stop() if sampler else None
+    status = _lib.device_status()
+    if status:
+        raise RuntimeError(f"device status word = {status:#x} (a bounded wait ran out)")
+
+    tot = torch.tensor([total_ms, work], device=dev, dtype=torch.float64)
+    if use_dist:
+        mx = tot.clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        sm = tot.clone()
+        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+        total_ms_max, work_all = float(mx[0]), float(sm[1])
+    else:
+        total_ms_max, work_all = total_ms, work
+    ms_per_step = total_ms_max / args.steps
+    value = work_all / (ms_per_step * 1e-3) / div
+
+    # ---- end to end through the public operator with host (pinned) buffers
+    e2e = run_e2e(args, kind, k, n, trans_b, sizes, inp, dev, use_dist, work_all if not use_dist else None, work)
+    if use_dist:
+        t = torch.tensor([e2e["ms"]], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e["ms"] = float(t[0])
+        e2e_value = work_all / (e2e["ms"] * 1e-3) / div
+    else:
+        e2e_value = work / (e2e["ms"] * 1e-3) / div
+
+    if rank == 0:
+        peaks = measured_peaks()
+        launch_ms = statistics.mean(per_step) / launches
+        if unit == "TFLOP/s":
+            peak = peaks["bf16"] * (2.0 if kind == "fp8_block" else 1.0)
+            achieved = work / (launch_ms * 1e-3) / 1e12
+            roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                    "traffic": None,
+                    "peak_source": f"{peaks['source']} cuBLAS bf16 burst" + (" x2 (no fp8 peak measured)" if kind == "fp8_block" else ""),
+                    "frac_of_nominal": achieved / (4500.0 if kind == "fp8_block" else 2250.0),
+                    "min_ms": min(per_step), "mean_ms": statistics.mean(per_step)}
+        else:
+            achieved = work / (launch_ms * 1e-3) / 1e9
+            roof = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm"], "unit": "GB/s",
+                    "frac": achieved / peaks["hbm"], "traffic": None, "peak_source": f"{peaks['source']} copy",
+                    "min_ms": min(per_step), "mean_ms": statistics.mean(per_step)}
+        cpu = None
+        if not args.no_cpu_baseline:
+            fn, cwork, desc = cpu_reference_step(kind, k, n, trans_b, sizes, 0.6e12 if unit == "TFLOP/s" else 1.5e9)
+            fn()
+            best = float("inf")
+            t_begin = time.perf_counter()
+            reps = 0
+            while reps < 3 or (time.perf_counter() - t_begin < 10 and reps < 20):
+                t0 = time.perf_counter()
+                fn()
+                best = min(best, time.perf_counter() - t0)
+                reps += 1
+            cpu = {"value": cwork / best / div, "unit": unit, "cores": torch.get_num_threads(), "kind": "port",
+                   "sample": desc + f"; best of {reps}", "host_cpus": os.cpu_count()}
+        line = {
+            "metric": metric_name(kind), "value": value, "unit": unit, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": dtype_name(kind), "data": "synthetic",
+            "config": config_of(args.workload, kind, k, n, trans_b, sizes, world),
+            "roofline": roof, "cpu_baseline": cpu,
+            "e2e": {"value": e2e_value, "unit": unit, "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"],
+                    "steps": e2e["steps"], "ms_per_step": e2e["ms"]},
+            "gpu_launches": launches * args.steps, "clocks": clocks, "wall_s_timed_region": t_wall,
+        }
+        print(json.dumps(line), flush=True)
+    if use_dist:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+def run_e2e(args, kind, k, n, trans_b, sizes, inp, dev, use_dist, _unused, work):
+    """Host inputs (pinned) -> device -> operator -> host result, every step."""
+    steps = max(1, min(args.steps, args.e2e_steps))
+    if kind == "m_grouped":
+        from triton_grouped_gemm_b200.gemm.BF16.m_grouped_gemm_TMA import m_grouped_gemm
+
+        host = {"a": inp["a"].cpu().pin_memory(), "b": inp["b"].cpu().pin_memory(), "s": sizes.pin_memory()}
+        out_host = torch.empty(inp["a"].shape[0], n, dtype=torch.bfloat16).pin_memory()
+        del inp["c"]
+
+        def one():
+            a = host["a"].to(dev, non_blocking=True)
+            b = host["b"].to(dev, non_blocking=True)
+            s = host["s"].to(dev, non_blocking=True)
+            c = m_grouped_gemm(a, b, s, trans_b)
+            out_host.copy_(c, non_blocking=True)
+    elif kind == "k_grouped":
+        from triton_grouped_gemm_b200.gemm.BF16.k_grouped_gemm_TMA import k_grouped_gemm
+
+        host = {"a": inp["a"].cpu().pin_memory(), "b": inp["b"].cpu().pin_memory(), "s": sizes.pin_memory()}
+        out_host = torch.empty(sizes.numel(), k, n, dtype=torch.bfloat16).pin_memory()
+
+        def one():
+            a = host["a"].to(dev, non_blocking=True)
+            b = host["b"].to(dev, non_blocking=True)
+            s = host["s"].to(dev, non_blocking=True)
+            out_host.copy_(k_grouped_gemm(a, b, s), non_blocking=True)
+    elif kind == "fp8_block":
+        from triton_grouped_gemm_b200.gemm.FP8.m_grouped_gemm_block_scaled import m_grouped_fp8_block_scaled
+
+        host = {kk: inp[kk].cpu().pin_memory() for kk in ("a8", "a_s", "b8", "b_s")}
+        host["s"] = sizes.pin_memory()
+        out_host = torch.empty(inp["a8"].shape[0], n, dtype=torch.bfloat16).pin_memory()
+        del inp["c"]
+
+        def one():
+            d = {kk: v.to(dev, non_blocking=True) for kk, v in host.items()}
+            c = m_grouped_fp8_block_scaled((d["a8"], d["a_s"]), (d["b8"], d["b_s"]), d["s"])
+            out_host.copy_(c, non_blocking=True)
+    else:
+        from triton_grouped_gemm_b200.quant.per_block_cast import per_token_cast_to_fp8
+
+        host = {"x": inp["x"].cpu().pin_memory()}
+        q_host = torch.empty(inp["x"].shape, dtype=torch.float8_e4m3fn).pin_memory()
+        s_host = torch.empty(inp["x"].shape[0], k // 128, dtype=torch.float32).pin_memory()
+        out_host = q_host
+
+        def one():
+            q, s = per_token_cast_to_fp8(host["x"].to(dev, non_blocking=True))
+            q_host.copy_(q, non_blocking=True)
+            s_host.copy_(s, non_blocking=True)
+        host["_extra_out"] = s_host
+    h2d = sum(v.numel() * v.element_size() for kk, v in host.items() if not kk.startswith("_"))
+    d2h = out_host.numel() * out_host.element_size() + sum(
+        v.numel() * v.element_size() for kk, v in host.items() if kk.startswith("_"))
+    one()
+    torch.cuda.synchronize()
+    if use_dist:
+        import torch.distributed as dist
+
+        dist.barrier()
+    torch.cuda.synchronize()
+    s_ev, e_ev = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s_ev.record()
+    for _ in range(steps):
+        one()
+    e_ev.record()
+    torch.cuda.synchronize()
+    return {"ms": s_ev.elapsed_time(e_ev) / steps, "h2d": h2d, "d2h": d2h, "steps": steps}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS), default="bf16_m_grouped_gate_up")
+    ap.add_argument("--e2e-steps", type=int, default=3, help="steps of the host-buffer end-to-end timing")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+        return 0
+    return run_b200(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main() or 0)

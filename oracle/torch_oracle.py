@@ -160,7 +160,9 @@ def per_token_cast_to_fp8(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
 
     amax over each 128-wide K block (taken on the 16-bit values, widened to fp32,
     clamped below at 1e-4); q = fp32(x) * (448 / amax) cast to e4m3 (round to
-    nearest even); scale = amax / 448.
+    nearest even); scale = amax / 448.  NOTE: ``448.0 / tensor`` is evaluated by torch as
+    ``tensor.reciprocal() * 448.0`` (two roundings) -- kept verbatim here because it
+    decides bytes; ``tensor / 448.0`` is a true division on the host.
     """
     assert x.dim() == 2 and x.size(1) % 128 == 0
     m, n = x.shape

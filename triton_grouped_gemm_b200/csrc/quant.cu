@@ -24,6 +24,11 @@ __device__ __forceinline__ uint32_t cvt_e4m3x2(float a, float b) {
   return static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3));
 }
 
+// The reference writes `448.0 / amax` with a Python scalar on the left; torch evaluates that
+// as reciprocal(amax) * 448 (two roundings), which differs from a single IEEE division in
+// the last bit often enough to flip e4m3 bytes.  Reproduce the two roundings.
+__device__ __forceinline__ float inv_scale_448(float amax) { return __fmul_rn(__frcp_rn(amax), 448.0f); }
+
 __device__ __forceinline__ float abs_max8(const uint4& v, int is_fp16) {
   const uint32_t w[4] = {v.x, v.y, v.z, v.w};
   float m = 0.f;
@@ -38,7 +43,7 @@ __device__ __forceinline__ float abs_max8(const uint4& v, int is_fp16) {
 // ------------------------------------------------------------------ 1x128 (activations)
 // Follows per_token_cast_to_fp8 (gemm/FP8/m_grouped_gemm_channel_expert.py:217-222):
 //   amax = max|x| over the block, clamped below at 1e-4
-//   q    = e4m3( fp32(x) * (448 / amax) ),  scale = amax / 448
+//   q    = e4m3( fp32(x) * (rcp(amax) * 448) ),  scale = amax / 448
 // 16 lanes own one block (8 elements = 16 bytes each): coalesced 16-byte loads, 8-byte stores.
 constexpr int kActThreads = 256;
 constexpr int kActUnroll = 4;
@@ -65,7 +70,7 @@ quant_act_1x128_kernel(const uint4* __restrict__ x, uint2* __restrict__ q, float
 #pragma unroll
       for (int o = 8; o >= 1; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
       amax = fmaxf(amax, 1e-4f);
-      const float inv = __fdiv_rn(448.0f, amax);
+      const float inv = inv_scale_448(amax);
       const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
       uint32_t out[2];
 #pragma unroll
@@ -139,7 +144,7 @@ quant_w_128x128_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ q, 
       amax = fmaxf(amax, abs_max8(v[p], is_fp16));
     }
     amax = fmaxf(block_max_256(amax, red), 1e-4f);
-    const float inv = __fdiv_rn(448.0f, amax);
+    const float inv = inv_scale_448(amax);
     if (threadIdx.x == 0) s[blk] = __fdiv_rn(amax, 448.0f);
 #pragma unroll
     for (int p = 0; p < 8; ++p) {
