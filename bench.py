@@ -47,6 +47,7 @@ WORKLOADS = {
 TOTAL_ROWS = 655360
 NUM_EXPERTS = 128
 ROUTING_SEED = 2026
+ROWS_USED = [TOTAL_ROWS]
 
 
 def measured_peaks():
@@ -122,13 +123,13 @@ def dist_env():
     return rank, world, local
 
 
-def rank_sizes(world: int, rank: int) -> torch.Tensor:
-    """Row counts of the experts this rank owns.  Every rank keeps TOTAL_ROWS routed rows over
-    its NUM_EXPERTS/world experts (routing seed varies with the rank)."""
-    g_local = NUM_EXPERTS // world
+def rank_sizes(world: int, rank: int, total_rows: int = TOTAL_ROWS, experts: int = NUM_EXPERTS) -> torch.Tensor:
+    """Row counts of the experts this rank owns.  Every rank keeps `total_rows` routed rows over
+    its experts/world experts (routing seed varies with the rank)."""
+    g_local = max(experts // world, 1)
     gen = torch.Generator().manual_seed(ROUTING_SEED + rank)
     logits = 0.5 * torch.randn(g_local, generator=gen)
-    draws = torch.multinomial(torch.softmax(logits, dim=0), TOTAL_ROWS, replacement=True, generator=gen)
+    draws = torch.multinomial(torch.softmax(logits, dim=0), total_rows, replacement=True, generator=gen)
     counts = torch.bincount(draws, minlength=g_local)
     return ((counts + 127) // 128 * 128).to(torch.int64)
 
@@ -255,7 +256,7 @@ def run_reference(args):
     if rank != 0:
         return
     kind, k, n, trans_b = WORKLOADS[args.workload]
-    sizes = rank_sizes(max(args.gpus, 1), 0)
+    sizes = rank_sizes(max(args.gpus, 1), 0, args.rows, args.experts)
     unit, div = unit_of(kind)
     budget = 0.6e12 if unit == "TFLOP/s" else 1.5e9
     fn, work, desc = cpu_reference_step(kind, k, n, trans_b, sizes, budget)
@@ -291,7 +292,7 @@ def dtype_name(kind):
 
 
 def config_of(name, kind, k, n, trans_b, sizes, gpus):
-    return {"workload": name, "groups_per_gpu": int(sizes.numel()), "routed_rows_per_gpu": TOTAL_ROWS,
+    return {"workload": name, "groups_per_gpu": int(sizes.numel()), "routed_rows_per_gpu": int(ROWS_USED[0]),
             "padded_rows_rank0": int(sizes.sum()), "K": k, "N": n, "trans_b": trans_b,
             "partition": f"experts split {NUM_EXPERTS}/{gpus} per GPU, no data-path collective",
             "l2": "inputs (>2.7 GB per step) exceed the 126 MB L2; no explicit flush"}
@@ -317,7 +318,7 @@ def run_b200(args):
 
     _lib.load()
     kind, k, n, trans_b = WORKLOADS[args.workload]
-    sizes = rank_sizes(world, rank)
+    sizes = rank_sizes(world, rank, args.rows, args.experts)
     sizes_dev = sizes.to(dev)
     inp = make_inputs(kind, k, n, trans_b, sizes, dev, seed=100 + rank)
     step, launches = build_step(kind, k, n, trans_b, sizes_dev, inp)
@@ -329,7 +330,8 @@ def run_b200(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(max(args.warmup, 3)):
+    warmup = args.warmup if args.profile else max(args.warmup, 3)
+    for _ in range(warmup):
         step()
     barrier()
     sampler = ClockSampler(local) if rank == 0 else None
@@ -366,6 +368,16 @@ def run_b200(args):
     value = work_all / (ms_per_step * 1e-3) / div
 
     # ---- end to end through the public operator with host (pinned) buffers
+    if args.profile:
+        # profiling run (under ncu): device-timed steps only, no host-buffer leg, no CPU leg
+        if rank == 0:
+            print(json.dumps({"profile_run": True, "workload": args.workload, "ms_per_step": ms_per_step,
+                              "value": value, "unit": unit, "rows": int(sizes.sum()), "groups": int(sizes.numel())}),
+                  flush=True)
+        if use_dist:
+            dist.barrier()
+            dist.destroy_process_group()
+        return 0
     e2e = run_e2e(args, kind, k, n, trans_b, sizes, inp, dev, use_dist, work_all if not use_dist else None, work)
     if use_dist:
         t = torch.tensor([e2e["ms"]], device=dev, dtype=torch.float64)
@@ -407,7 +419,7 @@ def run_b200(args):
                    "sample": desc + f"; best of {reps}", "host_cpus": os.cpu_count()}
         line = {
             "metric": metric_name(kind), "value": value, "unit": unit, "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": dtype_name(kind), "data": "synthetic",
             "config": config_of(args.workload, kind, k, n, trans_b, sizes, world),
             "roofline": roof, "cpu_baseline": cpu,
@@ -502,7 +514,12 @@ def main():
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="bf16_m_grouped_gate_up")
     ap.add_argument("--e2e-steps", type=int, default=3, help="steps of the host-buffer end-to-end timing")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--rows", type=int, default=TOTAL_ROWS, help="routed rows per GPU (default: the benchmark's 655360)")
+    ap.add_argument("--experts", type=int, default=NUM_EXPERTS, help="experts over all GPUs (default 128)")
+    ap.add_argument("--profile", action="store_true",
+                    help="for ncu captures: honour --warmup as given, skip the host-buffer and CPU legs")
     args = ap.parse_args()
+    ROWS_USED[0] = args.rows
     if args.impl == "reference":
         run_reference(args)
         return 0

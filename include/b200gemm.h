@@ -65,6 +65,14 @@ int b200gemm_m_grouped(const void* a, const void* b, void* c, const void* sizes,
                        int num_groups, int64_t m_rows, int n, int k, int trans_b, int dtype, int num_sms,
                        void* stream);
 
+/* Same product for the padded row layout of DeepGEMM's "contiguous" grouped GEMM, which the
+ * reference reaches through gemm/deep_gemm_ops.py:24-57: A and C hold each group's rows
+ * rounded up to a multiple of 128 (m_rows = sum of padded sizes); padding rows are neither
+ * read for results nor written. */
+int b200gemm_m_grouped_padded(const void* a, const void* b, void* c, const void* sizes, int sizes_is_i64,
+                              int num_groups, int64_t m_rows, int n, int k, int trans_b, int dtype, int num_sms,
+                              void* stream);
+
 /* Masked M-grouped GEMM: for each g, rows [g*expected_m, g*expected_m + masked_m[g]) of
  * out = same rows of lhs * rhs[g]^T; other rows of out are left untouched.
  * Replaces m_grouped_gemm_masked + m_grouped_gemm_masked_kernel
@@ -74,6 +82,60 @@ int b200gemm_m_grouped(const void* a, const void* b, void* c, const void* sizes,
 int b200gemm_m_grouped_masked(const void* lhs, const void* rhs, void* out, const void* masked_m,
                               int sizes_is_i64, int num_groups, int expected_m, int n, int k, int trans_b,
                               int dtype, int num_sms, void* stream);
+
+/* K-grouped GEMM (expert weight gradient): C[g] = A[gs:ge, :]^T * B[gs:ge, :], fp32
+ * accumulate, one rounding; an empty group yields zeros.  Replaces k_grouped_gemm +
+ * k_grouped_gemm_kernel (gemm/BF16/k_grouped_gemm_TMA.py:71-294; sm_80 twin
+ * gemm/BF16/k_grouped_gemm.py:62-216).
+ *   A [k_total, m_dim], B [k_total, n_dim] row-major; C [G, m_dim, n_dim].
+ *   Token ranges: group_start/group_end (int32 [G], both or neither) if given, else the
+ *   running prefix of sizes [G].  Requires m_dim % 8 == 0, n_dim % 8 == 0. */
+int b200gemm_k_grouped(const void* a, const void* b, void* c, const void* sizes, int sizes_is_i64,
+                       const int* group_start, const int* group_end, int num_groups, int64_t k_total, int m_dim,
+                       int n_dim, int dtype, int num_sms, void* stream);
+
+/* ---- FP8 grouped GEMMs with per-row x per-channel scales ------------------------------- */
+
+/* FP8 M-grouped GEMM: C[m, n] = (sum_k A[m,k] * B[g,n,k])_fp32 * a_scale[m] * b_scale[g*n_dim+n].
+ * Replaces gmm_fp8_act_per_channel_w_per_expert + its Triton kernel
+ * (gemm/FP8/m_grouped_gemm_channel_expert.py:64-198).  A [m_rows, k] fp8 (fmt_a), a_scale
+ * [m_rows] fp32, B [G, n, k] fp8 (fmt_b), b_scale [G*n] fp32, C [m_rows, n] of out_dtype
+ * (0 = bf16, 1 = fp16).  Requires k % 16 == 0, n % 8 == 0. */
+int b200gemm_fp8_m_grouped_rowcol(const void* a, const float* a_scale, const void* b, const float* b_scale, void* c,
+                                  const void* sizes, int sizes_is_i64, int num_groups, int64_t m_rows, int n, int k,
+                                  int fmt_a, int fmt_b, int out_dtype, int num_sms, void* stream);
+
+/* FP8 K-grouped GEMM: out[g, m, n] = (sum_{k in group g} X[m,k] * Y[n,k])_fp32 *
+ * x_scale[g*m_dim+m] * y_scale[g*n_dim+n] -> bf16.  Replaces matmul + gemm_kernel_tma
+ * (gemm/FP8/k_grouped_gemm_channel_expert.py:64-181).  X [m_dim, k_total], Y [n_dim, k_total]
+ * fp8, K-major; the scales are group-major in memory; tokens_per_expert[g] must be a multiple
+ * of 128 with zero-padded data, as in the reference.  out [G, m_dim, n_dim] bf16. */
+int b200gemm_fp8_k_grouped_rowcol(const void* x, const float* x_scale, const void* y, const float* y_scale, void* out,
+                                  const void* tokens_per_expert, int sizes_is_i64, int num_groups, int64_t k_total,
+                                  int m_dim, int n_dim, int fmt_x, int fmt_y, int num_sms, void* stream);
+
+/* ---- FP8 grouped GEMMs with 1x128 / 128x128 block scales -------------------------------- */
+
+/* Block-scaled FP8 M-grouped GEMM:
+ *   C[m,n] = sum_kb (sum_{k in kb} a[m,k] * b[g,n,k]) * a_scale[m,kb] * b_scale[g, n/128, kb] -> bf16.
+ * The reference has no kernel of its own for this: gemm/deep_gemm_ops.py:60-100 forwards to the
+ * external DeepGEMM package; this entry point takes over that call with fp32 scales as produced
+ * by per_token_cast_to_fp8 / per_block_cast_to_fp8
+ * (gemm/FP8/m_grouped_gemm_channel_expert.py:217-245).
+ *   a [m_rows, k] e4m3, a_scale [m_rows, ceil(k/128)] fp32 (row-major);
+ *   b [G, n, k] e4m3, b_scale [G, ceil(n/128), ceil(k/128)] fp32; c [m_rows, n] bf16.
+ *   rows_padded == 0: a / c rows are compact; != 0: each group's rows are padded to 128 (the
+ *   layout gemm/deep_gemm_ops.py:87-89 requires).  Requires k % 16 == 0, n % 8 == 0. */
+int b200gemm_fp8_m_grouped_block(const void* a, const float* a_scale, const void* b, const float* b_scale, void* c,
+                                 const void* sizes, int sizes_is_i64, int num_groups, int64_t m_rows, int n, int k,
+                                 int rows_padded, int num_sms, void* stream);
+
+/* Masked-layout twin (decode): rows [g*expected_m, g*expected_m + masked_m[g]) of out.  No
+ * reference counterpart as a kernel; it combines the masked layout of
+ * gemm/BF16/m_grouped_gemm_masked_TMA.py:164-250 with the block-scaled contract above. */
+int b200gemm_fp8_m_grouped_masked_block(const void* a, const float* a_scale, const void* b, const float* b_scale,
+                                        void* out, const void* masked_m, int sizes_is_i64, int num_groups,
+                                        int expected_m, int n, int k, int num_sms, void* stream);
 
 /* ---- per-block FP8 (e4m3) quantisers: bytes and fp32 scales identical to the reference's
  *      torch functions ------------------------------------------------------------------ */

@@ -1,0 +1,180 @@
+"""Block-scaled FP8 M-grouped / masked GEMM against the CPU oracle (dequantise, fp32 matmul,
+one rounding to bf16).  Tolerance rdiff <= 2e-3 (build target); the kernel accumulates the
+same products in a different order and multiplies the scales after instead of before the
+block sum, so 5e-4 is asserted."""
+
+import pytest
+import torch
+
+import oracle as O
+from triton_grouped_gemm_b200 import _lib
+from triton_grouped_gemm_b200.gemm import deep_gemm_ops
+from triton_grouped_gemm_b200.gemm.FP8.m_grouped_gemm_block_scaled import (
+    m_grouped_fp8_block_scaled,
+    m_grouped_fp8_block_scaled_masked,
+)
+from triton_grouped_gemm_b200.quant.per_block_cast import per_block_cast_to_fp8, per_token_cast_to_fp8
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+TOL = 5e-4
+
+
+@pytest.fixture(autouse=True)
+def _status_clean():
+    yield
+    assert _lib.device_status() == 0
+
+
+def _quantised(m, g, n, k, seed):
+    gen = torch.Generator().manual_seed(seed)
+    x = torch.randn(m, k, generator=gen).bfloat16()
+    w = (torch.randn(g, n, k, generator=gen) * 0.02).bfloat16()
+    a8, a_s = O.per_token_cast_to_fp8(x)
+    qs = [O.per_block_cast_to_fp8(w[i]) for i in range(g)]
+    return a8, a_s, torch.stack([q for q, _ in qs]), torch.stack([s for _, s in qs])
+
+
+def test_single_block_known_answer():
+    """One 128x128x128 block with unit scales and small integers: exact."""
+    m = n = k = 128
+    a = ((torch.arange(m)[:, None] + torch.arange(k)[None, :]) % 5 - 2).float()
+    b = ((torch.arange(n)[:, None] * 2 + torch.arange(k)[None, :]) % 7 - 3).float()
+    ref = (a @ b.t()) * 0.5 * 0.25
+    a8, b8 = a.to(torch.float8_e4m3fn), b.to(torch.float8_e4m3fn)[None].contiguous()
+    a_s = torch.full((m, 1), 0.5)
+    b_s = torch.full((1, 1, 1), 0.25)
+    out = m_grouped_fp8_block_scaled((a8.to(DEV), a_s.to(DEV)), (b8.to(DEV), b_s.to(DEV)),
+                                     torch.tensor([m], device=DEV)).cpu()
+    assert torch.equal(out.float(), ref.bfloat16().float())
+
+
+@pytest.mark.parametrize("sizes,n,k", [
+    ([128], 128, 128),
+    ([128], 256, 256),
+    ([300, 0, 1, 127, 129], 384, 512),
+    ([5, 700], 3072, 1024),
+    ([64, 64], 200, 400),            # n not a multiple of 128, k not a multiple of 128
+    ([130] * 30, 512, 384),
+])
+def test_compact_vs_oracle(sizes, n, k):
+    m, g = sum(sizes), len(sizes)
+    a8, a_s, b8, b_s = _quantised(m + 3, g, n, (k + 127) // 128 * 128, seed=n + k + g)
+    if k % 128:
+        a8, b8 = a8[:, :k].contiguous(), b8[:, :, :k].contiguous()
+        kpad = a_s.shape[1] * 128
+        a_ref = torch.zeros(m + 3, kpad, dtype=a8.dtype)
+        a_ref[:, :k] = a8
+        b_ref = torch.zeros(g, (n + 127) // 128 * 128, kpad, dtype=b8.dtype)
+        b_ref[:, :n, :k] = b8
+    else:
+        a_ref = a8
+        b_ref = torch.zeros(g, (n + 127) // 128 * 128, k, dtype=b8.dtype)
+        b_ref[:, :n] = b8
+    ref = O.fp8_block_m_grouped_ref(a_ref[:m], a_s[:m], b_ref, b_s, sizes)[:, :n]
+    out = torch.full((m + 3, n), float("nan"), dtype=torch.bfloat16, device=DEV)
+    m_grouped_fp8_block_scaled((a8.to(DEV), a_s.to(DEV)), (b8.to(DEV), b_s.to(DEV)),
+                               torch.tensor(sizes, device=DEV), out=out)
+    out = out.cpu()
+    assert not torch.isnan(out[:m].float()).any()
+    assert torch.isnan(out[m:].float()).all()
+    assert O.rdiff(out[:m].float(), ref.float()) < TOL
+
+
+def test_gpu_quantisers_feed_the_gemm():
+    """bf16 -> GPU quantisers -> GPU GEMM equals the all-oracle pipeline."""
+    sizes = [200, 56, 384]
+    m, g, n, k = sum(sizes), 3, 512, 768
+    gen = torch.Generator().manual_seed(9)
+    x = torch.randn(m, k, generator=gen).bfloat16()
+    w = (torch.randn(g, n, k, generator=gen) * 0.02).bfloat16()
+    a = per_token_cast_to_fp8(x.to(DEV))
+    b = per_block_cast_to_fp8(w.to(DEV))
+    out = m_grouped_fp8_block_scaled(a, b, torch.tensor(sizes, device=DEV)).cpu()
+    a8, a_s = O.per_token_cast_to_fp8(x)
+    qs = [O.per_block_cast_to_fp8(w[i]) for i in range(g)]
+    ref = O.fp8_block_m_grouped_ref(a8, a_s, torch.stack([q for q, _ in qs]), torch.stack([s for _, s in qs]), sizes)
+    assert O.rdiff(out.float(), ref.float()) < TOL
+    # and close to the unquantised product (fp8 quantisation noise only)
+    full = O.m_grouped_ref(x, w, sizes, True).float()
+    assert O.rdiff(out.float(), full) < 0.06
+
+
+@pytest.mark.parametrize("g,e,n,k", [(16, 256, 3072, 512), (4, 128, 128, 256), (3, 384, 640, 384)])
+def test_masked_vs_oracle(g, e, n, k):
+    a8, a_s, b8, b_s = _quantised(g * e, g, n, k, seed=g + e)
+    gen = torch.Generator().manual_seed(e)
+    masked = torch.randint(0, e + 1, (g,), generator=gen)
+    masked[0] = e
+    if g > 2:
+        masked[1] = 0
+    init = torch.full((g * e, n), 3.0, dtype=torch.bfloat16)
+    ref = O.fp8_block_m_grouped_masked_ref(a8, a_s, b8, b_s, init, masked, e)
+    out = init.clone().to(DEV)
+    assert m_grouped_fp8_block_scaled_masked((a8.to(DEV), a_s.to(DEV)), (b8.to(DEV), b_s.to(DEV)), out,
+                                             masked.to(DEV), e) is None
+    out = out.cpu()
+    assert O.rdiff(out.float(), ref.float()) < TOL
+    untouched = torch.ones(g * e, dtype=torch.bool)
+    for i, m in enumerate(masked.tolist()):
+        untouched[i * e:i * e + m] = False
+    assert torch.all(out[untouched] == 3.0)
+
+
+def test_deep_gemm_ops_padded_layout():
+    """The reference's wrapper contract (gemm/deep_gemm_ops.py:60-100): A holds padded rows."""
+    sizes = [130, 5, 256]
+    padded = [256, 128, 256]
+    g, n, k = 3, 256, 256
+    a8, a_s, b8, b_s = _quantised(sum(padded), g, n, k, seed=4)
+    st = torch.tensor(sizes, device=DEV)
+    out = torch.full((sum(padded), n), 9.0, dtype=torch.bfloat16, device=DEV)
+    res = deep_gemm_ops.m_grouped_fp8_nt_contiguous((a8.to(DEV), a_s.to(DEV)), (b8.to(DEV), b_s.to(DEV)), st, out=out)
+    assert res.data_ptr() == out.data_ptr()
+    out = out.cpu()
+    row = 0
+    for i, (s, p) in enumerate(zip(sizes, padded)):
+        ref = O.fp8_block_m_grouped_ref(a8[row:row + s], a_s[row:row + s], b8[i:i + 1], b_s[i:i + 1], [s])
+        assert O.rdiff(out[row:row + s].float(), ref.float()) < TOL
+        assert torch.all(out[row + s:row + p] == 9.0)
+        row += p
+    with pytest.raises(ValueError, match="A must include padded expert rows"):
+        deep_gemm_ops.m_grouped_fp8_nt_contiguous((a8[:-128].to(DEV), a_s[:-128].to(DEV)),
+                                                  (b8.to(DEV), b_s.to(DEV)), st)
+    # bf16 twin
+    gen = torch.Generator().manual_seed(1)
+    a = torch.randn(sum(padded), k, generator=gen).bfloat16()
+    b = torch.randn(g, n, k, generator=gen).bfloat16()
+    o = torch.full((sum(padded), n), 9.0, dtype=torch.bfloat16, device=DEV)
+    deep_gemm_ops.m_grouped_bf16_nt_contiguous(a.to(DEV), b.to(DEV), st, out=o)
+    o = o.cpu()
+    row = 0
+    for i, (s, p) in enumerate(zip(sizes, padded)):
+        ref = (a[row:row + s].float() @ b[i].float().t()).bfloat16()
+        assert O.rdiff(o[row:row + s].float(), ref.float()) < 2e-4
+        assert torch.all(o[row + s:row + p] == 9.0)
+        row += p
+
+
+def test_full_size_properties():
+    """Benchmark size (G=128, ~663k rows, K=4096, N=3072): sampled rows against the oracle and
+    exact linearity in the weight scales over the whole output."""
+    sizes = O.routing_sizes(128, 655360, seed=2026)
+    m = int(sizes.sum())
+    gen = torch.Generator(device=DEV).manual_seed(3)
+    x = torch.randn(m, 4096, device=DEV, generator=gen, dtype=torch.bfloat16)
+    w = (torch.randn(128, 3072, 4096, device=DEV, generator=gen, dtype=torch.bfloat16) * 0.02)
+    a = per_token_cast_to_fp8(x)
+    b = per_block_cast_to_fp8(w)
+    del x, w
+    sz = sizes.to(DEV)
+    c1 = m_grouped_fp8_block_scaled(a, b, sz)
+    c2 = m_grouped_fp8_block_scaled(a, (b[0], b[1] * 2), sz)
+    assert torch.equal(c1 * 2, c2)
+    starts = torch.cumsum(sizes, 0) - sizes
+    for g in (0, 64, 127):
+        s = int(starts[g])
+        rows = 64
+        ref = O.fp8_block_m_grouped_ref(a[0][s:s + rows].cpu(), a[1][s:s + rows].cpu(), b[0][g:g + 1].cpu(),
+                                        b[1][g:g + 1].cpu(), [rows])
+        assert O.rdiff(c1[s:s + rows].float().cpu(), ref.float()) < TOL

@@ -1,0 +1,92 @@
+"""FP8 grouped GEMMs with per-row x per-channel scales against the CPU oracle (dequantised
+fp32 reference of the same fp8 bytes).  Tolerance rdiff <= 2e-3; only accumulation order and
+the final rounding differ, so 5e-4 is asserted."""
+
+import pytest
+import torch
+
+import oracle as O
+from triton_grouped_gemm_b200 import _lib
+from triton_grouped_gemm_b200.gemm.FP8.k_grouped_gemm_channel_expert import matmul
+from triton_grouped_gemm_b200.gemm.FP8.m_grouped_gemm_channel_expert import gmm_fp8_act_per_channel_w_per_expert
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+E4, E5 = torch.float8_e4m3fn, torch.float8_e5m2
+
+
+@pytest.fixture(autouse=True)
+def _status_clean():
+    yield
+    _lib.load().b200gemm_set_block_n(0)
+    assert _lib.device_status() == 0
+
+
+@pytest.mark.parametrize("block_n", [0, 64, 128, 256])
+@pytest.mark.parametrize("dt_a,dt_b", [(E4, E4), (E5, E4)])
+@pytest.mark.parametrize("sizes,n,k,dtype_out", [
+    ([128], 256, 128, torch.bfloat16),
+    ([125, 0, 509, 3], 384, 640, torch.float16),
+    ([300, 77], 264, 272, torch.bfloat16),     # n and k tails
+])
+def test_m_grouped_rowcol(sizes, n, k, dtype_out, dt_a, dt_b, block_n):
+    gen = torch.Generator().manual_seed(n + k + len(sizes))
+    m, g = sum(sizes), len(sizes)
+    x = torch.randn(m + 5, (k + 127) // 128 * 128, generator=gen).bfloat16()
+    w = torch.randn(g, 128, 128, generator=gen).bfloat16()
+    a8, a_s = O.per_channel_cast_to_fp8(x, dt_a)
+    a8 = a8[:, :k].contiguous()
+    b8 = (torch.randn(g, n, k, generator=gen) * 100).clamp(-400, 400).to(dt_b)
+    b_s = torch.rand(g, n, generator=gen) * 0.01 + 0.001
+    del w
+    ref = O.fp8_rowcol_m_grouped_ref(a8[:m], a_s[:m], b8, b_s, sizes, dtype_out)
+    _lib.load().b200gemm_set_block_n(block_n)
+    out = gmm_fp8_act_per_channel_w_per_expert(a8.to(DEV), a_s.to(DEV), b8.to(DEV), b_s.reshape(-1).to(DEV),
+                                               torch.tensor(sizes, dtype=torch.int32, device=DEV), dtype_out).cpu()
+    assert out.dtype == dtype_out and out.shape == (m + 5, n)
+    assert O.rdiff(out[:m].float(), ref.float()) < 5e-4
+
+
+def test_m_grouped_rowcol_reference_test_shape_family():
+    """Scaled-down version of the reference's own test (tests/test_FP8/
+    test_m_grouped_gemm_channel_expert.py:104-126): ragged experts, e5m2 activations x e4m3
+    weights, per-expert weight scale expanded to [G, N]."""
+    bias = 3
+    tokens = [512 - bias, 1024 - 512 + bias, 128 - bias, 1024 - 128 + bias] * 2
+    n, k = 768, 640
+    gen = torch.Generator().manual_seed(0)
+    m, g = sum(tokens), len(tokens)
+    x = torch.randn(m, k, generator=gen).bfloat16()
+    w = torch.randn(g, n, k, generator=gen).bfloat16()
+    a8, a_s = O.per_channel_cast_to_fp8(x, E5)
+    b8, b_s = O.per_expert_cast_to_fp8(w, E4)
+    b_s_full = b_s.view(-1, 1).repeat(1, n)
+    ref = O.fp8_rowcol_m_grouped_ref(a8, a_s, b8, b_s_full, tokens, torch.bfloat16)
+    out = gmm_fp8_act_per_channel_w_per_expert(a8.to(DEV), a_s.to(DEV), b8.to(DEV), b_s_full.to(DEV),
+                                               torch.tensor(tokens, dtype=torch.int32, device=DEV),
+                                               dtype_out=torch.bfloat16).cpu()
+    assert O.rdiff(out.float(), ref.float()) < 5e-4
+    # and the quantised product is close to the unquantised one, as the reference's test prints
+    full = O.m_grouped_ref(x, w, tokens, True).float()
+    assert (out.float() - full).abs().max() / full.abs().max() < 0.1
+
+
+@pytest.mark.parametrize("dt_a,dt_b", [(E4, E4), (E5, E4)])
+@pytest.mark.parametrize("tokens,m,n", [([128], 128, 256), ([256, 0, 128, 512], 256, 384), ([128, 128], 136, 72)])
+def test_k_grouped_rowcol(tokens, m, n, dt_a, dt_b):
+    gen = torch.Generator().manual_seed(m + n + len(tokens))
+    g, k_tot = len(tokens), sum(tokens)
+    x8 = (torch.randn(m, k_tot, generator=gen) * 50).to(dt_a)
+    y8 = (torch.randn(n, k_tot, generator=gen) * 50).to(dt_b)
+    # logical [M, G] with group-major memory, as the reference's data generator builds it
+    xs = (torch.rand(g, m, generator=gen) * 0.01 + 0.001).t()
+    ys = (torch.rand(g, n, generator=gen) * 0.01 + 0.001).t()
+    assert xs.stride() == (1, m) or g == 1
+    ref = O.fp8_rowcol_k_grouped_ref(x8, xs, y8, ys, tokens, m, n, g)
+    out = matmul(x8.to(DEV), xs.to(DEV), y8.to(DEV), ys.to(DEV), torch.tensor(tokens, dtype=torch.int32, device=DEV),
+                 m, n, k_tot, g, 1 if dt_a == E4 else 2, 1 if dt_b == E4 else 2).cpu()
+    assert out.shape == (g, m, n) and out.dtype == torch.bfloat16
+    assert O.rdiff(out.float(), ref.float()) < 5e-4
+    for i, t in enumerate(tokens):
+        if t == 0:
+            assert torch.all(out[i] == 0)

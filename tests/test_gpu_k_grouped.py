@@ -1,0 +1,134 @@
+"""BF16 / FP16 K-grouped GEMM (C[g] = A_g^T B_g) on the GPU against the CPU oracle.
+Tolerance: rdiff <= 2e-3 (build target); asserted tighter because only accumulation order
+differs from the oracle's fp32-accumulated, once-rounded result."""
+
+import pytest
+import torch
+
+import oracle as O
+from triton_grouped_gemm_b200 import _lib
+from triton_grouped_gemm_b200.gemm.BF16.k_grouped_gemm_TMA import k_grouped_gemm
+from triton_grouped_gemm_b200.gemm.BF16 import k_grouped_gemm as k_mod
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+@pytest.fixture(autouse=True)
+def _status_clean():
+    yield
+    assert _lib.device_status() == 0
+
+
+def test_golden(golden_dir):
+    c = torch.load(golden_dir / "k_grouped.pt", weights_only=False)
+    out = k_grouped_gemm(c["a"].to(DEV), c["b"].to(DEV), c["sizes"].to(DEV)).cpu()
+    assert out.shape == c["out"].shape
+    assert O.rdiff(out.float(), c["out"].float()) < 2e-4
+    assert torch.all(out[1] == 0)  # empty group -> zeros
+
+
+@pytest.mark.parametrize("trans", [True, False])
+def test_known_answer_single_block(trans):
+    """64 tokens, one-hot A: C[g][m, n] = B[token(m), n] exactly."""
+    k_tot, m_dim, n_dim = 64, 128, 256
+    a = torch.zeros(k_tot, m_dim)
+    a[torch.arange(m_dim) % k_tot, torch.arange(m_dim)] = 1.0
+    b = ((torch.arange(k_tot)[:, None] * 7 + torch.arange(n_dim)[None, :] * 3) % 101 - 50).float()
+    ref = a.t() @ b
+    out = k_grouped_gemm(a.bfloat16().to(DEV), b.bfloat16().to(DEV), torch.tensor([k_tot], device=DEV)).cpu()
+    assert torch.equal(out[0].float(), ref)
+
+
+CASES = [
+    # sizes, M_DIM, N_DIM
+    ([64], 128, 256),
+    ([1], 128, 64),
+    ([63, 65, 0, 17, 128, 200], 256, 512),
+    ([5, 0, 0, 300], 136, 72),          # M_DIM / N_DIM not multiples of the tile
+    ([1000, 24, 40], 2048, 768),
+    ([16] * 20, 128, 128),
+    ([0, 0], 128, 128),
+]
+
+
+@pytest.mark.parametrize("sizes,m_dim,n_dim", CASES)
+@pytest.mark.parametrize("size_dtype", [torch.int32, torch.int64])
+def test_ragged_vs_oracle(sizes, m_dim, n_dim, size_dtype):
+    gen = torch.Generator().manual_seed(m_dim + n_dim + len(sizes))
+    k_tot = sum(sizes)
+    extra = 9  # rows after the last group must not leak into it
+    a = (torch.randn(k_tot + extra, m_dim, generator=gen) * 0.5).bfloat16()
+    b = (torch.randn(k_tot + extra, n_dim, generator=gen) * 0.5).bfloat16()
+    ref = O.k_grouped_ref(a[:k_tot], b[:k_tot], sizes, fp32_accumulate_explicit=True)
+    out = k_grouped_gemm(a.to(DEV), b.to(DEV), torch.tensor(sizes, dtype=size_dtype, device=DEV)).cpu()
+    assert out.shape == ref.shape
+    assert not torch.isnan(out.float()).any()
+    assert O.rdiff(out.float(), ref.float()) < 2e-4
+    for g, s in enumerate(sizes):
+        if s == 0:
+            assert torch.all(out[g] == 0)
+
+
+def test_tail_rows_of_next_group_do_not_leak_even_if_nonfinite():
+    """The k-block holding a group's tail also holds the next group's first rows; they are
+    zeroed in shared memory, so even Inf/NaN there must not reach this group's result."""
+    sizes = [40, 50]
+    gen = torch.Generator().manual_seed(3)
+    a = torch.randn(90, 128, generator=gen).bfloat16()
+    b = torch.randn(90, 128, generator=gen).bfloat16()
+    a[40:48] = float("inf")
+    b[40:48] = float("nan")
+    out = k_grouped_gemm(a.to(DEV), b.to(DEV), torch.tensor(sizes, device=DEV)).cpu()
+    ref0 = (a[:40].float().t() @ b[:40].float()).bfloat16()
+    assert torch.isfinite(out[0].float()).all()
+    assert O.rdiff(out[0].float(), ref0.float()) < 2e-4
+
+
+def test_explicit_group_ranges_and_fp16_and_alias_module():
+    gen = torch.Generator().manual_seed(11)
+    sizes = torch.tensor([70, 30, 100])
+    a = torch.randn(200, 128, generator=gen).half()
+    b = torch.randn(200, 192, generator=gen).half()
+    ref = O.k_grouped_ref(a, b, sizes, fp32_accumulate_explicit=True)
+    ends = sizes.cumsum(0)
+    starts = ends - sizes
+    out = k_grouped_gemm(a.to(DEV), b.to(DEV), sizes.to(DEV), starts.to(DEV), ends.to(DEV)).cpu()
+    assert O.rdiff(out.float(), ref.float()) < 2e-4
+    out2 = k_mod.k_grouped_gemm(a.to(DEV), b.to(DEV), sizes.to(DEV)).cpu()
+    assert torch.equal(out, out2)
+
+
+def test_input_checks():
+    a = torch.zeros(16, 128, dtype=torch.bfloat16, device=DEV)
+    b = torch.zeros(16, 128, dtype=torch.bfloat16, device=DEV)
+    s = torch.tensor([16], device=DEV)
+    with pytest.raises(AssertionError, match="trans_b=True path has been removed"):
+        k_grouped_gemm(a, b, s, trans_b=True)
+    with pytest.raises(AssertionError, match="must equal"):
+        k_grouped_gemm(a, b[:8], s)
+    with pytest.raises(AssertionError, match="int32 or int64"):
+        k_grouped_gemm(a, b, s.float())
+
+
+def test_full_size_properties():
+    """Benchmark size (G=128, K_total ~ 663k, 2048 x 768): sampled groups against the oracle and
+    exact linearity in B over the whole output."""
+    sizes = O.routing_sizes(128, 655360, seed=2026)
+    k_tot = int(sizes.sum())
+    gen = torch.Generator(device=DEV).manual_seed(2)
+    a = (torch.randn(k_tot, 2048, device=DEV, generator=gen) * 0.02).bfloat16()
+    b = (torch.randn(k_tot, 768, device=DEV, generator=gen) * 0.02).bfloat16()
+    sz = sizes.to(DEV)
+    c1 = k_grouped_gemm(a, b, sz)
+    c2 = k_grouped_gemm(a, b * 2, sz)
+    assert torch.equal(c1 * 2, c2)
+    starts = torch.cumsum(sizes, 0) - sizes
+    for g in (0, 77, 127):
+        s, e = int(starts[g]), int(starts[g] + sizes[g])
+        ref = (a[s:e].float().t() @ b[s:e].float()).bfloat16()  # fp32 on the GPU as a cross-check only
+        assert O.rdiff(c1[g].float().cpu(), ref.float().cpu()) < 1e-3
+    g = 5
+    s, e = int(starts[g]), int(starts[g] + sizes[g])
+    ref = (a[s:e].cpu().float().t() @ b[s:e].cpu().float()).bfloat16()
+    assert O.rdiff(c1[g].float().cpu(), ref.float()) < 2e-4

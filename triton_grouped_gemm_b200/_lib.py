@@ -27,8 +27,20 @@ _SIGNATURES = {
     "b200gemm_set_block_n": [c_int],
     "b200gemm_m_grouped": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_int, c_int, c_int, c_int,
                            c_int, c_void_p],
+    "b200gemm_m_grouped_padded": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_int, c_int, c_int,
+                                  c_int, c_int, c_void_p],
     "b200gemm_m_grouped_masked": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                                   c_int, c_int, c_void_p],
+    "b200gemm_k_grouped": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int64, c_int, c_int,
+                           c_int, c_int, c_void_p],
+    "b200gemm_fp8_m_grouped_rowcol": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64,
+                                      c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "b200gemm_fp8_k_grouped_rowcol": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64,
+                                      c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "b200gemm_fp8_m_grouped_block": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64,
+                                     c_int, c_int, c_int, c_int, c_void_p],
+    "b200gemm_fp8_m_grouped_masked_block": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                            c_int, c_int, c_int, c_int, c_void_p],
     "b200quant_act_1x128": [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_void_p],
     "b200quant_w_128x128": [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p],
     "b200quant_trans_expand_128x": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int,

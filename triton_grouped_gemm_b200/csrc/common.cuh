@@ -81,13 +81,15 @@ __device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, vola
 // Tiles are numbered in "padded tile space": group g owns ceil(size_g / kTileRows)
 // consecutive row tiles.  A walker is advanced monotonically to the row tile a role is about
 // to process; all lanes of a warp run it redundantly (uniform loads, no divergence).
-// kind 0: contiguous rows (A is compact, group g starts at sum of earlier sizes)
-// kind 1: masked layout (group g starts at g * stride, only sizes[g] rows are valid)
+// stride == 0 : compact rows (group g starts at the sum of the earlier sizes)
+// stride  > 0 : masked layout (group g starts at g * stride, only sizes[g] rows are valid)
+// stride == -1: padded rows (group g starts at the sum of the earlier sizes, each rounded up
+//               to a multiple of tile_rows; rows between size and the padded size are skipped)
 struct GroupWalker {
   const void* sizes;
   int sizes_i64;
   int num_groups;
-  int stride;        // masked: rows per group slot; contiguous: unused
+  int stride;        // see above
   int tile_rows;
   int g;             // current group
   int tile_begin;    // first padded tile of group g
@@ -121,7 +123,7 @@ struct GroupWalker {
   __device__ __forceinline__ bool seek(int t) {
     while (g < num_groups && t >= tile_begin + ntiles) {
       tile_begin += ntiles;
-      row_begin += size;
+      row_begin += stride < 0 ? static_cast<long long>(ntiles) * tile_rows : static_cast<long long>(size);
       ++g;
       if (g < num_groups) {
         size = load_size(g);

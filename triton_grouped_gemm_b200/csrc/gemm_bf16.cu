@@ -15,14 +15,9 @@
 
 #include "../../include/b200gemm.h"
 #include "common.cuh"
+#include "gemm_tile.cuh"
 
 namespace b200 {
-
-constexpr int kBlockM = 128;
-constexpr int kBlockK = 64;  // 64 16-bit elements = one 128-byte swizzle row
-constexpr int kUmmaK = 16;
-constexpr int kNumThreads = 192;
-constexpr int kSwizzle128 = 2;
 
 template <int kBlockN, int kStages>
 struct MGroupedSmem {
@@ -36,11 +31,20 @@ struct MGroupedSmem {
   static constexpr int kDynamicBytes = kTotal + 1024;  // slack for manual 1024-byte alignment
 };
 
-template <int kBlockN, int kStages, bool kBMnMajor>
+// kFp8 = false: 16-bit operands (`in_fmt`: 0 = f16, 1 = bf16), kBlockK = 64 elements.
+// kFp8 = true:  8-bit operands (`in_fmt` = a_fmt | b_fmt << 4, 0 = e4m3, 1 = e5m2), 128
+//               elements per k-block, and the epilogue applies a_scale[row] * b_scale[g*n+col]
+//               (per-row activation x per-expert-per-channel weight scales, the reference's
+//               gemm/FP8/m_grouped_gemm_channel_expert.py:119-136).  A k-block is 128 bytes
+//               per row either way, so the shared-memory ring is identical.
+template <int kBlockN, int kStages, bool kBMnMajor, bool kFp8>
 __global__ void __launch_bounds__(kNumThreads, 1)
 m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                  void* __restrict__ c_ptr, const void* __restrict__ sizes, int sizes_i64, int num_groups,
-                 int masked_stride, int n, int k, int is_fp16, unsigned* status) {
+                 int masked_stride, int n, int k, int in_fmt, int out_fp16, const float* __restrict__ a_scale,
+                 const float* __restrict__ b_scale, unsigned* status) {
+  static_assert(!(kFp8 && kBMnMajor), "fp8 operands are K-major only");
+  constexpr int kElemsPerKb = kFp8 ? 128 : 64;
   using L = MGroupedSmem<kBlockN, kStages>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -56,7 +60,7 @@ m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int n_tiles = (n + kBlockN - 1) / kBlockN;
-  const int num_kb = (k + kBlockK - 1) / kBlockK;
+  const int num_kb = (k + kElemsPerKb - 1) / kElemsPerKb;
   constexpr uint32_t kTmemCols = 2 * kBlockN;
 
   if (threadIdx.x == 0) {
@@ -106,9 +110,9 @@ m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           const uint32_t a_dst = smem_base + stage * L::kStageBytes;
           const uint32_t b_dst = a_dst + L::kABytes;
           mbar_arrive_expect_tx(full_bar(stage), L::kStageBytes);
-          tma_load_2d(a_dst, &tm_a, full_bar(stage), kb * kBlockK, row0);
+          tma_load_2d(a_dst, &tm_a, full_bar(stage), kb * kElemsPerKb, row0);
           if constexpr (!kBMnMajor) {
-            tma_load_3d(b_dst, &tm_b, full_bar(stage), kb * kBlockK, nt * kBlockN, g);
+            tma_load_3d(b_dst, &tm_b, full_bar(stage), kb * kElemsPerKb, nt * kBlockN, g);
           } else {
 #pragma unroll
             for (int j = 0; j < kBlockN / 64; ++j)
@@ -126,8 +130,9 @@ m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     // ------------------------------------------------------------ MMA issuer
     GroupWalker w;
     w.init(sizes, sizes_i64, num_groups, masked_stride, kBlockM);
-    const uint32_t fmt = is_fp16 ? 0u : 1u;
-    const uint32_t idesc = make_instr_desc(fmt, fmt, 0u, kBMnMajor ? 1u : 0u, kBlockM, kBlockN);
+    const uint32_t a_fmt = kFp8 ? static_cast<uint32_t>(in_fmt & 0xF) : static_cast<uint32_t>(in_fmt);
+    const uint32_t b_fmt = kFp8 ? static_cast<uint32_t>((in_fmt >> 4) & 0xF) : static_cast<uint32_t>(in_fmt);
+    const uint32_t idesc = make_instr_desc(a_fmt, b_fmt, 0u, kBMnMajor ? 1u : 0u, kBlockM, kBlockN);
     int stage = 0;
     uint32_t phase = 0;
     uint32_t tile_iter = 0;
@@ -155,7 +160,7 @@ m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             const uint64_t b_desc =
                 kBMnMajor ? make_smem_desc(b_addr + k16 * (kUmmaK * 128), kBlockK * 128, 1024, kSwizzle128)
                           : make_smem_desc(b_addr + k16 * (kUmmaK * 2), 16, 1024, kSwizzle128);
-            umma<1, false>(d_tmem, a_desc, b_desc, idesc, (kb | k16) != 0 ? 1u : 0u);
+            umma<1, kFp8>(d_tmem, a_desc, b_desc, idesc, (kb | k16) != 0 ? 1u : 0u);
           }
           umma_commit_1cta(empty_bar(stage));
         }
@@ -186,33 +191,12 @@ m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       tc_fence_after_sync();
       const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * kBlockN;
       uint16_t* c_row = static_cast<uint16_t*>(c_ptr) + row * static_cast<long long>(n);
-#pragma unroll 1
-      for (int c = 0; c < kBlockN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(t_addr + c * 32, r);
-        tmem_ld_wait();
-        const int col0 = nt * kBlockN + c * 32;
-        if (row_ok && col0 < n) {
-#pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            if (col0 + v * 8 < n) {
-              uint32_t p[4];
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const float lo = __uint_as_float(r[v * 8 + 2 * e]);
-                const float hi = __uint_as_float(r[v * 8 + 2 * e + 1]);
-                if (is_fp16) {
-                  __half2 h = __floats2half2_rn(lo, hi);
-                  p[e] = *reinterpret_cast<uint32_t*>(&h);
-                } else {
-                  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
-                  p[e] = *reinterpret_cast<uint32_t*>(&h);
-                }
-              }
-              *reinterpret_cast<uint4*>(c_row + col0 + v * 8) = make_uint4(p[0], p[1], p[2], p[3]);
-            }
-          }
-        }
+      if constexpr (kFp8) {
+        const float rs = row_ok ? __ldg(a_scale + row) : 0.f;
+        store_acc_row_16bit<kBlockN, true>(t_addr, c_row, row_ok, nt * kBlockN, n, out_fp16, rs,
+                                           b_scale + static_cast<long long>(w.g) * n);
+      } else {
+        store_acc_row_16bit<kBlockN, false>(t_addr, c_row, row_ok, nt * kBlockN, n, out_fp16);
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -236,16 +220,17 @@ m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 }
 
 // ------------------------------------------------------------------ host side
-template <int kBlockN, int kStages, bool kBMnMajor>
+template <int kBlockN, int kStages, bool kBMnMajor, bool kFp8>
 static int launch_m_grouped(const CUtensorMap& tm_a, const CUtensorMap& tm_b, void* c, const void* sizes,
-                            int sizes_is_i64, int num_groups, int masked_stride, int n, int k, int is_fp16, int grid,
+                            int sizes_is_i64, int num_groups, int masked_stride, int n, int k, int in_fmt,
+                            int out_fp16, const float* a_scale, const float* b_scale, int grid,
                             cudaStream_t stream) {
   using L = MGroupedSmem<kBlockN, kStages>;
-  auto kern = m_grouped_kernel<kBlockN, kStages, kBMnMajor>;
+  auto kern = m_grouped_kernel<kBlockN, kStages, kBMnMajor, kFp8>;
   B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes));
   unsigned* status = device_status_ptr();
   kern<<<grid, kNumThreads, L::kDynamicBytes, stream>>>(tm_a, tm_b, c, sizes, sizes_is_i64, num_groups, masked_stride,
-                                                        n, k, is_fp16, status);
+                                                        n, k, in_fmt, out_fp16, a_scale, b_scale, status);
   B200_CUDA(cudaGetLastError());
   return 0;
 }
@@ -302,20 +287,81 @@ static int m_grouped_common(const void* a, const void* b, void* c, const void* s
     if (rc) return rc;
   }
 
+  const int in_fmt = dtype == 1 ? 0 : 1;  // UMMA kind::f16 operand format: 0 = f16, 1 = bf16
 #define B200_LAUNCH(BN, ST)                                                                                          \
-  (trans_b ? launch_m_grouped<BN, ST, false>(tm_a, tm_b, c, sizes, sizes_is_i64, num_groups, masked_stride, n, k,     \
-                                             dtype, grid, stream)                                                    \
-           : launch_m_grouped<BN, ST, true>(tm_a, tm_b, c, sizes, sizes_is_i64, num_groups, masked_stride, n, k,      \
-                                            dtype, grid, stream))
+  (trans_b ? launch_m_grouped<BN, ST, false, false>(tm_a, tm_b, c, sizes, sizes_is_i64, num_groups, masked_stride, n, \
+                                                    k, in_fmt, dtype, nullptr, nullptr, grid, stream)                \
+           : launch_m_grouped<BN, ST, true, false>(tm_a, tm_b, c, sizes, sizes_is_i64, num_groups, masked_stride, n,  \
+                                                   k, in_fmt, dtype, nullptr, nullptr, grid, stream))
   if (block_n == 256) return B200_LAUNCH(256, 4);
   if (block_n == 128) return B200_LAUNCH(128, 6);
   return B200_LAUNCH(64, 8);
 #undef B200_LAUNCH
 }
 
+// FP8 operands with per-row activation scales and per-expert-per-channel weight scales.
+static int fp8_rowcol_m_grouped(const void* a, const float* a_scale, const void* b, const float* b_scale, void* c,
+                                const void* sizes, int sizes_is_i64, int num_groups, int64_t m_rows, int n, int k,
+                                int fmt_a, int fmt_b, int out_dtype, int num_sms, void* stream_v) {
+  const char* who = "b200gemm_fp8_m_grouped_rowcol";
+  B200_REQUIRE((fmt_a == 0 || fmt_a == 1) && (fmt_b == 0 || fmt_b == 1), "%s: fp8 format must be 0 (e4m3) or 1 (e5m2)",
+               who);
+  B200_REQUIRE(out_dtype == 0 || out_dtype == 1, "%s: out_dtype must be 0 (bf16) or 1 (fp16)", who);
+  B200_REQUIRE(num_groups >= 0 && m_rows >= 0 && n >= 0 && k >= 0, "%s: negative dimension", who);
+  if (num_groups == 0 || m_rows == 0 || n == 0) return 0;
+  B200_REQUIRE(k > 0, "%s: k must be positive", who);
+  B200_REQUIRE(a && b && c && sizes && a_scale && b_scale, "%s: null pointer", who);
+  B200_REQUIRE(k % 16 == 0, "%s: TMA required 16-byte alignment: k bytes (k=%d)", who, k);
+  B200_REQUIRE(n % 8 == 0, "%s: n must be a multiple of 8 (n=%d)", who, n);
+  B200_REQUIRE((reinterpret_cast<uintptr_t>(a) & 15) == 0 && (reinterpret_cast<uintptr_t>(b) & 15) == 0 &&
+                   (reinterpret_cast<uintptr_t>(c) & 15) == 0 && (reinterpret_cast<uintptr_t>(b_scale) & 15) == 0,
+               "%s: a, b, c and b_scale must be 16-byte aligned", who);
+  B200_REQUIRE(m_rows < (1ll << 31), "%s: m_rows must fit in int32", who);
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  const int sms = sm_count();
+  B200_REQUIRE(sms > 0, "%s: no CUDA device", who);
+  const int grid = (num_sms > 0 && num_sms < sms) ? num_sms : sms;
+  const long long m_tiles_est = (m_rows + kBlockM - 1) / kBlockM;
+  int block_n = 256;
+  if (n <= 64 || m_tiles_est * ((n + 127) / 128) < grid) block_n = 64;
+  else if (n <= 128 || m_tiles_est * ((n + 255) / 256) < grid) block_n = 128;
+  if (g_forced_block_n) block_n = g_forced_block_n;
+  CUtensorMap tm_a, tm_b;
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(m_rows)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(k)};
+    const uint32_t box[2] = {128, kBlockM};
+    int rc = encode_tmap(&tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, a, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B, "A");
+    if (rc) return rc;
+  }
+  {
+    const uint64_t dims[3] = {static_cast<uint64_t>(k), static_cast<uint64_t>(n), static_cast<uint64_t>(num_groups)};
+    const uint64_t strides[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(k) * n};
+    const uint32_t box[3] = {128, static_cast<uint32_t>(block_n), 1};
+    int rc = encode_tmap(&tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, b, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B,
+                         "B[G,N,K]");
+    if (rc) return rc;
+  }
+  const int in_fmt = fmt_a | (fmt_b << 4);
+#define B200_LAUNCH8(BN, ST)                                                                                        \
+  launch_m_grouped<BN, ST, false, true>(tm_a, tm_b, c, sizes, sizes_is_i64, num_groups, 0, n, k, in_fmt, out_dtype, \
+                                        a_scale, b_scale, grid, stream)
+  if (block_n == 256) return B200_LAUNCH8(256, 4);
+  if (block_n == 128) return B200_LAUNCH8(128, 6);
+  return B200_LAUNCH8(64, 8);
+#undef B200_LAUNCH8
+}
+
 }  // namespace b200
 
 extern "C" {
+
+int b200gemm_fp8_m_grouped_rowcol(const void* a, const float* a_scale, const void* b, const float* b_scale, void* c,
+                                  const void* sizes, int sizes_is_i64, int num_groups, int64_t m_rows, int n, int k,
+                                  int fmt_a, int fmt_b, int out_dtype, int num_sms, void* stream) {
+  return b200::fp8_rowcol_m_grouped(a, a_scale, b, b_scale, c, sizes, sizes_is_i64, num_groups, m_rows, n, k, fmt_a,
+                                    fmt_b, out_dtype, num_sms, stream);
+}
 
 int b200gemm_set_block_n(int block_n) {
   if (block_n != 0 && block_n != 64 && block_n != 128 && block_n != 256)
@@ -328,6 +374,13 @@ int b200gemm_m_grouped(const void* a, const void* b, void* c, const void* sizes,
                        int64_t m_rows, int n, int k, int trans_b, int dtype, int num_sms, void* stream) {
   return b200::m_grouped_common(a, b, c, sizes, sizes_is_i64, num_groups, m_rows, /*masked_stride=*/0, n, k, trans_b,
                                 dtype, num_sms, stream, "b200gemm_m_grouped");
+}
+
+int b200gemm_m_grouped_padded(const void* a, const void* b, void* c, const void* sizes, int sizes_is_i64,
+                              int num_groups, int64_t m_rows, int n, int k, int trans_b, int dtype, int num_sms,
+                              void* stream) {
+  return b200::m_grouped_common(a, b, c, sizes, sizes_is_i64, num_groups, m_rows, /*padded rows*/ -1, n, k, trans_b,
+                                dtype, num_sms, stream, "b200gemm_m_grouped_padded");
 }
 
 int b200gemm_m_grouped_masked(const void* lhs, const void* rhs, void* out, const void* masked_m, int sizes_is_i64,

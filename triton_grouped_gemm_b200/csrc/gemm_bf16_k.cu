@@ -1,0 +1,427 @@
+// BF16 / FP16 K-grouped GEMM (expert weight gradient) for sm_100a:
+//   C[g] = A[gs:ge, :]^T * B[gs:ge, :],  A [K_total, M_DIM], B [K_total, N_DIM], C [G, M_DIM, N_DIM]
+// The grouping runs along the contraction (token) axis, so both operands are MN-major in
+// shared memory: a k-block is 64 token rows, each row 128 bytes of one 64-column chunk
+// (128-byte swizzle), and the UMMA descriptors carry the "MN-major" bit for A and B.
+//
+// Same warp roles as the M-grouped kernel (TMA producer / MMA issuer / 4 epilogue warps,
+// double-buffered TMEM accumulator).  Tiles are numbered g * tiles_per_group + local, and the
+// token range of a group comes from a running prefix over the device-resident sizes.
+// The last k-block of a group may hold rows of the next group (TMA cannot clip in the
+// middle of a tensor): the MMA warp zeroes those rows in shared memory up to the next
+// multiple of 16 and issues only as many K=16 steps as the group has rows for.
+// An empty group writes zeros (the reference's TMA kernel stores its zero accumulator,
+// gemm/BF16/k_grouped_gemm_TMA.py:141,167-170).
+#include "../../include/b200gemm.h"
+#include "common.cuh"
+#include "gemm_tile.cuh"
+
+namespace b200 {
+
+template <int kBlockN, int kStages>
+struct KGroupedSmem {
+  static constexpr int kABytes = kBlockM * kBlockK * 2;  // 2 chunks of [64 tokens][64 m]
+  static constexpr int kBBytes = kBlockN * kBlockK * 2;  // kBlockN/64 chunks of [64 tokens][64 n]
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kBarOffset = kStages * kStageBytes;
+  static constexpr int kNumBars = 2 * kStages + 4;
+  static constexpr int kTotal = kBarOffset + kNumBars * 8 + 16;
+  static constexpr int kDynamicBytes = kTotal + 1024;
+};
+
+// Token range of a group: either explicit int32 [start, end) arrays, or a running exclusive
+// prefix over the group sizes (`g` only moves forward).
+struct TokenRange {
+  const void* sizes;
+  const int* starts;
+  const int* ends;
+  int sizes_i64;
+  int cur;
+  long long start;
+  __device__ __forceinline__ long long size_of(int i) const {
+    long long v = sizes_i64 ? static_cast<const long long*>(sizes)[i]
+                            : static_cast<long long>(static_cast<const int*>(sizes)[i]);
+    return v < 0 ? 0 : v;
+  }
+  __device__ __forceinline__ void init(const void* s, int i64, const int* gs, const int* ge) {
+    sizes = s;
+    sizes_i64 = i64;
+    starts = gs;
+    ends = ge;
+    cur = 0;
+    start = 0;
+  }
+  // returns the number of tokens of group g; start = first token row of g
+  __device__ __forceinline__ long long seek(int g) {
+    if (starts) {
+      start = starts[g];
+      const long long t = static_cast<long long>(ends[g]) - start;
+      return t < 0 ? 0 : t;
+    }
+    while (cur < g) {
+      start += size_of(cur);
+      ++cur;
+    }
+    return size_of(g);
+  }
+};
+
+// kFp8 = false: 16-bit A [K_total, M_DIM], B [K_total, N_DIM] (MN-major operands, 64 tokens
+//               per k-block, `in_fmt`: 0 = f16, 1 = bf16).
+// kFp8 = true:  8-bit X [M, K_total], Y [N, K_total] (K-major operands, 128 tokens per
+//               k-block, `in_fmt` = x_fmt | y_fmt << 4 with 0 = e4m3, 1 = e5m2); the epilogue
+//               applies x_scale[g*M+m] * y_scale[g*N+n]; token counts are multiples of 128
+//               with zero padding (gemm/FP8/k_grouped_gemm_channel_expert.py:64-140).
+template <int kBlockN, int kStages, bool kFp8>
+__global__ void __launch_bounds__(kNumThreads, 1)
+k_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                 void* __restrict__ c_ptr, const void* __restrict__ sizes, int sizes_i64,
+                 const int* __restrict__ group_start, const int* __restrict__ group_end, int num_groups, int m_dim,
+                 int n_dim, long long k_total, int in_fmt, int out_fp16, const float* __restrict__ a_scale,
+                 const float* __restrict__ b_scale, unsigned* status) {
+  constexpr int kTokensPerKb = kFp8 ? 128 : kBlockK;
+  using L = KGroupedSmem<kBlockN, kStages>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bar_base = smem_base + L::kBarOffset;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
+  auto tmem_full_bar = [&](int a) { return bar_base + 8u * (2 * kStages + a); };
+  auto tmem_empty_bar = [&](int a) { return bar_base + 8u * (2 * kStages + 2 + a); };
+  volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(smem + L::kBarOffset + L::kNumBars * 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kBarOffset + L::kNumBars * 8 + 4);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int m_tiles = (m_dim + kBlockM - 1) / kBlockM;
+  const int n_tiles = (n_dim + kBlockN - 1) / kBlockN;
+  const int tiles_per_group = m_tiles * n_tiles;
+  const long long num_tiles = static_cast<long long>(tiles_per_group) * num_groups;
+  constexpr uint32_t kTmemCols = 2 * kBlockN;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tmem_full_bar(a), 1);
+      mbar_init(tmem_empty_bar(a), 4);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0 && lane == 0) {
+    prefetch_tmap(&tm_a);
+    prefetch_tmap(&tm_b);
+  }
+  if (warp == 1) {
+    tmem_alloc<1>(smem_u32(const_cast<uint32_t*>(tmem_holder)), kTmemCols);
+    tmem_relinquish<1>();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_holder;
+
+  // tile -> (group, m tile, n tile): n fastest, so CTAs running side by side share A chunks
+  auto decode = [&](long long tile, int& g, int& mt, int& nt) {
+    g = static_cast<int>(tile / tiles_per_group);
+    const int local = static_cast<int>(tile - static_cast<long long>(g) * tiles_per_group);
+    mt = local / n_tiles;
+    nt = local - mt * n_tiles;
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    TokenRange tr;
+    tr.init(sizes, sizes_i64, group_start, group_end);
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (long long tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+      int g, mt, nt;
+      decode(tile, g, mt, nt);
+      const long long tokens = tr.seek(g);
+      const int num_kb = static_cast<int>((tokens + kTokensPerKb - 1) / kTokensPerKb);
+      for (int kb = 0; kb < num_kb; ++kb) {
+        if (!wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag, status, kDevTimeoutProducer)) {
+          ok = false;
+          break;
+        }
+        if (lane == 0) {
+          const uint32_t a_dst = smem_base + stage * L::kStageBytes;
+          const uint32_t b_dst = a_dst + L::kABytes;
+          const int krow = static_cast<int>(tr.start + static_cast<long long>(kb) * kTokensPerKb);
+          mbar_arrive_expect_tx(full_bar(stage), L::kStageBytes);
+          if constexpr (kFp8) {
+            tma_load_2d(a_dst, &tm_a, full_bar(stage), krow, mt * kBlockM);
+            tma_load_2d(b_dst, &tm_b, full_bar(stage), krow, nt * kBlockN);
+          } else {
+#pragma unroll
+            for (int j = 0; j < kBlockM / 64; ++j)
+              tma_load_2d(a_dst + j * (kBlockK * 128), &tm_a, full_bar(stage), mt * kBlockM + j * 64, krow);
+#pragma unroll
+            for (int j = 0; j < kBlockN / 64; ++j)
+              tma_load_2d(b_dst + j * (kBlockK * 128), &tm_b, full_bar(stage), nt * kBlockN + j * 64, krow);
+          }
+        }
+        __syncwarp();
+        if (++stage == kStages) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    TokenRange tr;
+    tr.init(sizes, sizes_i64, group_start, group_end);
+    const uint32_t a_fmt = kFp8 ? static_cast<uint32_t>(in_fmt & 0xF) : static_cast<uint32_t>(in_fmt);
+    const uint32_t b_fmt = kFp8 ? static_cast<uint32_t>((in_fmt >> 4) & 0xF) : static_cast<uint32_t>(in_fmt);
+    const uint32_t mn_major = kFp8 ? 0u : 1u;
+    const uint32_t idesc = make_instr_desc(a_fmt, b_fmt, mn_major, mn_major, kBlockM, kBlockN);
+    int stage = 0;
+    uint32_t phase = 0;
+    uint32_t tile_iter = 0;  // counts non-empty tiles only (same rule in the epilogue)
+    bool ok = true;
+    for (long long tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+      int g, mt, nt;
+      decode(tile, g, mt, nt);
+      const long long tokens = tr.seek(g);
+      if (tokens == 0) continue;
+      const int num_kb = static_cast<int>((tokens + kTokensPerKb - 1) / kTokensPerKb);
+      const uint32_t acc = tile_iter & 1u;
+      const uint32_t acc_phase = (tile_iter >> 1) & 1u;
+      ++tile_iter;
+      if (!wait_bounded(tmem_empty_bar(acc), acc_phase ^ 1u, abort_flag, status, kDevTimeoutMma)) break;
+      tc_fence_after_sync();
+      const uint32_t d_tmem = tmem_base + acc * kBlockN;
+      for (int kb = 0; kb < num_kb; ++kb) {
+        if (!wait_bounded(full_bar(stage), phase, abort_flag, status, kDevTimeoutMma)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t a_addr = smem_base + stage * L::kStageBytes;
+        int k16_steps = kBlockK / kUmmaK;
+        if (!kFp8 && kb == num_kb - 1) {
+          const int valid = static_cast<int>(tokens - static_cast<long long>(kb) * kBlockK);  // 1..64
+          k16_steps = (valid + kUmmaK - 1) / kUmmaK;
+          const int zero_rows = k16_steps * kUmmaK - valid;  // rows [valid, valid + zero_rows)
+          if (zero_rows > 0) {
+            // every chunk (A: 2, B: kBlockN/64) is [64 token rows][128 bytes]; a token row keeps
+            // its own 128 bytes under the swizzle, so clearing whole rows is layout-agnostic
+            constexpr int kChunks = (kBlockM + kBlockN) / 64;
+            const int vec_per_chunk = zero_rows * 8;  // 16-byte vectors
+            uint8_t* stage_ptr = smem + stage * L::kStageBytes;
+            for (int i = lane; i < kChunks * vec_per_chunk; i += 32) {
+              const int ch = i / vec_per_chunk;
+              const int v = i - ch * vec_per_chunk;
+              *reinterpret_cast<uint4*>(stage_ptr + ch * (kBlockK * 128) + valid * 128 + v * 16) =
+                  make_uint4(0, 0, 0, 0);
+            }
+            fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core
+          }
+          __syncwarp();
+        }
+        if (lane == 0) {
+          const uint32_t b_addr = a_addr + L::kABytes;
+          for (int k16 = 0; k16 < k16_steps; ++k16) {
+            // MN-major: a K step is 16 token rows of 128 bytes; K-major (fp8): 32 bytes in a row
+            const uint32_t step = kFp8 ? 32u : kUmmaK * 128u;
+            const uint32_t lbo = kFp8 ? 16u : kBlockK * 128u;
+            const uint64_t a_desc = make_smem_desc(a_addr + k16 * step, lbo, 1024, kSwizzle128);
+            const uint64_t b_desc = make_smem_desc(b_addr + k16 * step, lbo, 1024, kSwizzle128);
+            umma<1, kFp8>(d_tmem, a_desc, b_desc, idesc, (kb | k16) != 0 ? 1u : 0u);
+          }
+          umma_commit_1cta(empty_bar(stage));
+        }
+        __syncwarp();
+        if (++stage == kStages) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+      if (ok && lane == 0) umma_commit_1cta(tmem_full_bar(acc));
+      __syncwarp();
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    TokenRange tr;
+    tr.init(sizes, sizes_i64, group_start, group_end);
+    const int quarter = warp & 3;
+    uint32_t tile_iter = 0;
+    for (long long tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+      int g, mt, nt;
+      decode(tile, g, mt, nt);
+      const long long tokens = tr.seek(g);
+      const int row = mt * kBlockM + quarter * 32 + lane;
+      const bool row_ok = row < m_dim;
+      uint16_t* c_row = static_cast<uint16_t*>(c_ptr) +
+                        (static_cast<long long>(g) * m_dim + row) * static_cast<long long>(n_dim);
+      if (tokens == 0) {
+        store_zero_row_16bit<kBlockN>(c_row, row_ok, nt * kBlockN, n_dim);
+        continue;
+      }
+      const uint32_t acc = tile_iter & 1u;
+      const uint32_t acc_phase = (tile_iter >> 1) & 1u;
+      ++tile_iter;
+      if (!wait_bounded(tmem_full_bar(acc), acc_phase, abort_flag, status, kDevTimeoutEpilogue)) break;
+      tc_fence_after_sync();
+      const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * kBlockN;
+      if constexpr (kFp8) {
+        const float rs = row_ok ? __ldg(a_scale + static_cast<long long>(g) * m_dim + row) : 0.f;
+        store_acc_row_16bit<kBlockN, true>(t_addr, c_row, row_ok, nt * kBlockN, n_dim, out_fp16, rs,
+                                           b_scale + static_cast<long long>(g) * n_dim);
+      } else {
+        store_acc_row_16bit<kBlockN, false>(t_addr, c_row, row_ok, nt * kBlockN, n_dim, out_fp16);
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tmem_empty_bar(acc));
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    for (int i = 0; i < 64; ++i) __nanosleep(4000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc<1>(tmem_base, kTmemCols);
+  }
+}
+
+template <int kBlockN, int kStages, bool kFp8>
+static int launch_k_grouped(const CUtensorMap& tm_a, const CUtensorMap& tm_b, void* c, const void* sizes,
+                            int sizes_is_i64, const int* gs, const int* ge, int num_groups, int m_dim, int n_dim,
+                            long long k_total, int in_fmt, int out_fp16, const float* a_scale, const float* b_scale,
+                            int grid, cudaStream_t stream) {
+  using L = KGroupedSmem<kBlockN, kStages>;
+  auto kern = k_grouped_kernel<kBlockN, kStages, kFp8>;
+  B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes));
+  kern<<<grid, kNumThreads, L::kDynamicBytes, stream>>>(tm_a, tm_b, c, sizes, sizes_is_i64, gs, ge, num_groups, m_dim,
+                                                        n_dim, k_total, in_fmt, out_fp16, a_scale, b_scale,
+                                                        device_status_ptr());
+  B200_CUDA(cudaGetLastError());
+  return 0;
+}
+
+// tile width: 256 output columns unless that leaves SMs without a tile
+static int pick_block_n(int num_groups, int m_dim, int n_dim, int grid) {
+  const long long m_tiles = static_cast<long long>(num_groups) * ((m_dim + 127) / 128);
+  if (n_dim <= 64 || m_tiles * ((n_dim + 127) / 128) < grid) return 64;
+  if (n_dim <= 128 || m_tiles * ((n_dim + 255) / 256) < grid) return 128;
+  return 256;
+}
+
+}  // namespace b200
+
+extern "C" int b200gemm_k_grouped(const void* a, const void* b, void* c, const void* sizes, int sizes_is_i64,
+                                  const int* group_start, const int* group_end, int num_groups, int64_t k_total, int m_dim, int n_dim, int dtype, int num_sms,
+                                  void* stream_v) {
+  using namespace b200;
+  const char* who = "b200gemm_k_grouped";
+  B200_REQUIRE(dtype == 0 || dtype == 1, "%s: dtype must be 0 (bf16) or 1 (fp16), got %d", who, dtype);
+  B200_REQUIRE(num_groups >= 0 && k_total >= 0 && m_dim >= 0 && n_dim >= 0, "%s: negative dimension", who);
+  if (num_groups == 0 || m_dim == 0 || n_dim == 0) return 0;
+  B200_REQUIRE(c && (sizes || (group_start && group_end)), "%s: null pointer", who);
+  B200_REQUIRE((group_start == nullptr) == (group_end == nullptr), "%s: pass both group_start and group_end or neither",
+               who);
+  B200_REQUIRE(m_dim % 8 == 0, "%s: A row stride must be 16-byte aligned (M_DIM=%d)", who, m_dim);
+  B200_REQUIRE(n_dim % 8 == 0, "%s: B row stride must be 16-byte aligned (N_DIM=%d)", who, n_dim);
+  B200_REQUIRE(k_total < (1ll << 31), "%s: K_TOTAL must fit in int32", who);
+  B200_REQUIRE((reinterpret_cast<uintptr_t>(a) & 15) == 0 && (reinterpret_cast<uintptr_t>(b) & 15) == 0 &&
+                   (reinterpret_cast<uintptr_t>(c) & 15) == 0,
+               "%s: base pointers must be 16-byte aligned", who);
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  const int sms = sm_count();
+  B200_REQUIRE(sms > 0, "%s: no CUDA device", who);
+  const int grid = (num_sms > 0 && num_sms < sms) ? num_sms : sms;
+
+  // With no tokens at all there is nothing to load: tensor maps need a non-empty tensor, so
+  // point them at the (never dereferenced) output instead.
+  const void* a_base = (k_total > 0 && a) ? a : c;
+  const void* b_base = (k_total > 0 && b) ? b : c;
+  B200_REQUIRE(k_total == 0 || (a && b), "%s: null pointer", who);
+  const uint64_t rows = k_total > 0 ? static_cast<uint64_t>(k_total) : 1;
+  const CUtensorMapDataType dt = dtype == 1 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  CUtensorMap tm_a, tm_b;
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(m_dim), rows};
+    const uint64_t strides[1] = {static_cast<uint64_t>(m_dim) * 2};
+    const uint32_t box[2] = {64, kBlockK};
+    int rc = encode_tmap(&tm_a, dt, 2, a_base, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B, "A[K_TOTAL,M_DIM]");
+    if (rc) return rc;
+  }
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(n_dim), rows};
+    const uint64_t strides[1] = {static_cast<uint64_t>(n_dim) * 2};
+    const uint32_t box[2] = {64, kBlockK};
+    int rc = encode_tmap(&tm_b, dt, 2, b_base, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B, "B[K_TOTAL,N_DIM]");
+    if (rc) return rc;
+  }
+  const int in_fmt = dtype == 1 ? 0 : 1;  // UMMA kind::f16 operand format: 0 = f16, 1 = bf16
+  const int bn = pick_block_n(num_groups, m_dim, n_dim, grid);
+#define B200_LAUNCH_K(BN, ST)                                                                                     \
+  launch_k_grouped<BN, ST, false>(tm_a, tm_b, c, sizes, sizes_is_i64, group_start, group_end, num_groups, m_dim,  \
+                                  n_dim, k_total, in_fmt, dtype, nullptr, nullptr, grid, stream)
+  if (bn == 64) return B200_LAUNCH_K(64, 8);
+  if (bn == 128) return B200_LAUNCH_K(128, 6);
+  return B200_LAUNCH_K(256, 4);
+#undef B200_LAUNCH_K
+}
+
+extern "C" int b200gemm_fp8_k_grouped_rowcol(const void* x, const float* x_scale, const void* y, const float* y_scale,
+                                             void* out, const void* tokens_per_expert, int sizes_is_i64,
+                                             int num_groups, int64_t k_total, int m_dim, int n_dim, int fmt_x,
+                                             int fmt_y, int num_sms, void* stream_v) {
+  using namespace b200;
+  const char* who = "b200gemm_fp8_k_grouped_rowcol";
+  B200_REQUIRE((fmt_x == 0 || fmt_x == 1) && (fmt_y == 0 || fmt_y == 1), "%s: fp8 format must be 0 (e4m3) or 1 (e5m2)",
+               who);
+  B200_REQUIRE(num_groups >= 0 && k_total >= 0 && m_dim >= 0 && n_dim >= 0, "%s: negative dimension", who);
+  if (num_groups == 0 || m_dim == 0 || n_dim == 0) return 0;
+  B200_REQUIRE(x && y && out && tokens_per_expert && x_scale && y_scale, "%s: null pointer", who);
+  B200_REQUIRE(k_total > 0 && k_total % 16 == 0, "%s: K_total (%lld) must be a positive multiple of 16", who,
+               (long long)k_total);
+  B200_REQUIRE(n_dim % 8 == 0, "%s: N must be a multiple of 8 (N=%d)", who, n_dim);
+  B200_REQUIRE(k_total < (1ll << 31), "%s: K_total must fit in int32", who);
+  B200_REQUIRE((reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(y) & 15) == 0 &&
+                   (reinterpret_cast<uintptr_t>(out) & 15) == 0 && (reinterpret_cast<uintptr_t>(y_scale) & 15) == 0,
+               "%s: x, y, out and y_scale must be 16-byte aligned", who);
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  const int sms = sm_count();
+  B200_REQUIRE(sms > 0, "%s: no CUDA device", who);
+  const int grid = (num_sms > 0 && num_sms < sms) ? num_sms : sms;
+  const int bn = pick_block_n(num_groups, m_dim, n_dim, grid);
+  CUtensorMap tm_x, tm_y;
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(k_total), static_cast<uint64_t>(m_dim)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(k_total)};
+    const uint32_t box[2] = {128, kBlockM};
+    int rc = encode_tmap(&tm_x, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, x, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B,
+                         "X[M,K_TOTAL]");
+    if (rc) return rc;
+  }
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(k_total), static_cast<uint64_t>(n_dim)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(k_total)};
+    const uint32_t box[2] = {128, static_cast<uint32_t>(bn)};
+    int rc = encode_tmap(&tm_y, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, y, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B,
+                         "Y[N,K_TOTAL]");
+    if (rc) return rc;
+  }
+  const int in_fmt = fmt_x | (fmt_y << 4);
+#define B200_LAUNCH_K8(BN, ST)                                                                                  \
+  launch_k_grouped<BN, ST, true>(tm_x, tm_y, out, tokens_per_expert, sizes_is_i64, nullptr, nullptr, num_groups, \
+                                 m_dim, n_dim, k_total, in_fmt, /*out bf16*/ 0, x_scale, y_scale, grid, stream)
+  if (bn == 64) return B200_LAUNCH_K8(64, 8);
+  if (bn == 128) return B200_LAUNCH_K8(128, 6);
+  return B200_LAUNCH_K8(256, 4);
+#undef B200_LAUNCH_K8
+}

@@ -234,6 +234,18 @@ __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)
 
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// ------------------------------------------------------------------ register re-balancing
+// Executed by all warps of one warpgroup (4 consecutive warps): shrink / grow the per-thread
+// register budget so that data-movement warps hand registers to the math warps.
+template <int kRegs>
+__device__ __forceinline__ void warpgroup_reg_dec() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegs));
+}
+template <int kRegs>
+__device__ __forceinline__ void warpgroup_reg_inc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegs));
+}
+
 // ------------------------------------------------------------------ cluster helpers
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;

@@ -1,0 +1,76 @@
+"""Block-scaled FP8 (e4m3) M-grouped GEMMs: 1x128 activation scales x 128x128 weight scales.
+
+The reference reaches this operation only through an external package
+(gemm/deep_gemm_ops.py:60-100); here it is a hand-written sm_100a kernel.  Inputs are what
+``per_token_cast_to_fp8`` / ``per_block_cast_to_fp8`` produce:
+
+    a = (a_fp8 [M, K], a_scale [M, ceil(K/128)] fp32)
+    b = (b_fp8 [G, N, K], b_scale [G, ceil(N/128), ceil(K/128)] fp32)
+    C[m, n] = sum_kb (sum_{k in kb} a_fp8[m,k] * b_fp8[g,n,k]) * a_scale[m,kb] * b_scale[g,n//128,kb]  -> bf16
+"""
+
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+from torch import Tensor
+
+from ... import _lib
+
+Pair = Tuple[Tensor, Tensor]
+
+
+def _check_pairs(a: Pair, b: Pair):
+    a8, a_s = a
+    b8, b_s = b
+    assert a8.dim() == 2 and b8.dim() == 3, "expected a[0] shape [M, K] and b[0] shape [num_groups, N, K]"
+    m, k = a8.shape
+    g, n, bk = b8.shape
+    assert bk == k, f"K mismatch: a has K={k}, b has K={bk}"
+    assert a8.dtype == torch.float8_e4m3fn and b8.dtype == torch.float8_e4m3fn, "operands must be float8_e4m3fn"
+    kb, nb = (k + 127) // 128, (n + 127) // 128
+    assert a_s.dtype == torch.float32 and tuple(a_s.shape) == (m, kb), f"a_scale must be fp32 [{m}, {kb}]"
+    assert b_s.dtype == torch.float32 and tuple(b_s.shape) == (g, nb, kb), f"b_scale must be fp32 [{g}, {nb}, {kb}]"
+    assert a8.is_contiguous() and b8.is_contiguous() and a_s.is_contiguous() and b_s.is_contiguous()
+    assert k % 16 == 0, "TMA required 16-byte alignment"
+    assert n % 8 == 0, "N must be a multiple of 8"
+    _lib.require_cuda(a8, a_s, b8, b_s)
+    return a8, a_s, b8, b_s, m, n, k, g
+
+
+def m_grouped_fp8_block_scaled(a: Pair, b: Pair, size_per_group: Tensor, *, out: Optional[Tensor] = None,
+                               rows_padded: bool = False) -> Tensor:
+    """``rows_padded=False``: rows of ``a`` are compact (sum(size_per_group) rows used).
+    ``rows_padded=True``: each group's rows are padded to a multiple of 128 (DeepGEMM's
+    contiguous layout); padding rows of ``out`` are not written."""
+    a8, a_s, b8, b_s, m, n, k, g = _check_pairs(a, b)
+    assert size_per_group.numel() == g
+    _lib.require_cuda(size_per_group)
+    if out is None:
+        out = torch.empty((m, n), device=a8.device, dtype=torch.bfloat16)
+    assert out.shape == (m, n) and out.dtype == torch.bfloat16 and out.is_contiguous()
+    sizes, is64 = _lib.sizes_arg(size_per_group)
+    with torch.cuda.device(a8.device):
+        rc = _lib.load().b200gemm_fp8_m_grouped_block(
+            _lib.ptr(a8), _lib.ptr(a_s), _lib.ptr(b8), _lib.ptr(b_s), _lib.ptr(out), _lib.ptr(sizes), is64, g, m, n, k,
+            1 if rows_padded else 0, -1, _lib.stream_ptr(a8.device))
+    _lib.check(rc, "b200gemm_fp8_m_grouped_block")
+    return out
+
+
+def m_grouped_fp8_block_scaled_masked(a: Pair, b: Pair, out: Tensor, masked_m: Tensor, expected_m: int) -> None:
+    """Masked (decode) layout: ``a[0]`` is [G*expected_m, K]; rows [g*expected_m,
+    g*expected_m + masked_m[g]) of ``out`` are written, the rest is left untouched."""
+    a8, a_s, b8, b_s, m, n, k, g = _check_pairs(a, b)
+    assert m == g * expected_m, "a must hold expected_m rows per group"
+    assert out.shape == (m, n) and out.dtype == torch.bfloat16 and out.is_contiguous()
+    assert masked_m.numel() == g
+    _lib.require_cuda(out, masked_m)
+    sizes, is64 = _lib.sizes_arg(masked_m)
+    with torch.cuda.device(a8.device):
+        rc = _lib.load().b200gemm_fp8_m_grouped_masked_block(
+            _lib.ptr(a8), _lib.ptr(a_s), _lib.ptr(b8), _lib.ptr(b_s), _lib.ptr(out), _lib.ptr(sizes), is64, g,
+            int(expected_m), n, k, -1, _lib.stream_ptr(a8.device))
+    _lib.check(rc, "b200gemm_fp8_m_grouped_masked_block")
+    return None
