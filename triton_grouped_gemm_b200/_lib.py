@@ -13,8 +13,11 @@ from pathlib import Path
 
 import torch
 
+import os
+
 PKG = Path(__file__).resolve().parent
-LIB_PATH = PKG / "libb200gemm.so"
+# B200GEMM_LIBRARY overrides the in-tree library (e.g. a build with different tuning).
+LIB_PATH = Path(os.environ["B200GEMM_LIBRARY"]) if os.environ.get("B200GEMM_LIBRARY") else PKG / "libb200gemm.so"
 
 _lock = threading.Lock()
 _lib = None

@@ -24,7 +24,8 @@ struct MGroupedSmem {
   static constexpr int kABytes = kBlockM * kBlockK * 2;
   static constexpr int kBBytes = kBlockN * kBlockK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kBarOffset = kStages * kStageBytes;
+  static constexpr int kEpiOffset = kStages * kStageBytes;  // 4 warps x 2 x 4 KB store staging
+  static constexpr int kBarOffset = kEpiOffset + 4 * kEpiStageBytesPerWarp;
   // full[kStages], empty[kStages], tmem_full[2], tmem_empty[2], then tmem ptr + abort flag
   static constexpr int kNumBars = 2 * kStages + 4;
   static constexpr int kTotal = kBarOffset + kNumBars * 8 + 16;
@@ -40,7 +41,7 @@ struct MGroupedSmem {
 template <int kBlockN, int kStages, bool kBMnMajor, bool kFp8>
 __global__ void __launch_bounds__(kNumThreads, 1)
 m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
-                 void* __restrict__ c_ptr, const void* __restrict__ sizes, int sizes_i64, int num_groups,
+                 const __grid_constant__ CUtensorMap tm_c, void* __restrict__ c_ptr, const void* __restrict__ sizes, int sizes_i64, int num_groups,
                  int masked_stride, int n, int k, int in_fmt, int out_fp16, const float* __restrict__ a_scale,
                  const float* __restrict__ b_scale, unsigned* status) {
   static_assert(!(kFp8 && kBMnMajor), "fp8 operands are K-major only");
@@ -78,6 +79,7 @@ m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   if (warp == 0 && lane == 0) {
     prefetch_tmap(&tm_a);
     prefetch_tmap(&tm_b);
+    prefetch_tmap(&tm_c);
   }
   if (warp == 1) {
     tmem_alloc<1>(smem_u32(const_cast<uint32_t*>(tmem_holder)), kTmemCols);
@@ -178,6 +180,8 @@ m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     GroupWalker w;
     w.init(sizes, sizes_i64, num_groups, masked_stride, kBlockM);
     const int quarter = warp & 3;  // TMEM lane quarter this warp may read
+    uint8_t* epi_stage = smem + L::kEpiOffset + quarter * kEpiStageBytesPerWarp;
+    int epi_sel = 0;
     uint32_t tile_iter = 0;
     for (int tile = blockIdx.x;; tile += gridDim.x, ++tile_iter) {
       const int mt = tile / n_tiles;
@@ -191,17 +195,26 @@ m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       tc_fence_after_sync();
       const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * kBlockN;
       uint16_t* c_row = static_cast<uint16_t*>(c_ptr) + row * static_cast<long long>(n);
+      // warps whose 32 rows all belong to the group take the staged TMA-store path; a warp
+      // that straddles the end of its group falls back to masked per-thread stores
+      const long long row_w0 = w.tile_row0(mt) + quarter * 32;
+      const bool warp_full = row_w0 + 32 <= w.group_row_end();
+      float rs = 1.0f;
+      const float* cs = nullptr;
       if constexpr (kFp8) {
-        const float rs = row_ok ? __ldg(a_scale + row) : 0.f;
-        store_acc_row_16bit<kBlockN, true>(t_addr, c_row, row_ok, nt * kBlockN, n, out_fp16, rs,
-                                           b_scale + static_cast<long long>(w.g) * n);
-      } else {
-        store_acc_row_16bit<kBlockN, false>(t_addr, c_row, row_ok, nt * kBlockN, n, out_fp16);
+        rs = row_ok ? __ldg(a_scale + row) : 0.f;
+        cs = b_scale + static_cast<long long>(w.g) * n;
       }
+      if (warp_full)
+        store_acc_warp_tma<kBlockN, kFp8>(t_addr, &tm_c, epi_stage, epi_sel, static_cast<int>(row_w0), -1,
+                                          nt * kBlockN, n, out_fp16, lane, rs, cs);
+      else
+        store_acc_row_16bit<kBlockN, kFp8>(t_addr, c_row, row_ok, nt * kBlockN, n, out_fp16, rs, cs);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(tmem_empty_bar(acc));
     }
+    if (lane == 0) tma_store_wait_all<0>();  // staged stores have left shared memory and landed
   }
 
   // ---------------------------------------------------------------- teardown
@@ -221,7 +234,8 @@ m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 
 // ------------------------------------------------------------------ host side
 template <int kBlockN, int kStages, bool kBMnMajor, bool kFp8>
-static int launch_m_grouped(const CUtensorMap& tm_a, const CUtensorMap& tm_b, void* c, const void* sizes,
+static int launch_m_grouped(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const CUtensorMap& tm_c, void* c,
+                            const void* sizes,
                             int sizes_is_i64, int num_groups, int masked_stride, int n, int k, int in_fmt,
                             int out_fp16, const float* a_scale, const float* b_scale, int grid,
                             cudaStream_t stream) {
@@ -229,7 +243,7 @@ static int launch_m_grouped(const CUtensorMap& tm_a, const CUtensorMap& tm_b, vo
   auto kern = m_grouped_kernel<kBlockN, kStages, kBMnMajor, kFp8>;
   B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes));
   unsigned* status = device_status_ptr();
-  kern<<<grid, kNumThreads, L::kDynamicBytes, stream>>>(tm_a, tm_b, c, sizes, sizes_is_i64, num_groups, masked_stride,
+  kern<<<grid, kNumThreads, L::kDynamicBytes, stream>>>(tm_a, tm_b, tm_c, c, sizes, sizes_is_i64, num_groups, masked_stride,
                                                         n, k, in_fmt, out_fp16, a_scale, b_scale, status);
   B200_CUDA(cudaGetLastError());
   return 0;
@@ -287,11 +301,19 @@ static int m_grouped_common(const void* a, const void* b, void* c, const void* s
     if (rc) return rc;
   }
 
+  CUtensorMap tm_c;
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(n), static_cast<uint64_t>(m_rows)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(n) * 2};
+    const uint32_t box[2] = {64, 32};
+    int rc = encode_tmap(&tm_c, dt, 2, c, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B, "C");
+    if (rc) return rc;
+  }
   const int in_fmt = dtype == 1 ? 0 : 1;  // UMMA kind::f16 operand format: 0 = f16, 1 = bf16
 #define B200_LAUNCH(BN, ST)                                                                                          \
-  (trans_b ? launch_m_grouped<BN, ST, false, false>(tm_a, tm_b, c, sizes, sizes_is_i64, num_groups, masked_stride, n, \
+  (trans_b ? launch_m_grouped<BN, ST, false, false>(tm_a, tm_b, tm_c, c, sizes, sizes_is_i64, num_groups, masked_stride, n, \
                                                     k, in_fmt, dtype, nullptr, nullptr, grid, stream)                \
-           : launch_m_grouped<BN, ST, true, false>(tm_a, tm_b, c, sizes, sizes_is_i64, num_groups, masked_stride, n,  \
+           : launch_m_grouped<BN, ST, true, false>(tm_a, tm_b, tm_c, c, sizes, sizes_is_i64, num_groups, masked_stride, n,  \
                                                    k, in_fmt, dtype, nullptr, nullptr, grid, stream))
   if (block_n == 256) return B200_LAUNCH(256, 4);
   if (block_n == 128) return B200_LAUNCH(128, 6);
@@ -342,9 +364,17 @@ static int fp8_rowcol_m_grouped(const void* a, const float* a_scale, const void*
                          "B[G,N,K]");
     if (rc) return rc;
   }
+  CUtensorMap tm_c;
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(n), static_cast<uint64_t>(m_rows)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(n) * 2};
+    const uint32_t box[2] = {64, 32};
+    int rc = encode_tmap(&tm_c, (out_dtype == 1 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16), 2, c, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B, "C");
+    if (rc) return rc;
+  }
   const int in_fmt = fmt_a | (fmt_b << 4);
 #define B200_LAUNCH8(BN, ST)                                                                                        \
-  launch_m_grouped<BN, ST, false, true>(tm_a, tm_b, c, sizes, sizes_is_i64, num_groups, 0, n, k, in_fmt, out_dtype, \
+  launch_m_grouped<BN, ST, false, true>(tm_a, tm_b, tm_c, c, sizes, sizes_is_i64, num_groups, 0, n, k, in_fmt, out_dtype, \
                                         a_scale, b_scale, grid, stream)
   if (block_n == 256) return B200_LAUNCH8(256, 4);
   if (block_n == 128) return B200_LAUNCH8(128, 6);

@@ -23,7 +23,8 @@ struct KGroupedSmem {
   static constexpr int kABytes = kBlockM * kBlockK * 2;  // 2 chunks of [64 tokens][64 m]
   static constexpr int kBBytes = kBlockN * kBlockK * 2;  // kBlockN/64 chunks of [64 tokens][64 n]
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kBarOffset = kStages * kStageBytes;
+  static constexpr int kEpiOffset = kStages * kStageBytes;  // 4 warps x 2 x 4 KB store staging
+  static constexpr int kBarOffset = kEpiOffset + 4 * kEpiStageBytesPerWarp;
   static constexpr int kNumBars = 2 * kStages + 4;
   static constexpr int kTotal = kBarOffset + kNumBars * 8 + 16;
   static constexpr int kDynamicBytes = kTotal + 1024;
@@ -75,7 +76,7 @@ struct TokenRange {
 template <int kBlockN, int kStages, bool kFp8>
 __global__ void __launch_bounds__(kNumThreads, 1)
 k_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
-                 void* __restrict__ c_ptr, const void* __restrict__ sizes, int sizes_i64,
+                 const __grid_constant__ CUtensorMap tm_c, void* __restrict__ c_ptr, const void* __restrict__ sizes, int sizes_i64,
                  const int* __restrict__ group_start, const int* __restrict__ group_end, int num_groups, int m_dim,
                  int n_dim, long long k_total, int in_fmt, int out_fp16, const float* __restrict__ a_scale,
                  const float* __restrict__ b_scale, unsigned* status) {
@@ -115,6 +116,7 @@ k_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   if (warp == 0 && lane == 0) {
     prefetch_tmap(&tm_a);
     prefetch_tmap(&tm_b);
+    prefetch_tmap(&tm_c);
   }
   if (warp == 1) {
     tmem_alloc<1>(smem_u32(const_cast<uint32_t*>(tmem_holder)), kTmemCols);
@@ -252,6 +254,8 @@ k_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     TokenRange tr;
     tr.init(sizes, sizes_i64, group_start, group_end);
     const int quarter = warp & 3;
+    uint8_t* epi_stage = smem + L::kEpiOffset + quarter * kEpiStageBytesPerWarp;
+    int epi_sel = 0;
     uint32_t tile_iter = 0;
     for (long long tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
       int g, mt, nt;
@@ -271,17 +275,23 @@ k_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       if (!wait_bounded(tmem_full_bar(acc), acc_phase, abort_flag, status, kDevTimeoutEpilogue)) break;
       tc_fence_after_sync();
       const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * kBlockN;
+      float rs = 1.0f;
+      const float* cs = nullptr;
       if constexpr (kFp8) {
-        const float rs = row_ok ? __ldg(a_scale + static_cast<long long>(g) * m_dim + row) : 0.f;
-        store_acc_row_16bit<kBlockN, true>(t_addr, c_row, row_ok, nt * kBlockN, n_dim, out_fp16, rs,
-                                           b_scale + static_cast<long long>(g) * n_dim);
-      } else {
-        store_acc_row_16bit<kBlockN, false>(t_addr, c_row, row_ok, nt * kBlockN, n_dim, out_fp16);
+        rs = row_ok ? __ldg(a_scale + static_cast<long long>(g) * m_dim + row) : 0.f;
+        cs = b_scale + static_cast<long long>(g) * n_dim;
       }
+      const int row_w0 = mt * kBlockM + quarter * 32;
+      if (row_w0 + 32 <= m_dim)
+        store_acc_warp_tma<kBlockN, kFp8>(t_addr, &tm_c, epi_stage, epi_sel, row_w0, g, nt * kBlockN, n_dim, out_fp16,
+                                          lane, rs, cs);
+      else
+        store_acc_row_16bit<kBlockN, kFp8>(t_addr, c_row, row_ok, nt * kBlockN, n_dim, out_fp16, rs, cs);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(tmem_empty_bar(acc));
     }
+    if (lane == 0) tma_store_wait_all<0>();
   }
 
   tc_fence_before_sync();
@@ -297,14 +307,15 @@ k_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 }
 
 template <int kBlockN, int kStages, bool kFp8>
-static int launch_k_grouped(const CUtensorMap& tm_a, const CUtensorMap& tm_b, void* c, const void* sizes,
+static int launch_k_grouped(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const CUtensorMap& tm_c, void* c,
+                            const void* sizes,
                             int sizes_is_i64, const int* gs, const int* ge, int num_groups, int m_dim, int n_dim,
                             long long k_total, int in_fmt, int out_fp16, const float* a_scale, const float* b_scale,
                             int grid, cudaStream_t stream) {
   using L = KGroupedSmem<kBlockN, kStages>;
   auto kern = k_grouped_kernel<kBlockN, kStages, kFp8>;
   B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes));
-  kern<<<grid, kNumThreads, L::kDynamicBytes, stream>>>(tm_a, tm_b, c, sizes, sizes_is_i64, gs, ge, num_groups, m_dim,
+  kern<<<grid, kNumThreads, L::kDynamicBytes, stream>>>(tm_a, tm_b, tm_c, c, sizes, sizes_is_i64, gs, ge, num_groups, m_dim,
                                                         n_dim, k_total, in_fmt, out_fp16, a_scale, b_scale,
                                                         device_status_ptr());
   B200_CUDA(cudaGetLastError());
@@ -365,10 +376,19 @@ extern "C" int b200gemm_k_grouped(const void* a, const void* b, void* c, const v
     int rc = encode_tmap(&tm_b, dt, 2, b_base, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B, "B[K_TOTAL,N_DIM]");
     if (rc) return rc;
   }
+  CUtensorMap tm_c;
+  {
+    const uint64_t dims[3] = {static_cast<uint64_t>(n_dim), static_cast<uint64_t>(m_dim),
+                              static_cast<uint64_t>(num_groups)};
+    const uint64_t strides[2] = {static_cast<uint64_t>(n_dim) * 2, static_cast<uint64_t>(n_dim) * m_dim * 2};
+    const uint32_t box[3] = {64, 32, 1};
+    int rc = encode_tmap(&tm_c, dt, 3, c, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B, "C[G,M_DIM,N_DIM]");
+    if (rc) return rc;
+  }
   const int in_fmt = dtype == 1 ? 0 : 1;  // UMMA kind::f16 operand format: 0 = f16, 1 = bf16
   const int bn = pick_block_n(num_groups, m_dim, n_dim, grid);
 #define B200_LAUNCH_K(BN, ST)                                                                                     \
-  launch_k_grouped<BN, ST, false>(tm_a, tm_b, c, sizes, sizes_is_i64, group_start, group_end, num_groups, m_dim,  \
+  launch_k_grouped<BN, ST, false>(tm_a, tm_b, tm_c, c, sizes, sizes_is_i64, group_start, group_end, num_groups, m_dim,  \
                                   n_dim, k_total, in_fmt, dtype, nullptr, nullptr, grid, stream)
   if (bn == 64) return B200_LAUNCH_K(64, 8);
   if (bn == 128) return B200_LAUNCH_K(128, 6);
@@ -416,9 +436,18 @@ extern "C" int b200gemm_fp8_k_grouped_rowcol(const void* x, const float* x_scale
                          "Y[N,K_TOTAL]");
     if (rc) return rc;
   }
+  CUtensorMap tm_c;
+  {
+    const uint64_t dims[3] = {static_cast<uint64_t>(n_dim), static_cast<uint64_t>(m_dim),
+                              static_cast<uint64_t>(num_groups)};
+    const uint64_t strides[2] = {static_cast<uint64_t>(n_dim) * 2, static_cast<uint64_t>(n_dim) * m_dim * 2};
+    const uint32_t box[3] = {64, 32, 1};
+    int rc = encode_tmap(&tm_c, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, out, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B, "C[G,M_DIM,N_DIM]");
+    if (rc) return rc;
+  }
   const int in_fmt = fmt_x | (fmt_y << 4);
 #define B200_LAUNCH_K8(BN, ST)                                                                                  \
-  launch_k_grouped<BN, ST, true>(tm_x, tm_y, out, tokens_per_expert, sizes_is_i64, nullptr, nullptr, num_groups, \
+  launch_k_grouped<BN, ST, true>(tm_x, tm_y, tm_c, out, tokens_per_expert, sizes_is_i64, nullptr, nullptr, num_groups, \
                                  m_dim, n_dim, k_total, in_fmt, /*out bf16*/ 0, x_scale, y_scale, grid, stream)
   if (bn == 64) return B200_LAUNCH_K8(64, 8);
   if (bn == 128) return B200_LAUNCH_K8(128, 6);

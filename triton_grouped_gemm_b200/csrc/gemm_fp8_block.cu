@@ -37,7 +37,8 @@ struct Fp8BlockCfg {
   static constexpr int kABytes = kBlockM * 128;
   static constexpr int kBBytes = kBlockN * 128;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kBarOffset = kStages * kStageBytes;
+  static constexpr int kEpiOffset = kStages * kStageBytes;  // one 4 KB store-staging buffer per promotion warp
+  static constexpr int kBarOffset = kEpiOffset + kPromoWarps * 32 * 128;
   static constexpr int kNumBars = 2 * kStages + 4;
   static constexpr int kDynamicBytes = kBarOffset + kNumBars * 8 + 16 + 1024;
 };
@@ -45,7 +46,7 @@ struct Fp8BlockCfg {
 template <int kBlockN>
 __global__ void __launch_bounds__(Fp8BlockCfg<kBlockN>::kThreads, 1)
 fp8_block_m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
-                           __nv_bfloat16* __restrict__ c_ptr, const float* __restrict__ a_scale,
+                           const __grid_constant__ CUtensorMap tm_c, __nv_bfloat16* __restrict__ c_ptr, const float* __restrict__ a_scale,
                            const float* __restrict__ b_scale, const void* __restrict__ sizes, int sizes_i64,
                            int num_groups, int masked_stride, int n, int k, unsigned* status) {
   using L = Fp8BlockCfg<kBlockN>;
@@ -83,6 +84,7 @@ fp8_block_m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
   if (warp == 0 && lane == 0) {
     prefetch_tmap(&tm_a);
     prefetch_tmap(&tm_b);
+    prefetch_tmap(&tm_c);
   }
   if (warp == 1) {
     tmem_alloc<1>(smem_u32(const_cast<uint32_t*>(tmem_holder)), kTmemCols);
@@ -192,35 +194,78 @@ fp8_block_m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
       float acc[128];
 #pragma unroll
       for (int j = 0; j < 128; ++j) acc[j] = 0.f;
+      // Software pipeline over 32-column chunks: two tcgen05.ld are kept in flight (t0, t1)
+      // while the previous two chunks are multiplied in, so the TMEM read latency overlaps
+      // the FMAs; the first two chunks of k-block kb+1 are requested before the last FMAs of kb.
+      uint32_t t0[32], t1[32];
+      const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + half * 128;
       float s_next = __ldg(as_row) * __ldg(bs_blk);
+      if (!wait_bounded(tmem_full_bar(it & 1u), (it >> 1) & 1u, abort_flag, status, kDevTimeoutPromote)) break;
+      tc_fence_after_sync();
+      tmem_ld_32x32b_x32(t_lane + (it & 1u) * kBlockN, t0);
+      tmem_ld_32x32b_x32(t_lane + (it & 1u) * kBlockN + 32, t1);
       for (int kb = 0; kb < num_kb; ++kb, ++it) {
         const float s = s_next;
-        if (kb + 1 < num_kb) s_next = __ldg(as_row + kb + 1) * __ldg(bs_blk + kb + 1);
+        const bool more = kb + 1 < num_kb;
+        if (more) s_next = __ldg(as_row + kb + 1) * __ldg(bs_blk + kb + 1);
         const uint32_t buf = it & 1u;
-        const uint32_t buf_phase = (it >> 1) & 1u;
-        if (!wait_bounded(tmem_full_bar(buf), buf_phase, abort_flag, status, kDevTimeoutPromote)) {
-          ok = false;
-          break;
-        }
-        tc_fence_after_sync();
-        const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * kBlockN + half * 128;
+        const uint32_t t_addr = t_lane + buf * kBlockN;
+        tmem_ld_wait();
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32b_x32(t_addr + c * 32, r);
-          tmem_ld_wait();
-          if (c == 3) {
-            // the buffer has been read completely: hand it back before the last FMAs
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(tmem_empty_bar(buf));
+        for (int j = 0; j < 32; ++j) acc[j] = fmaf(s, __uint_as_float(t0[j]), acc[j]);
+        tmem_ld_32x32b_x32(t_addr + 64, t0);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) acc[32 + j] = fmaf(s, __uint_as_float(t1[j]), acc[32 + j]);
+        tmem_ld_32x32b_x32(t_addr + 96, t1);
+        tmem_ld_wait();
+        // every column of this buffer is in registers now: hand it back to the MMA warp
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tmem_empty_bar(buf));
+#pragma unroll
+        for (int j = 0; j < 32; ++j) acc[64 + j] = fmaf(s, __uint_as_float(t0[j]), acc[64 + j]);
+        if (more) {
+          const uint32_t nit = it + 1;
+          if (!wait_bounded(tmem_full_bar(nit & 1u), (nit >> 1) & 1u, abort_flag, status, kDevTimeoutPromote)) {
+            ok = false;
+            break;
           }
-#pragma unroll
-          for (int j = 0; j < 32; ++j) acc[c * 32 + j] = fmaf(s, __uint_as_float(r[j]), acc[c * 32 + j]);
+          tc_fence_after_sync();
+          tmem_ld_32x32b_x32(t_lane + (nit & 1u) * kBlockN, t0);
         }
+#pragma unroll
+        for (int j = 0; j < 32; ++j) acc[96 + j] = fmaf(s, __uint_as_float(t1[j]), acc[96 + j]);
+        if (more) tmem_ld_32x32b_x32(t_lane + ((it + 1) & 1u) * kBlockN + 32, t1);
       }
       if (!ok) break;
-      if (row_ok) {
+      const long long row_w0 = w.tile_row0(mt) + quarter * 32;
+      if (row_w0 + 32 <= w.group_row_end()) {
+        // all 32 rows of this warp are valid: round, stage in the 128-byte-swizzle layout and
+        // let TMA write 64-column chunks (the tensor map clips columns >= n)
+        uint8_t* buf = smem + L::kEpiOffset + (warp - 4) * (32 * 128);
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          const int col0 = col_base + c * 64;
+          if (col0 < n) {
+            if (lane == 0) tma_store_wait_read<0>();
+            __syncwarp();
+#pragma unroll
+            for (int v = 0; v < 8; ++v) {
+              uint32_t p[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e)
+                p[e] = pack2_16bit(acc[c * 64 + v * 8 + 2 * e], acc[c * 64 + v * 8 + 2 * e + 1], 0);
+              *reinterpret_cast<uint4*>(buf + lane * 128 + ((v ^ (lane & 7)) << 4)) = make_uint4(p[0], p[1], p[2], p[3]);
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_2d(&tm_c, smem_u32(buf), col0, static_cast<int>(row_w0));
+              tma_store_commit();
+            }
+          }
+        }
+      } else if (row_ok) {
         __nv_bfloat16* c_row = c_ptr + row * static_cast<long long>(n);
 #pragma unroll
         for (int v = 0; v < 16; ++v) {
@@ -234,6 +279,7 @@ fp8_block_m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
         }
       }
     }
+    if (lane == 0) tma_store_wait_all<0>();
   }
 
   tc_fence_before_sync();
@@ -249,13 +295,13 @@ fp8_block_m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
 }
 
 template <int kBlockN>
-static int launch_fp8_block(const CUtensorMap& tm_a, const CUtensorMap& tm_b, void* c, const float* a_scale,
+static int launch_fp8_block(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const CUtensorMap& tm_c, void* c, const float* a_scale,
                             const float* b_scale, const void* sizes, int sizes_is_i64, int num_groups,
                             int masked_stride, int n, int k, int grid, cudaStream_t stream) {
   using L = Fp8BlockCfg<kBlockN>;
   auto kern = fp8_block_m_grouped_kernel<kBlockN>;
   B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes));
-  kern<<<grid, L::kThreads, L::kDynamicBytes, stream>>>(tm_a, tm_b, static_cast<__nv_bfloat16*>(c), a_scale, b_scale,
+  kern<<<grid, L::kThreads, L::kDynamicBytes, stream>>>(tm_a, tm_b, tm_c, static_cast<__nv_bfloat16*>(c), a_scale, b_scale,
                                                         sizes, sizes_is_i64, num_groups, masked_stride, n, k,
                                                         device_status_ptr());
   B200_CUDA(cudaGetLastError());
@@ -297,10 +343,19 @@ static int fp8_block_common(const void* a, const float* a_scale, const void* b, 
                          "B[G,N,K]");
     if (rc) return rc;
   }
+  CUtensorMap tm_c;
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(n), static_cast<uint64_t>(m_rows)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(n) * 2};
+    const uint32_t box[2] = {64, 32};
+    int rc = encode_tmap(&tm_c, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, c, dims, strides, box,
+                         CU_TENSOR_MAP_SWIZZLE_128B, "C");
+    if (rc) return rc;
+  }
   if (block_n == 256)
-    return launch_fp8_block<256>(tm_a, tm_b, c, a_scale, b_scale, sizes, sizes_is_i64, num_groups, masked_stride, n, k,
+    return launch_fp8_block<256>(tm_a, tm_b, tm_c, c, a_scale, b_scale, sizes, sizes_is_i64, num_groups, masked_stride, n, k,
                                  grid, stream);
-  return launch_fp8_block<128>(tm_a, tm_b, c, a_scale, b_scale, sizes, sizes_is_i64, num_groups, masked_stride, n, k,
+  return launch_fp8_block<128>(tm_a, tm_b, tm_c, c, a_scale, b_scale, sizes, sizes_is_i64, num_groups, masked_stride, n, k,
                                grid, stream);
 }
 

@@ -62,6 +62,64 @@ __device__ __forceinline__ void store_acc_row_16bit(uint32_t t_addr, uint16_t* c
   }
 }
 
+// Warp-collective variant for warps whose 32 rows are all valid: 64-column chunks are rounded,
+// staged in shared memory in the 128-byte-swizzle layout (conflict-free 16-byte stores) and
+// written with one TMA store per chunk; two 4 KB staging buffers per warp alternate so the
+// next chunk is converted while the previous one drains.  The tensor map clips columns >= n
+// and rows past the end of the tensor.  `stage` is this warp's 8 KB (1024-byte aligned),
+// `sel` its current buffer; z >= 0 selects a 3-D map (x = column, y = row, z).
+constexpr int kEpiStageBytesPerWarp = 2 * 32 * 128;
+
+template <int kBlockN, bool kScaled>
+__device__ __forceinline__ void store_acc_warp_tma(uint32_t t_addr, const CUtensorMap* tm_c, uint8_t* stage, int& sel,
+                                                   int row_warp0, int z, int col_base, int n, int is_fp16, int lane,
+                                                   float row_scale = 1.0f,
+                                                   const float* __restrict__ col_scale = nullptr) {
+#pragma unroll 1
+  for (int c = 0; c < kBlockN / 64; ++c) {
+    const int col0 = col_base + c * 64;
+    if (col0 >= n) break;
+    uint32_t r[64];
+    {
+      uint32_t(&lo)[32] = *reinterpret_cast<uint32_t(*)[32]>(&r[0]);
+      uint32_t(&hi)[32] = *reinterpret_cast<uint32_t(*)[32]>(&r[32]);
+      tmem_ld_32x32b_x32(t_addr + c * 64, lo);
+      tmem_ld_32x32b_x32(t_addr + c * 64 + 32, hi);
+    }
+    tmem_ld_wait();
+    if (lane == 0) tma_store_wait_read<1>();  // the buffer written two chunks ago has been read
+    __syncwarp();
+    uint8_t* buf = stage + sel * (32 * 128);
+#pragma unroll
+    for (int v = 0; v < 8; ++v) {
+      float f[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[v * 8 + e]);
+      if constexpr (kScaled) {
+        if (col0 + v * 8 < n) {
+          const float4 s0 = __ldg(reinterpret_cast<const float4*>(col_scale + col0 + v * 8));
+          const float4 s1 = __ldg(reinterpret_cast<const float4*>(col_scale + col0 + v * 8 + 4));
+          const float cs[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+          for (int e = 0; e < 8; ++e) f[e] = __fmul_rn(__fmul_rn(f[e], row_scale), cs[e]);
+        }
+      }
+      uint32_t p[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) p[e] = pack2_16bit(f[2 * e], f[2 * e + 1], is_fp16);
+      *reinterpret_cast<uint4*>(buf + lane * 128 + ((v ^ (lane & 7)) << 4)) = make_uint4(p[0], p[1], p[2], p[3]);
+    }
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      if (z >= 0) tma_store_3d(tm_c, smem_u32(buf), col0, row_warp0, z);
+      else tma_store_2d(tm_c, smem_u32(buf), col0, row_warp0);
+      tma_store_commit();
+    }
+    sel ^= 1;
+  }
+}
+
 // Same footprint, all zeros (a K-grouped output whose group is empty).
 template <int kBlockN>
 __device__ __forceinline__ void store_zero_row_16bit(uint16_t* c_row, bool row_ok, int col_base, int n) {
