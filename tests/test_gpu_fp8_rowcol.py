@@ -19,6 +19,7 @@ E4, E5 = torch.float8_e4m3fn, torch.float8_e5m2
 def _status_clean():
     yield
     _lib.load().b200gemm_set_block_n(0)
+    _lib.load().b200gemm_set_cta_pair(-1)
     assert _lib.device_status() == 0
 
 
@@ -45,6 +46,21 @@ def test_m_grouped_rowcol(sizes, n, k, dtype_out, dt_a, dt_b, block_n):
                                                torch.tensor(sizes, dtype=torch.int32, device=DEV), dtype_out).cpu()
     assert out.dtype == dtype_out and out.shape == (m + 5, n)
     assert O.rdiff(out[:m].float(), ref.float()) < 5e-4
+
+
+def test_m_grouped_rowcol_pair_kernel():
+    sizes, n, k = [300, 0, 700, 130], 512, 384
+    gen = torch.Generator().manual_seed(21)
+    m, g = sum(sizes), len(sizes)
+    x = torch.randn(m, k, generator=gen).bfloat16()
+    a8, a_s = O.per_channel_cast_to_fp8(x, E5)
+    b8 = (torch.randn(g, n, k, generator=gen) * 100).clamp(-400, 400).to(E4)
+    b_s = torch.rand(g, n, generator=gen) * 0.01 + 0.001
+    ref = O.fp8_rowcol_m_grouped_ref(a8, a_s, b8, b_s, sizes, torch.bfloat16)
+    _lib.load().b200gemm_set_cta_pair(1)
+    out = gmm_fp8_act_per_channel_w_per_expert(a8.to(DEV), a_s.to(DEV), b8.to(DEV), b_s.reshape(-1).to(DEV),
+                                               torch.tensor(sizes, dtype=torch.int32, device=DEV), torch.bfloat16).cpu()
+    assert O.rdiff(out.float(), ref.float()) < 5e-4
 
 
 def test_m_grouped_rowcol_reference_test_shape_family():

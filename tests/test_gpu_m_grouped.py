@@ -21,11 +21,13 @@ RDIFF_TOL = 2e-3
 def _reset_tuning():
     yield
     _lib.load().b200gemm_set_block_n(0)
+    _lib.load().b200gemm_set_cta_pair(-1)
     assert _lib.device_status() == 0
 
 
-def _run(a, b, sizes, trans_b, block_n=0, size_dtype=torch.int64):
+def _run(a, b, sizes, trans_b, block_n=0, size_dtype=torch.int64, pair=-1):
     _lib.load().b200gemm_set_block_n(block_n)
+    _lib.load().b200gemm_set_cta_pair(pair)
     n = b.shape[1] if trans_b else b.shape[2]
     c = torch.full((a.shape[0], n), float("nan"), device=DEV, dtype=a.dtype)
     _m_grouped_gemm_launch(a.to(DEV), b.to(DEV), c, sizes.to(DEV, size_dtype), trans_b)
@@ -101,6 +103,52 @@ def test_ragged_vs_oracle(sizes, n, k, trans_b, block_n):
     bb = b if trans_b else b.transpose(1, 2).contiguous()
     out = _run(a, bb, torch.tensor(sizes), trans_b, block_n)
     _check(out, ref, m, tol=2e-4)
+
+
+@pytest.mark.parametrize("trans_b", [True, False])
+def test_pair_kernel_known_answer(trans_b):
+    """CTA-pair kernel on one 256 x 256 x 64 tile with exact integer data."""
+    m, n, k = 256, 256, 64
+    a = torch.zeros(m, k)
+    a[torch.arange(m), torch.arange(m) % k] = 1.0
+    a[128:, 0] += 2.0
+    b_nk = ((torch.arange(n)[:, None] * 3 + torch.arange(k)[None, :] * 5) % 97 - 48).float()
+    b = b_nk if trans_b else b_nk.t().contiguous()
+    ref = a @ b_nk.t()
+    out = _run(a.bfloat16(), b.bfloat16()[None].contiguous(), torch.tensor([m]), trans_b, pair=1)
+    assert torch.equal(out.float(), ref), f"max abs err {(out.float() - ref).abs().max()}"
+
+
+@pytest.mark.parametrize("trans_b", [True, False])
+@pytest.mark.parametrize("sizes,n,k", CASES + [([256, 512, 130, 0, 384, 127], 512, 256), ([1000, 3000], 1536, 512)])
+def test_pair_kernel_vs_oracle(sizes, n, k, trans_b):
+    gen = torch.Generator().manual_seed(n * 31 + k + len(sizes))
+    m = sum(sizes)
+    extra = 7
+    a = (torch.randn(m + extra, k, generator=gen) * 0.5).bfloat16()
+    b = (torch.randn(len(sizes), n, k, generator=gen) * 0.5).bfloat16()
+    ref = O.m_grouped_ref(a[:m], b, sizes, True, fp32_accumulate_explicit=True)
+    bb = b if trans_b else b.transpose(1, 2).contiguous()
+    out = _run(a, bb, torch.tensor(sizes), trans_b, pair=1)
+    _check(out, ref, m, tol=2e-4)
+
+
+def test_pair_kernel_masked():
+    g, e, n, k = 6, 512, 512, 192
+    gen = torch.Generator().manual_seed(17)
+    lhs = (torch.randn(g * e, k, generator=gen) * 0.5).bfloat16()
+    rhs = (torch.randn(g, n, k, generator=gen) * 0.5).bfloat16()
+    masked = torch.tensor([512, 0, 129, 300, 1, 256])
+    init = torch.full((g * e, n), 3.0, dtype=torch.bfloat16)
+    ref = O.m_grouped_masked_ref(lhs, rhs, init, masked, e, fp32_accumulate_explicit=True)
+    out = init.clone().to(DEV)
+    _lib.load().b200gemm_set_cta_pair(1)
+    m_grouped_gemm_masked(lhs.to(DEV), rhs.to(DEV), out, masked.to(DEV), e, True)
+    torch.cuda.synchronize()
+    out = out.cpu()
+    assert O.rdiff(out.float(), ref.float()) < 2e-4
+    for i, mm in enumerate(masked.tolist()):
+        assert torch.all(out[i * e + mm:(i + 1) * e] == 3.0)
 
 
 @pytest.mark.parametrize("size_dtype", [torch.int32, torch.int64])

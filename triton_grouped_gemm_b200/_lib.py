@@ -28,6 +28,8 @@ _SIGNATURES = {
     "b200gemm_device_status": [POINTER(c_uint), c_int],
     "b200gemm_sm_count": [],
     "b200gemm_set_block_n": [c_int],
+    "b200gemm_set_cta_pair": [c_int],
+    "b200gemm_cta_pair_grid": [],
     "b200gemm_m_grouped": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_int, c_int, c_int, c_int,
                            c_int, c_void_p],
     "b200gemm_m_grouped_padded": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_int, c_int, c_int,

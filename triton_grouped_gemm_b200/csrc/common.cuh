@@ -77,6 +77,25 @@ __device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, vola
   return true;
 }
 
+// same, for barriers that the peer CTA of a pair arrives on (cluster-scope acquire)
+__device__ __forceinline__ bool wait_bounded_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                                     unsigned* status, unsigned role_bit) {
+  if (mbar_try_wait_cluster(bar, parity)) return true;
+  const uint64_t t0 = global_timer_ns();
+  uint32_t spins = 0;
+  while (!mbar_try_wait_cluster(bar, parity)) {
+    if ((++spins & 63u) == 0u) {
+      if (*abort_flag) return false;
+      if (global_timer_ns() - t0 > kWaitLimitNs) {
+        *abort_flag = 1;
+        if (status) atomicOr(status, role_bit);
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
 // ------------------------------------------------------------------ group walker
 // Tiles are numbered in "padded tile space": group g owns ceil(size_g / kTileRows)
 // consecutive row tiles.  A walker is advanced monotonically to the row tile a role is about

@@ -251,6 +251,16 @@ static int launch_m_grouped(const CUtensorMap& tm_a, const CUtensorMap& tm_b, co
 
 // 0 = choose the tile width from the problem size; 64 / 128 / 256 force one variant
 static int g_forced_block_n = 0;
+int g_cta_pair_mode = -1;
+
+// The CTA-pair kernel pays off when every pair of SMs gets 256 x 256 tiles to work on.
+static bool want_pair(long long m_rows, int num_groups, int n, int grid, int block_n) {
+  if (g_cta_pair_mode == 0 || grid < 2) return false;
+  if (g_cta_pair_mode == 1) return true;
+  if (block_n != 256 || g_forced_block_n) return false;
+  const long long pair_tiles = (m_rows / 256) * ((n + 255) / 256);
+  return pair_tiles >= grid / 2 && m_rows / 256 >= 4ll * num_groups;
+}
 
 static int m_grouped_common(const void* a, const void* b, void* c, const void* sizes, int sizes_is_i64,
                             int num_groups, int64_t m_rows, int masked_stride, int n, int k, int trans_b, int dtype,
@@ -277,6 +287,8 @@ static int m_grouped_common(const void* a, const void* b, void* c, const void* s
   if (n <= 64 || m_tiles_est * ((n + 127) / 128) < grid) block_n = 64;
   else if (n <= 128 || m_tiles_est * ((n + 255) / 256) < grid) block_n = 128;
   if (g_forced_block_n) block_n = g_forced_block_n;
+  const bool pair = want_pair(m_rows, num_groups, n, grid, block_n);
+  if (pair) block_n = 128;  // per-CTA slice of the 256-wide pair tile (tensor-map box rows)
 
   const CUtensorMapDataType dt = dtype == 1 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   CUtensorMap tm_a, tm_b;
@@ -310,6 +322,15 @@ static int m_grouped_common(const void* a, const void* b, void* c, const void* s
     if (rc) return rc;
   }
   const int in_fmt = dtype == 1 ? 0 : 1;  // UMMA kind::f16 operand format: 0 = f16, 1 = bf16
+  if (pair) {
+    const int want = (num_sms > 0 && num_sms < sms) ? num_sms : 0;
+    return trans_b ? launch_m_grouped_pair<false, false>(tm_a, tm_b, tm_c, c, sizes, sizes_is_i64, num_groups,
+                                                         masked_stride, n, k, in_fmt, dtype, nullptr, nullptr, want,
+                                                         stream)
+                   : launch_m_grouped_pair<true, false>(tm_a, tm_b, tm_c, c, sizes, sizes_is_i64, num_groups,
+                                                        masked_stride, n, k, in_fmt, dtype, nullptr, nullptr, want,
+                                                        stream);
+  }
 #define B200_LAUNCH(BN, ST)                                                                                          \
   (trans_b ? launch_m_grouped<BN, ST, false, false>(tm_a, tm_b, tm_c, c, sizes, sizes_is_i64, num_groups, masked_stride, n, \
                                                     k, in_fmt, dtype, nullptr, nullptr, grid, stream)                \
@@ -348,6 +369,8 @@ static int fp8_rowcol_m_grouped(const void* a, const float* a_scale, const void*
   if (n <= 64 || m_tiles_est * ((n + 127) / 128) < grid) block_n = 64;
   else if (n <= 128 || m_tiles_est * ((n + 255) / 256) < grid) block_n = 128;
   if (g_forced_block_n) block_n = g_forced_block_n;
+  const bool pair = want_pair(m_rows, num_groups, n, grid, block_n);
+  if (pair) block_n = 128;
   CUtensorMap tm_a, tm_b;
   {
     const uint64_t dims[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(m_rows)};
@@ -373,6 +396,10 @@ static int fp8_rowcol_m_grouped(const void* a, const float* a_scale, const void*
     if (rc) return rc;
   }
   const int in_fmt = fmt_a | (fmt_b << 4);
+  if (pair)
+    return launch_m_grouped_pair<false, true>(tm_a, tm_b, tm_c, c, sizes, sizes_is_i64, num_groups, 0, n, k, in_fmt,
+                                              out_dtype, a_scale, b_scale,
+                                              (num_sms > 0 && num_sms < sms) ? num_sms : 0, stream);
 #define B200_LAUNCH8(BN, ST)                                                                                        \
   launch_m_grouped<BN, ST, false, true>(tm_a, tm_b, tm_c, c, sizes, sizes_is_i64, num_groups, 0, n, k, in_fmt, out_dtype, \
                                         a_scale, b_scale, grid, stream)
@@ -399,6 +426,15 @@ int b200gemm_set_block_n(int block_n) {
   b200::g_forced_block_n = block_n;
   return 0;
 }
+
+int b200gemm_set_cta_pair(int mode) {
+  if (mode < -1 || mode > 1)
+    return b200::set_error(b200::kErrInvalidArgument, "b200gemm_set_cta_pair: mode must be -1 (auto), 0 or 1");
+  b200::g_cta_pair_mode = mode;
+  return 0;
+}
+
+int b200gemm_cta_pair_grid(void) { return b200::pair_kernel_grid(); }
 
 int b200gemm_m_grouped(const void* a, const void* b, void* c, const void* sizes, int sizes_is_i64, int num_groups,
                        int64_t m_rows, int n, int k, int trans_b, int dtype, int num_sms, void* stream) {

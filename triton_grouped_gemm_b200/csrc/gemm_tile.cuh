@@ -129,4 +129,16 @@ __device__ __forceinline__ void store_zero_row_16bit(uint16_t* c_row, bool row_o
     *reinterpret_cast<uint4*>(c_row + col) = make_uint4(0, 0, 0, 0);
 }
 
+// CTA-pair (cta_group::2) variant of the M-grouped kernels, 256 x 256 tiles (gemm_pair.cu).
+// `want_ctas` <= 0: as many CTAs as are co-resident.  tm_b must describe 128-row (K-major) or
+// 64 x 64 (MN-major) boxes; tm_a 128-row boxes; tm_c 32 x 64 boxes.
+template <bool kBMnMajor, bool kFp8>
+int launch_m_grouped_pair(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const CUtensorMap& tm_c, void* c,
+                          const void* sizes, int sizes_is_i64, int num_groups, int masked_stride, int n, int k,
+                          int in_fmt, int out_fp16, const float* a_scale, const float* b_scale, int want_ctas,
+                          cudaStream_t stream);
+// -1 = use the pair kernel when the problem is large enough, 0 = never, 1 = whenever possible
+extern int g_cta_pair_mode;
+int pair_kernel_grid();
+
 }  // namespace b200
