@@ -23,6 +23,7 @@ TOL = 5e-4
 @pytest.fixture(autouse=True)
 def _status_clean():
     yield
+    _lib.load().b200gemm_set_cta_pair(-1)
     assert _lib.device_status() == 0
 
 
@@ -57,7 +58,9 @@ def test_single_block_known_answer():
     ([64, 64], 200, 400),            # n not a multiple of 128, k not a multiple of 128
     ([130] * 30, 512, 384),
 ])
-def test_compact_vs_oracle(sizes, n, k):
+@pytest.mark.parametrize("pair", [0, 1])
+def test_compact_vs_oracle(sizes, n, k, pair):
+    _lib.load().b200gemm_set_cta_pair(pair)
     m, g = sum(sizes), len(sizes)
     a8, a_s, b8, b_s = _quantised(m + 3, g, n, (k + 127) // 128 * 128, seed=n + k + g)
     if k % 128:
@@ -101,7 +104,9 @@ def test_gpu_quantisers_feed_the_gemm():
 
 
 @pytest.mark.parametrize("g,e,n,k", [(16, 256, 3072, 512), (4, 128, 128, 256), (3, 384, 640, 384)])
-def test_masked_vs_oracle(g, e, n, k):
+@pytest.mark.parametrize("pair", [0, 1])
+def test_masked_vs_oracle(g, e, n, k, pair):
+    _lib.load().b200gemm_set_cta_pair(pair)
     a8, a_s, b8, b_s = _quantised(g * e, g, n, k, seed=g + e)
     gen = torch.Generator().manual_seed(e)
     masked = torch.randint(0, e + 1, (g,), generator=gen)

@@ -77,6 +77,27 @@ __device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, vola
   return true;
 }
 
+// Polling variant (mbarrier.test_wait, no hardware suspend) for handshakes whose wake-up
+// latency is on the critical path; same bound, same abort protocol.
+__device__ __forceinline__ bool wait_bounded_spin(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                                  unsigned* status, unsigned role_bit) {
+  uint32_t spins = 0;
+  uint64_t t0 = 0;
+  while (!mbar_test_wait(bar, parity)) {
+    if ((++spins & 1023u) == 0u) {
+      if (*abort_flag) return false;
+      const uint64_t now = global_timer_ns();
+      if (t0 == 0) t0 = now;
+      if (now - t0 > kWaitLimitNs) {
+        *abort_flag = 1;
+        if (status) atomicOr(status, role_bit);
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
 // same, for barriers that the peer CTA of a pair arrives on (cluster-scope acquire)
 __device__ __forceinline__ bool wait_bounded_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                                      unsigned* status, unsigned role_bit) {

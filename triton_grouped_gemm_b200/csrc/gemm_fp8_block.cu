@@ -25,32 +25,46 @@
 
 namespace b200 {
 
-template <int kBlockN>
+// kPair: the CTA-pair form (tcgen05 cta_group::2).  Two CTAs on two SMs share a 256 x 256 tile:
+// CTA r holds rows [128 r, +128) of A and of the accumulator and supplies columns [128 r, +128)
+// of B; the leader (rank 0) issues the MMAs for both, its commits are delivered to both CTAs,
+// and both CTAs' promotion warps hand the TMEM buffers back to the leader.  Per CTA a k-block
+// is then 16 KB of A plus 16 KB of B, a third less shared-memory and L2 traffic.
+template <int kBlockN, bool kPair>
 struct Fp8BlockCfg {
-  static constexpr int kStages = kBlockN == 256 ? 4 : 6;
+  static_assert(!kPair || kBlockN == 256, "the CTA-pair form uses 256-column tiles");
+  // 224 KB of shared memory: operand ring + 32 KB store staging + 32 KB scale staging
+  static constexpr int kStages = (kPair || kBlockN == 128) ? 5 : 3;
+  static constexpr int kBRows = kPair ? 128 : kBlockN;  // rows of B_g this CTA loads per k-block
   static constexpr int kPromoWarps = kBlockN / 32;  // 4 lane quarters x (kBlockN/128) column halves
   static constexpr int kThreads = 128 + 32 * kPromoWarps;
-  // 384 threads start at 168 registers each; warpgroup 0 drops to 72 and the two promotion
-  // warpgroups rise to 216 (128*72 + 256*216 <= 64K).  256 threads (BLOCK_N = 128) already
+  // 384 threads start at 168 registers each; warpgroup 0 drops to 56 and the two promotion
+  // warpgroups rise to 224 (128*56 + 256*224 <= 64K).  256 threads (BLOCK_N = 128) already
   // get 255 each and need no re-balancing.
   static constexpr bool kRebalance = kBlockN == 256;
   static constexpr int kABytes = kBlockM * 128;
-  static constexpr int kBBytes = kBlockN * 128;
+  static constexpr int kBBytes = kBRows * 128;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kEpiOffset = kStages * kStageBytes;  // one 4 KB store-staging buffer per promotion warp
-  static constexpr int kBarOffset = kEpiOffset + kPromoWarps * 32 * 128;
-  static constexpr int kNumBars = 2 * kStages + 4;
+  // two 128-row x 32-k-block tiles of a_scale (fp32, 128-byte swizzle), filled by TMA
+  static constexpr int kScaleTileBytes = kBlockM * 128;
+  static constexpr int kScaleOffset = kEpiOffset + 8 * 32 * 128;
+  static constexpr int kBarOffset = kScaleOffset + 2 * kScaleTileBytes;
+  static constexpr int kNumBars = 2 * kStages + 8;  // + scale_full[2], scale_empty[2]
   static constexpr int kDynamicBytes = kBarOffset + kNumBars * 8 + 16 + 1024;
 };
 
-template <int kBlockN>
-__global__ void __launch_bounds__(Fp8BlockCfg<kBlockN>::kThreads, 1)
+template <int kBlockN, bool kPair>
+__global__ void __launch_bounds__(Fp8BlockCfg<kBlockN, kPair>::kThreads, 1)
 fp8_block_m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
-                           const __grid_constant__ CUtensorMap tm_c, __nv_bfloat16* __restrict__ c_ptr, const float* __restrict__ a_scale,
+                           const __grid_constant__ CUtensorMap tm_c, const __grid_constant__ CUtensorMap tm_as,
+                           int scales_by_tma, __nv_bfloat16* __restrict__ c_ptr, const float* __restrict__ a_scale,
                            const float* __restrict__ b_scale, const void* __restrict__ sizes, int sizes_i64,
                            int num_groups, int masked_stride, int n, int k, unsigned* status) {
-  using L = Fp8BlockCfg<kBlockN>;
+  using L = Fp8BlockCfg<kBlockN, kPair>;
   constexpr int kStages = L::kStages;
+  constexpr int kCtas = kPair ? 2 : 1;
+  constexpr int kTileM = kBlockM * kCtas;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t smem_base = smem_u32(smem);
@@ -59,11 +73,16 @@ fp8_block_m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
   auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
   auto tmem_full_bar = [&](int a) { return bar_base + 8u * (2 * kStages + a); };
   auto tmem_empty_bar = [&](int a) { return bar_base + 8u * (2 * kStages + 2 + a); };
+  auto scale_full_bar = [&](int a) { return bar_base + 8u * (2 * kStages + 4 + a); };
+  auto scale_empty_bar = [&](int a) { return bar_base + 8u * (2 * kStages + 6 + a); };
   volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(smem + L::kBarOffset + L::kNumBars * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kBarOffset + L::kNumBars * 8 + 4);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  const uint32_t rank = kPair ? cluster_ctarank() : 0u;  // 0 = leader of the pair
+  const int first_tile = kPair ? (blockIdx.x >> 1) : blockIdx.x;
+  const int tile_step = kPair ? (gridDim.x >> 1) : gridDim.x;
   const int n_tiles = (n + kBlockN - 1) / kBlockN;
   const int num_kb = (k + 127) / 128;
   const int n_blocks = (n + 127) / 128;  // scale blocks of B along n
@@ -76,7 +95,9 @@ fp8_block_m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tmem_full_bar(a), 1);
-      mbar_init(tmem_empty_bar(a), L::kPromoWarps);
+      mbar_init(tmem_empty_bar(a), L::kPromoWarps * kCtas);
+      mbar_init(scale_full_bar(a), 1);
+      mbar_init(scale_empty_bar(a), L::kPromoWarps);
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -85,41 +106,68 @@ fp8_block_m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
     prefetch_tmap(&tm_a);
     prefetch_tmap(&tm_b);
     prefetch_tmap(&tm_c);
+    if (scales_by_tma) prefetch_tmap(&tm_as);
   }
   if (warp == 1) {
-    tmem_alloc<1>(smem_u32(const_cast<uint32_t*>(tmem_holder)), kTmemCols);
-    tmem_relinquish<1>();
+    tmem_alloc<kCtas>(smem_u32(const_cast<uint32_t*>(tmem_holder)), kTmemCols);
+    tmem_relinquish<kCtas>();
   }
   tc_fence_before_sync();
-  __syncthreads();
+  if constexpr (kPair) cluster_sync_all();  // the peer's barriers exist before anyone signals them
+  else __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_holder;
 
   if (warp < 4) {
-  if constexpr (L::kRebalance) warpgroup_reg_dec<72>();
+  if constexpr (L::kRebalance) warpgroup_reg_dec<56>();
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     GroupWalker w;
-    w.init(sizes, sizes_i64, num_groups, masked_stride, kBlockM);
+    w.init(sizes, sizes_i64, num_groups, masked_stride, kTileM);
     int stage = 0;
     uint32_t phase = 0;
+    uint32_t scale_it = 0;  // scale tiles requested so far: buffer = scale_it & 1
     bool ok = true;
-    for (int tile = blockIdx.x; ok; tile += gridDim.x) {
+    for (int tile = first_tile; ok; tile += tile_step) {
       const int mt = tile / n_tiles;
       const int nt = tile - mt * n_tiles;
       if (!w.seek(mt)) break;
-      const int row0 = static_cast<int>(w.tile_row0(mt));
+      const int row0 = static_cast<int>(w.tile_row0(mt)) + static_cast<int>(rank) * kBlockM;
+      const int col0 = nt * kBlockN + static_cast<int>(rank) * L::kBRows;
       const int g = w.g;
       for (int kb = 0; kb < num_kb; ++kb) {
+        if (scales_by_tma && (kb & 31) == 0) {
+          // a_scale[rows of this CTA, 32 k-blocks] -> shared memory, one tile per 32 k-blocks
+          const uint32_t sb = scale_it & 1u;
+          if (!wait_bounded(scale_empty_bar(sb), ((scale_it >> 1) & 1u) ^ 1u, abort_flag, status,
+                            kDevTimeoutProducer)) {
+            ok = false;
+            break;
+          }
+          if (lane == 0) {
+            mbar_arrive_expect_tx(scale_full_bar(sb), L::kScaleTileBytes);
+            tma_load_2d(smem_base + L::kScaleOffset + sb * L::kScaleTileBytes, &tm_as, scale_full_bar(sb), kb, row0);
+          }
+          __syncwarp();
+          ++scale_it;
+        }
         if (!wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag, status, kDevTimeoutProducer)) {
           ok = false;
           break;
         }
         if (lane == 0) {
           const uint32_t a_dst = smem_base + stage * L::kStageBytes;
-          mbar_arrive_expect_tx(full_bar(stage), L::kStageBytes);
-          tma_load_2d(a_dst, &tm_a, full_bar(stage), kb * 128, row0);
-          tma_load_3d(a_dst + L::kABytes, &tm_b, full_bar(stage), kb * 128, nt * kBlockN, g);
+          if constexpr (kPair) {
+            // the leader's barrier collects both CTAs' bytes; one arrival per phase (leader)
+            const uint32_t leader_full = mapa_u32(full_bar(stage), 0);
+            if (rank == 0) mbar_arrive_expect_tx(full_bar(stage), 2 * L::kStageBytes);
+            tma_load_2d_pair(a_dst, &tm_a, leader_full, kb * 128, row0);
+            tma_load_3d_pair(a_dst + L::kABytes, &tm_b, leader_full, kb * 128, col0, g);
+          } else {
+            mbar_arrive_expect_tx(full_bar(stage), L::kStageBytes);
+            tma_load_2d(a_dst, &tm_a, full_bar(stage), kb * 128, row0);
+            tma_load_3d(a_dst + L::kABytes, &tm_b, full_bar(stage), kb * 128, col0, g);
+          }
         }
         __syncwarp();
         if (++stage == kStages) {
@@ -129,15 +177,15 @@ fp8_block_m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer
+    // ------------------------------------------------------------ MMA issuer (pair: leader only)
     GroupWalker w;
-    w.init(sizes, sizes_i64, num_groups, masked_stride, kBlockM);
-    const uint32_t idesc = make_instr_desc(0u, 0u, 0u, 0u, kBlockM, kBlockN);  // e4m3 x e4m3 -> f32
+    w.init(sizes, sizes_i64, num_groups, masked_stride, kTileM);
+    const uint32_t idesc = make_instr_desc(0u, 0u, 0u, 0u, kTileM, kBlockN);  // e4m3 x e4m3 -> f32
     int stage = 0;
     uint32_t phase = 0;
     uint32_t it = 0;  // k-blocks issued so far: TMEM buffer = it & 1
-    bool ok = true;
-    for (int tile = blockIdx.x; ok; tile += gridDim.x) {
+    bool ok = rank == 0;
+    for (int tile = first_tile; ok; tile += tile_step) {
       const int mt = tile / n_tiles;
       if (!w.seek(mt)) break;
       for (int kb = 0; kb < num_kb; ++kb, ++it) {
@@ -157,10 +205,15 @@ fp8_block_m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
           for (int k32 = 0; k32 < 4; ++k32) {
             const uint64_t a_desc = make_smem_desc(a_addr + k32 * 32, 16, 1024, kSwizzle128);
             const uint64_t b_desc = make_smem_desc(b_addr + k32 * 32, 16, 1024, kSwizzle128);
-            umma<1, true>(d_tmem, a_desc, b_desc, idesc, k32 != 0 ? 1u : 0u);
+            umma<kCtas, true>(d_tmem, a_desc, b_desc, idesc, k32 != 0 ? 1u : 0u);
           }
-          umma_commit_1cta(empty_bar(stage));
-          umma_commit_1cta(tmem_full_bar(buf));
+          if constexpr (kPair) {
+            umma_commit_2cta(empty_bar(stage), 0x3);
+            umma_commit_2cta(tmem_full_bar(buf), 0x3);
+          } else {
+            umma_commit_1cta(empty_bar(stage));
+            umma_commit_1cta(tmem_full_bar(buf));
+          }
         }
         __syncwarp();
         if (++stage == kStages) {
@@ -172,18 +225,28 @@ fp8_block_m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
   }
   } else {
     // ------------------------------------------------------------ promotion + epilogue
-    if constexpr (L::kRebalance) warpgroup_reg_inc<216>();
+    if constexpr (L::kRebalance) warpgroup_reg_inc<224>();
     GroupWalker w;
-    w.init(sizes, sizes_i64, num_groups, masked_stride, kBlockM);
+    w.init(sizes, sizes_i64, num_groups, masked_stride, kTileM);
     const int quarter = warp & 3;
     const int half = (warp - 4) >> 2;
     uint32_t it = 0;
+    uint32_t scale_it = 0;
+    // this thread's row inside a staged scale tile: 128 bytes per row, 16-byte chunks XOR-ed
+    // with (row % 8) by the 128-byte swizzle
+    const int srow = quarter * 32 + lane;
+    const uint8_t* scale_tiles = smem + L::kScaleOffset + srow * 128;
+    auto staged_a_scale = [&](uint32_t sb, int kbl) -> float {
+      return *reinterpret_cast<const float*>(scale_tiles + sb * L::kScaleTileBytes +
+                                             ((((kbl >> 2) ^ (srow & 7)) << 4) | ((kbl & 3) << 2)));
+    };
     bool ok = true;
-    for (int tile = blockIdx.x; ok; tile += gridDim.x) {
+    for (int tile = first_tile; ok; tile += tile_step) {
       const int mt = tile / n_tiles;
       const int nt = tile - mt * n_tiles;
       if (!w.seek(mt)) break;
-      const long long row = w.tile_row0(mt) + quarter * 32 + lane;
+      const long long row_w0 = w.tile_row0(mt) + static_cast<long long>(rank) * kBlockM + quarter * 32;
+      const long long row = row_w0 + lane;
       const bool row_ok = row < w.group_row_end();
       const int col_base = nt * kBlockN + half * 128;
       // scales of this thread: its row of A, and the one 128-wide block of B it covers
@@ -191,39 +254,72 @@ fp8_block_m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
       int nb = col_base >> 7;
       if (nb >= n_blocks) nb = n_blocks - 1;  // columns past n: results are discarded
       const float* bs_blk = b_scale + (static_cast<long long>(w.g) * n_blocks + nb) * num_kb;
-      float acc[128];
+      // 128 fp32 accumulators as 64 packed pairs (fma.rn.f32x2: two lanes per instruction)
+      unsigned long long acc2[64];
 #pragma unroll
-      for (int j = 0; j < 128; ++j) acc[j] = 0.f;
+      for (int j = 0; j < 64; ++j) acc2[j] = 0ull;
       // Software pipeline over 32-column chunks: two tcgen05.ld are kept in flight (t0, t1)
       // while the previous two chunks are multiplied in, so the TMEM read latency overlaps
       // the FMAs; the first two chunks of k-block kb+1 are requested before the last FMAs of kb.
       uint32_t t0[32], t1[32];
       const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + half * 128;
-      float s_next = __ldg(as_row) * __ldg(bs_blk);
+      // scale of k-block kb: a_scale[row, kb] * b_scale[g, nb, kb].  With staged scales the a
+      // part comes from shared memory and the b part (uniform over the warp) from a register
+      // of lane kb % 32; otherwise both are read from global memory.
+      float bs_reg = 0.f;
+      uint32_t sb = 0;
+      auto begin_segment = [&](int kb0) -> bool {
+        sb = scale_it & 1u;
+        bs_reg = (kb0 + lane < num_kb) ? __ldg(bs_blk + kb0 + lane) : 0.f;
+        if (!wait_bounded(scale_full_bar(sb), (scale_it >> 1) & 1u, abort_flag, status, kDevTimeoutPromote))
+          return false;
+        ++scale_it;
+        return true;
+      };
+      auto scale_of = [&](int kb) -> float {
+        if (scales_by_tma) return staged_a_scale(sb, kb & 31) * __shfl_sync(0xFFFFFFFFu, bs_reg, kb & 31);
+        return __ldg(as_row + kb) * __ldg(bs_blk + kb);
+      };
+      if (scales_by_tma && !begin_segment(0)) break;
+      float s_next = scale_of(0);
       if (!wait_bounded(tmem_full_bar(it & 1u), (it >> 1) & 1u, abort_flag, status, kDevTimeoutPromote)) break;
       tc_fence_after_sync();
       tmem_ld_32x32b_x32(t_lane + (it & 1u) * kBlockN, t0);
       tmem_ld_32x32b_x32(t_lane + (it & 1u) * kBlockN + 32, t1);
       for (int kb = 0; kb < num_kb; ++kb, ++it) {
-        const float s = s_next;
+        const unsigned long long s2 = pack_f32x2(__float_as_uint(s_next), __float_as_uint(s_next));
         const bool more = kb + 1 < num_kb;
-        if (more) s_next = __ldg(as_row + kb + 1) * __ldg(bs_blk + kb + 1);
+        if (more) {
+          if (scales_by_tma && ((kb + 1) & 31) == 0) {
+            // last use of this scale tile is behind us: hand it back, move to the next one
+            __syncwarp();
+            if (lane == 0) mbar_arrive(scale_empty_bar(sb));
+            if (!begin_segment(kb + 1)) {
+              ok = false;
+              break;
+            }
+          }
+          s_next = scale_of(kb + 1);
+        }
         const uint32_t buf = it & 1u;
         const uint32_t t_addr = t_lane + buf * kBlockN;
         tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < 32; ++j) acc[j] = fmaf(s, __uint_as_float(t0[j]), acc[j]);
+        for (int j = 0; j < 16; ++j) fma_f32x2(acc2[j], s2, pack_f32x2(t0[2 * j], t0[2 * j + 1]));
         tmem_ld_32x32b_x32(t_addr + 64, t0);
 #pragma unroll
-        for (int j = 0; j < 32; ++j) acc[32 + j] = fmaf(s, __uint_as_float(t1[j]), acc[32 + j]);
+        for (int j = 0; j < 16; ++j) fma_f32x2(acc2[16 + j], s2, pack_f32x2(t1[2 * j], t1[2 * j + 1]));
         tmem_ld_32x32b_x32(t_addr + 96, t1);
         tmem_ld_wait();
         // every column of this buffer is in registers now: hand it back to the MMA warp
         tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) mbar_arrive(tmem_empty_bar(buf));
+        if (lane == 0) {
+          if constexpr (kPair) mbar_arrive_cluster(tmem_empty_bar(buf), 0);
+          else mbar_arrive(tmem_empty_bar(buf));
+        }
 #pragma unroll
-        for (int j = 0; j < 32; ++j) acc[64 + j] = fmaf(s, __uint_as_float(t0[j]), acc[64 + j]);
+        for (int j = 0; j < 16; ++j) fma_f32x2(acc2[32 + j], s2, pack_f32x2(t0[2 * j], t0[2 * j + 1]));
         if (more) {
           const uint32_t nit = it + 1;
           if (!wait_bounded(tmem_full_bar(nit & 1u), (nit >> 1) & 1u, abort_flag, status, kDevTimeoutPromote)) {
@@ -234,11 +330,18 @@ fp8_block_m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
           tmem_ld_32x32b_x32(t_lane + (nit & 1u) * kBlockN, t0);
         }
 #pragma unroll
-        for (int j = 0; j < 32; ++j) acc[96 + j] = fmaf(s, __uint_as_float(t1[j]), acc[96 + j]);
+        for (int j = 0; j < 16; ++j) fma_f32x2(acc2[48 + j], s2, pack_f32x2(t1[2 * j], t1[2 * j + 1]));
         if (more) tmem_ld_32x32b_x32(t_lane + ((it + 1) & 1u) * kBlockN + 32, t1);
       }
       if (!ok) break;
-      const long long row_w0 = w.tile_row0(mt) + quarter * 32;
+      if (scales_by_tma) {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(scale_empty_bar(sb));
+      }
+      float acc[128];
+#pragma unroll
+      for (int j = 0; j < 64; ++j) unpack_f32x2(acc2[j], acc[2 * j], acc[2 * j + 1]);
+      if (!ok) break;
       if (row_w0 + 32 <= w.group_row_end()) {
         // all 32 rows of this warp are valid: round, stage in the 128-byte-swizzle layout and
         // let TMA write 64-column chunks (the tensor map clips columns >= n)
@@ -288,22 +391,67 @@ fp8_block_m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
     for (int i = 0; i < 64; ++i) __nanosleep(4000);
     __syncthreads();
   }
+  if constexpr (kPair) cluster_sync_all();  // the peer may still signal this CTA / write its TMEM
   if (warp == 1) {
     tc_fence_after_sync();
-    tmem_dealloc<1>(tmem_base, kTmemCols);
+    tmem_dealloc<kCtas>(tmem_base, kTmemCols);
   }
 }
 
-template <int kBlockN>
-static int launch_fp8_block(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const CUtensorMap& tm_c, void* c, const float* a_scale,
-                            const float* b_scale, const void* sizes, int sizes_is_i64, int num_groups,
-                            int masked_stride, int n, int k, int grid, cudaStream_t stream) {
-  using L = Fp8BlockCfg<kBlockN>;
-  auto kern = fp8_block_m_grouped_kernel<kBlockN>;
+template <int kBlockN, bool kPair>
+static int launch_fp8_block(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const CUtensorMap& tm_c,
+                            const CUtensorMap& tm_as, int scales_by_tma, void* c, const float* a_scale, const float* b_scale, const void* sizes, int sizes_is_i64,
+                            int num_groups, int masked_stride, int n, int k, int grid, cudaStream_t stream) {
+  using L = Fp8BlockCfg<kBlockN, kPair>;
+  auto kern = fp8_block_m_grouped_kernel<kBlockN, kPair>;
   B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes));
-  kern<<<grid, L::kThreads, L::kDynamicBytes, stream>>>(tm_a, tm_b, tm_c, static_cast<__nv_bfloat16*>(c), a_scale, b_scale,
-                                                        sizes, sizes_is_i64, num_groups, masked_stride, n, k,
-                                                        device_status_ptr());
+  if constexpr (kPair) {
+    // a cluster of two CTAs per tile; keep only as many CTAs as are co-resident
+    static int resident[64] = {0};
+    int dev = 0;
+    B200_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return set_error(kErrUnsupported, "device index %d out of range", dev);
+    if (!resident[dev]) {
+      cudaLaunchConfig_t q = {};
+      q.gridDim = dim3(2, 1, 1);
+      q.blockDim = dim3(L::kThreads, 1, 1);
+      q.dynamicSmemBytes = L::kDynamicBytes;
+      cudaLaunchAttribute qa[1];
+      qa[0].id = cudaLaunchAttributeClusterDimension;
+      qa[0].val.clusterDim.x = 2;
+      qa[0].val.clusterDim.y = 1;
+      qa[0].val.clusterDim.z = 1;
+      q.attrs = qa;
+      q.numAttrs = 1;
+      int clusters = 0;
+      if (cudaOccupancyMaxActiveClusters(&clusters, kern, &q) != cudaSuccess || clusters <= 0) {
+        cudaGetLastError();
+        clusters = sm_count() / 2;
+      }
+      resident[dev] = 2 * clusters;
+    }
+    grid = (grid < resident[dev] ? grid : resident[dev]) & ~1;
+    if (grid < 2) return set_error(kErrUnsupported, "the CTA-pair kernel needs at least 2 SMs");
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid, 1, 1);
+    cfg.blockDim = dim3(L::kThreads, 1, 1);
+    cfg.dynamicSmemBytes = L::kDynamicBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    B200_CUDA(cudaLaunchKernelEx(&cfg, kern, tm_a, tm_b, tm_c, tm_as, scales_by_tma, static_cast<__nv_bfloat16*>(c), a_scale, b_scale, sizes,
+                                 sizes_is_i64, num_groups, masked_stride, n, k, device_status_ptr()));
+  } else {
+    kern<<<grid, L::kThreads, L::kDynamicBytes, stream>>>(tm_a, tm_b, tm_c, tm_as, scales_by_tma,
+                                                          static_cast<__nv_bfloat16*>(c), a_scale,
+                                                          b_scale, sizes, sizes_is_i64, num_groups, masked_stride, n,
+                                                          k, device_status_ptr());
+  }
   B200_CUDA(cudaGetLastError());
   return 0;
 }
@@ -327,6 +475,13 @@ static int fp8_block_common(const void* a, const float* a_scale, const void* b, 
   const int grid = (num_sms > 0 && num_sms < sms) ? num_sms : sms;
   const long long m_tiles_est = (m_rows + kBlockM - 1) / kBlockM;
   const int block_n = (n <= 128 || m_tiles_est * ((n + 255) / 256) < grid) ? 128 : 256;
+  // CTA pairs when every pair of SMs gets 256 x 256 tiles (or when forced by the tuning knob)
+  bool pair = false;
+  if (g_cta_pair_mode == 1) pair = grid >= 2;
+  else if (g_cta_pair_mode == -1)
+    pair = block_n == 256 && grid >= 2 && (m_rows / 256) * ((n + 255) / 256) >= grid / 2 &&
+           m_rows / 256 >= 4ll * num_groups;
+  const int b_box_rows = pair ? 128 : block_n;
   CUtensorMap tm_a, tm_b;
   {
     const uint64_t dims[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(m_rows)};
@@ -338,7 +493,7 @@ static int fp8_block_common(const void* a, const float* a_scale, const void* b, 
   {
     const uint64_t dims[3] = {static_cast<uint64_t>(k), static_cast<uint64_t>(n), static_cast<uint64_t>(num_groups)};
     const uint64_t strides[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(k) * n};
-    const uint32_t box[3] = {128, static_cast<uint32_t>(block_n), 1};
+    const uint32_t box[3] = {128, static_cast<uint32_t>(b_box_rows), 1};
     int rc = encode_tmap(&tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, b, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B,
                          "B[G,N,K]");
     if (rc) return rc;
@@ -352,11 +507,26 @@ static int fp8_block_common(const void* a, const float* a_scale, const void* b, 
                          CU_TENSOR_MAP_SWIZZLE_128B, "C");
     if (rc) return rc;
   }
+  // a_scale [m_rows, ceil(k/128)] staged by TMA when its row pitch allows (multiple of 16 bytes)
+  const int num_kb = (k + 127) / 128;
+  const int scales_by_tma = ((num_kb * 4) % 16 == 0 && (reinterpret_cast<uintptr_t>(a_scale) & 15) == 0) ? 1 : 0;
+  CUtensorMap tm_as = tm_c;  // placeholder when unused
+  if (scales_by_tma) {
+    const uint64_t dims[2] = {static_cast<uint64_t>(num_kb), static_cast<uint64_t>(m_rows)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(num_kb) * 4};
+    const uint32_t box[2] = {32, kBlockM};
+    int rc = encode_tmap(&tm_as, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, a_scale, dims, strides, box,
+                         CU_TENSOR_MAP_SWIZZLE_128B, "a_scale");
+    if (rc) return rc;
+  }
+  if (pair)
+    return launch_fp8_block<256, true>(tm_a, tm_b, tm_c, tm_as, scales_by_tma, c, a_scale, b_scale, sizes, sizes_is_i64, num_groups,
+                                       masked_stride, n, k, grid, stream);
   if (block_n == 256)
-    return launch_fp8_block<256>(tm_a, tm_b, tm_c, c, a_scale, b_scale, sizes, sizes_is_i64, num_groups, masked_stride, n, k,
-                                 grid, stream);
-  return launch_fp8_block<128>(tm_a, tm_b, tm_c, c, a_scale, b_scale, sizes, sizes_is_i64, num_groups, masked_stride, n, k,
-                               grid, stream);
+    return launch_fp8_block<256, false>(tm_a, tm_b, tm_c, tm_as, scales_by_tma, c, a_scale, b_scale, sizes, sizes_is_i64, num_groups,
+                                        masked_stride, n, k, grid, stream);
+  return launch_fp8_block<128, false>(tm_a, tm_b, tm_c, tm_as, scales_by_tma, c, a_scale, b_scale, sizes, sizes_is_i64, num_groups,
+                                      masked_stride, n, k, grid, stream);
 }
 
 }  // namespace b200

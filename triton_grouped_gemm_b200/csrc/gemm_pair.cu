@@ -108,7 +108,7 @@ m_grouped_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
       const int col0 = nt * kPairTileN + static_cast<int>(rank) * 128;
       const int g = w.g;
       for (int kb = 0; kb < num_kb; ++kb) {
-        if (!wait_bounded_cluster(empty_bar(stage), phase ^ 1u, abort_flag, status, kDevTimeoutProducer)) {
+        if (!wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag, status, kDevTimeoutProducer)) {
           ok = false;
           break;
         }
@@ -154,11 +154,11 @@ m_grouped_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
         if (!w.seek(mt)) break;
         const uint32_t acc = tile_iter & 1u;
         const uint32_t acc_phase = (tile_iter >> 1) & 1u;
-        if (!wait_bounded_cluster(tmem_empty_bar(acc), acc_phase ^ 1u, abort_flag, status, kDevTimeoutMma)) break;
+        if (!wait_bounded(tmem_empty_bar(acc), acc_phase ^ 1u, abort_flag, status, kDevTimeoutMma)) break;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * kPairTileN;
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!wait_bounded_cluster(full_bar(stage), phase, abort_flag, status, kDevTimeoutMma)) {
+          if (!wait_bounded(full_bar(stage), phase, abort_flag, status, kDevTimeoutMma)) {
             ok = false;
             break;
           }
@@ -203,7 +203,7 @@ m_grouped_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
       const bool row_ok = row < w.group_row_end();
       const uint32_t acc = tile_iter & 1u;
       const uint32_t acc_phase = (tile_iter >> 1) & 1u;
-      if (!wait_bounded_cluster(tmem_full_bar(acc), acc_phase, abort_flag, status, kDevTimeoutEpilogue)) break;
+      if (!wait_bounded(tmem_full_bar(acc), acc_phase, abort_flag, status, kDevTimeoutEpilogue)) break;
       tc_fence_after_sync();
       const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * kPairTileN;
       uint16_t* c_row = static_cast<uint16_t*>(c_ptr) + row * static_cast<long long>(n);
