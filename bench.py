@@ -43,7 +43,14 @@ WORKLOADS = {
     "fp8_block_m_grouped_gate_up": ("fp8_block", 4096, 3072, True),
     "fp8_block_m_grouped_down": ("fp8_block", 1536, 4096, True),
     "quant_act_1x128": ("quant_act", 4096, 0, True),
+    # expert-parallel FP8 MoE layer: K = hidden 4096, N = intermediate 1536, 128 experts, top-8,
+    # --rows = routed rows per GPU (tokens per GPU = rows / 8); NCCL all-to-all dispatch + combine
+    "moe_ep_fp8": ("moe_ep", 4096, 1536, True),
+    # decode: masked layout [experts per GPU, 256 slots], valid counts uniform in [0, 256]
+    "moe_decode_fp8": ("moe_decode", 4096, 1536, True),
 }
+TOP_K = 8
+DECODE_M_MAX = 256
 TOTAL_ROWS = 655360
 NUM_EXPERTS = 128
 ROUTING_SEED = 2026
@@ -134,6 +141,16 @@ def rank_sizes(world: int, rank: int, total_rows: int = TOTAL_ROWS, experts: int
     return ((counts + 127) // 128 * 128).to(torch.int64)
 
 
+def moe_sizes(kind, world, rank, rows):
+    """moe_ep: nominal rows per local expert (only the count of local experts matters; the real
+    sizes come from the routing at run time).  moe_decode: valid rows per local expert slot."""
+    e_loc = NUM_EXPERTS // world
+    if kind == "moe_ep":
+        return torch.full((e_loc,), rows // e_loc, dtype=torch.int64)
+    gen = torch.Generator().manual_seed(ROUTING_SEED + rank)
+    return torch.randint(0, DECODE_M_MAX + 1, (e_loc,), generator=gen, dtype=torch.int64)
+
+
 def make_inputs(kind, k, n, trans_b, sizes, device, seed):
     gen = torch.Generator(device=device).manual_seed(seed)
     m = int(sizes.sum())
@@ -157,6 +174,9 @@ def make_inputs(kind, k, n, trans_b, sizes, device, seed):
         return {"x": randn((m, k), 1.0), "w": randn((g, n, k), 0.02, chunk_rows=4)}
     if kind == "quant_act":
         return {"x": randn((m, k), 1.0)}
+    if kind in ("moe_ep", "moe_decode"):
+        # sizes = this rank's local-expert placeholder vector; k = hidden, n = intermediate
+        return {"w13": randn((g, 2 * n, k), 0.02, chunk_rows=2), "w2": randn((g, k, n), 0.02, chunk_rows=2)}
     raise ValueError(kind)
 
 
@@ -168,6 +188,9 @@ def algorithmic_work(kind, k, n, sizes):
         return 2.0 * rows * n * k, "flop"  # M_DIM=k, N_DIM=n, K_total=rows
     if kind == "quant_act":
         return rows * k * 3.0 + rows * (k // 128) * 4.0, "byte"
+    if kind in ("moe_ep", "moe_decode"):
+        # gate+up [2n x k] and down [k x n] GEMMs for every routed / valid row
+        return 2.0 * rows * (2 * n * k + k * n), "flop"
     raise ValueError(kind)
 
 
@@ -202,6 +225,32 @@ def build_step(kind, k, n, trans_b, sizes_dev, inp):
 
         x = inp["x"]
         return (lambda: inp.__setitem__("c", per_token_cast_to_fp8(x))), 1
+    if kind in ("moe_ep", "moe_decode"):
+        import torch.distributed as dist
+
+        from triton_grouped_gemm_b200.ep.moe_layer import Fp8MoELayer, synthetic_routing
+        from triton_grouped_gemm_b200.quant.per_block_cast import per_token_cast_to_fp8
+
+        group = dist.group.WORLD if dist.is_initialized() else None
+        world = dist.get_world_size() if dist.is_initialized() else 1
+        rank = dist.get_rank() if dist.is_initialized() else 0
+        dev = inp["w13"].device
+        layer = Fp8MoELayer(inp.pop("w13"), inp.pop("w2"), NUM_EXPERTS if kind == "moe_ep" else sizes_dev.numel(), group)
+        inp["layer"] = layer
+        gen = torch.Generator(device=dev).manual_seed(500 + rank)
+        if kind == "moe_ep":
+            tokens = ROWS_USED[0] // TOP_K
+            x = torch.randn(tokens, k, device=dev, generator=gen, dtype=torch.bfloat16)
+            idx, w = synthetic_routing(tokens, NUM_EXPERTS, TOP_K, seed=ROUTING_SEED + rank, device=dev)
+            inp.update(x=x, idx=idx, w=w)
+            # launches per step: 1 act quantiser + 2 GEMMs + 1 SwiGLU quantiser (ours); permutes are torch
+            return (lambda: inp.__setitem__("c", layer.forward(x, idx, w))), 4
+        e_loc = sizes_dev.numel()
+        x = torch.randn(e_loc * DECODE_M_MAX, k, device=dev, generator=gen, dtype=torch.bfloat16)
+        x8, xs = per_token_cast_to_fp8(x)
+        out = torch.zeros(e_loc * DECODE_M_MAX, k, device=dev, dtype=torch.bfloat16)
+        inp.update(x8=x8, xs=xs, out=out)
+        return (lambda: layer.decode(x8, xs, sizes_dev, DECODE_M_MAX, out=out)), 3
     raise ValueError(kind)
 
 
@@ -241,6 +290,19 @@ def cpu_reference_step(kind, k, n, trans_b, sizes, budget_work, seed=7):
     elif kind == "quant_act":
         x = torch.randn(m, k, generator=gen).bfloat16()
         fn = lambda: O.per_token_cast_to_fp8(x)  # noqa: E731
+    elif kind in ("moe_ep", "moe_decode"):
+        # the whole layer on a small token sample routed over 8 experts (fp32 loops on the host)
+        tokens, e_s = 256, 8
+        x = torch.randn(tokens, k, generator=gen).bfloat16()
+        w13 = (torch.randn(e_s, 2 * n, k, generator=gen) * 0.02).bfloat16()
+        w2 = (torch.randn(e_s, k, n, generator=gen) * 0.02).bfloat16()
+        logits = 0.5 * torch.randn(tokens, e_s, generator=gen)
+        wts, idx = torch.topk(torch.softmax(logits, -1), 2, dim=-1)
+        fn = lambda: O.moe_layer_ref(x, idx, wts, w13, w2)  # noqa: E731
+        work = 2.0 * tokens * 2 * (2 * n * k + k * n)
+        desc = (f"{tokens} tokens, top-2 over {e_s} experts of the layer (weights quantised inside the timed call), "
+                f"torch {torch.__version__} on host cores")
+        return fn, work, desc
     else:
         raise ValueError(kind)
     desc = f"first {g} of {sizes.numel()} groups ({m} rows) of the workload, torch {torch.__version__} on host cores"
@@ -256,7 +318,8 @@ def run_reference(args):
     if rank != 0:
         return
     kind, k, n, trans_b = WORKLOADS[args.workload]
-    sizes = rank_sizes(max(args.gpus, 1), 0, args.rows, args.experts)
+    sizes = (moe_sizes(kind, max(args.gpus, 1), 0, args.rows) if kind in ("moe_ep", "moe_decode")
+             else rank_sizes(max(args.gpus, 1), 0, args.rows, args.experts))
     unit, div = unit_of(kind)
     budget = 0.6e12 if unit == "TFLOP/s" else 1.5e9
     fn, work, desc = cpu_reference_step(kind, k, n, trans_b, sizes, budget)
@@ -284,11 +347,14 @@ def run_reference(args):
 def metric_name(kind):
     return {"m_grouped": "grouped-GEMM TFLOP/s (BF16 M-grouped)", "k_grouped": "grouped-GEMM TFLOP/s (BF16 K-grouped)",
             "fp8_block": "grouped-GEMM TFLOP/s (FP8 block-scaled M-grouped)",
-            "quant_act": "per-block quantiser GB/s (1x128 e4m3)"}[kind]
+            "quant_act": "per-block quantiser GB/s (1x128 e4m3)",
+            "moe_ep": "expert-parallel FP8 MoE layer, grouped-GEMM TFLOP/s incl. dispatch/combine",
+            "moe_decode": "FP8 MoE decode (masked layout), grouped-GEMM TFLOP/s"}[kind]
 
 
 def dtype_name(kind):
-    return {"m_grouped": "bf16", "k_grouped": "bf16", "fp8_block": "fp8_e4m3", "quant_act": "bf16->fp8_e4m3"}[kind]
+    return {"m_grouped": "bf16", "k_grouped": "bf16", "fp8_block": "fp8_e4m3", "quant_act": "bf16->fp8_e4m3",
+            "moe_ep": "fp8_e4m3", "moe_decode": "fp8_e4m3"}[kind]
 
 
 def config_of(name, kind, k, n, trans_b, sizes, gpus):
@@ -318,11 +384,14 @@ def run_b200(args):
 
     _lib.load()
     kind, k, n, trans_b = WORKLOADS[args.workload]
-    sizes = rank_sizes(world, rank, args.rows, args.experts)
+    sizes = (moe_sizes(kind, world, rank, args.rows) if kind in ("moe_ep", "moe_decode")
+             else rank_sizes(world, rank, args.rows, args.experts))
     sizes_dev = sizes.to(dev)
     inp = make_inputs(kind, k, n, trans_b, sizes, dev, seed=100 + rank)
     step, launches = build_step(kind, k, n, trans_b, sizes_dev, inp)
     work, _ = algorithmic_work(kind, k, n, sizes)
+    if kind == "moe_ep":
+        work = 2.0 * (args.rows // TOP_K) * TOP_K * (2 * n * k + k * n)
     unit, div = unit_of(kind)
 
     def barrier():
@@ -389,14 +458,16 @@ def run_b200(args):
 
     if rank == 0:
         peaks = measured_peaks()
-        launch_ms = statistics.mean(per_step) / launches
+        # a multi-kernel step (MoE layer) is judged as a whole: flops of its GEMMs over the step time
+        launch_ms = statistics.mean(per_step) / (1 if kind in ("moe_ep", "moe_decode") else launches)
         if unit == "TFLOP/s":
-            peak = peaks["bf16"] * (2.0 if kind == "fp8_block" else 1.0)
+            fp8 = kind in ("fp8_block", "moe_ep", "moe_decode")
+            peak = peaks["bf16"] * (2.0 if fp8 else 1.0)
             achieved = work / (launch_ms * 1e-3) / 1e12
             roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                     "traffic": None,
-                    "peak_source": f"{peaks['source']} cuBLAS bf16 burst" + (" x2 (no fp8 peak measured)" if kind == "fp8_block" else ""),
-                    "frac_of_nominal": achieved / (4500.0 if kind == "fp8_block" else 2250.0),
+                    "peak_source": f"{peaks['source']} cuBLAS bf16 burst" + (" x2 (no fp8 peak measured)" if fp8 else ""),
+                    "frac_of_nominal": achieved / (4500.0 if fp8 else 2250.0),
                     "min_ms": min(per_step), "mean_ms": statistics.mean(per_step)}
         else:
             achieved = work / (launch_ms * 1e-3) / 1e9
@@ -473,6 +544,22 @@ def run_e2e(args, kind, k, n, trans_b, sizes, inp, dev, use_dist, _unused, work)
             d = {kk: v.to(dev, non_blocking=True) for kk, v in host.items()}
             c = m_grouped_fp8_block_scaled((d["a8"], d["a_s"]), (d["b8"], d["b_s"]), d["s"])
             out_host.copy_(c, non_blocking=True)
+    elif kind == "moe_ep":
+        layer = inp["layer"]
+        host = {"x": inp["x"].cpu().pin_memory(), "idx": inp["idx"].cpu().pin_memory(), "w": inp["w"].cpu().pin_memory()}
+        out_host = torch.empty(inp["x"].shape, dtype=torch.bfloat16).pin_memory()
+
+        def one():
+            d = {kk: v.to(dev, non_blocking=True) for kk, v in host.items()}
+            out_host.copy_(layer.forward(d["x"], d["idx"], d["w"]), non_blocking=True)
+    elif kind == "moe_decode":
+        layer = inp["layer"]
+        host = {"x8": inp["x8"].cpu().pin_memory(), "xs": inp["xs"].cpu().pin_memory(), "s": sizes.pin_memory()}
+        out_host = torch.empty(inp["out"].shape, dtype=torch.bfloat16).pin_memory()
+
+        def one():
+            d = {kk: v.to(dev, non_blocking=True) for kk, v in host.items()}
+            out_host.copy_(layer.decode(d["x8"], d["xs"], d["s"], DECODE_M_MAX), non_blocking=True)
     else:
         from triton_grouped_gemm_b200.quant.per_block_cast import per_token_cast_to_fp8
 

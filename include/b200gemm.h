@@ -152,6 +152,12 @@ int b200gemm_fp8_m_grouped_masked_block(const void* a, const float* a_scale, con
  * q [rows, k] bytes; scales [rows, k/128] fp32. */
 int b200quant_act_1x128(const void* x, void* q, float* scales, int64_t rows, int64_t k, int dtype, void* stream);
 
+/* SwiGLU fused with the 1x128 quantiser, for the step between an expert's gate+up and down
+ * GEMMs: h [rows, 2*inter] bf16 (gate | up) -> act = bf16(silu(gate) * up), quantised as by
+ * b200quant_act_1x128.  q [rows, inter] bytes, scales [rows, inter/128].  The reference keeps
+ * this as separate torch steps (README.md:175-179); fusing it saves one HBM round trip of act. */
+int b200quant_swiglu_act_1x128(const void* h, void* q, float* scales, int64_t rows, int64_t inter, void* stream);
+
 /* 128x128 weight quantiser, batched over experts.  Replaces per_block_cast_to_fp8
  * (gemm/FP8/m_grouped_gemm_channel_expert.py:237-245) applied to each x[e].
  * x [batch, rows, cols] 16-bit; q same shape, bytes; scales [batch, ceil(rows/128),

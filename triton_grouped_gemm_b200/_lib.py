@@ -47,6 +47,7 @@ _SIGNATURES = {
     "b200gemm_fp8_m_grouped_masked_block": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                             c_int, c_int, c_int, c_int, c_void_p],
     "b200quant_act_1x128": [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_void_p],
+    "b200quant_swiglu_act_1x128": [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p],
     "b200quant_w_128x128": [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p],
     "b200quant_trans_expand_128x": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int,
                                     c_int64, c_int, c_void_p],

@@ -90,6 +90,62 @@ quant_act_1x128_kernel(const uint4* __restrict__ x, uint2* __restrict__ q, float
   }
 }
 
+// ------------------------------------------------------------------ SwiGLU + 1x128 (between the two expert GEMMs)
+// h [rows, 2*inter] holds gate | up (the gate+up GEMM's output).  act = bf16(silu(gate) * up)
+// with silu(x) = x / (1 + exp(-x)) evaluated in fp32 from the 16-bit inputs; act is then
+// quantised exactly like act_1x128 above (same bytes and scales as running
+// per_token_cast_to_fp8 on the rounded activation).  Saves writing and re-reading act.
+__device__ __forceinline__ float silu_mul_round_bf16(float g, float u) {
+  const float act = __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))), u);
+  return __bfloat162float(__float2bfloat16_rn(act));
+}
+
+__global__ void __launch_bounds__(kActThreads)
+quant_swiglu_1x128_kernel(const uint16_t* __restrict__ h, uint2* __restrict__ q, float* __restrict__ s,
+                          long long rows, int inter) {
+  const long long chunks_per_row = inter / 8;
+  const long long num_chunks = rows * chunks_per_row;
+  const long long stride = static_cast<long long>(gridDim.x) * kActThreads;
+  long long i = static_cast<long long>(blockIdx.x) * kActThreads + threadIdx.x;
+  for (; i - (threadIdx.x & 31) < num_chunks; i += stride) {
+    const bool live = i < num_chunks;
+    float f[8];
+    if (live) {
+      const long long r = i / chunks_per_row;
+      const long long c = (i - r * chunks_per_row) * 8;
+      const uint4 gv = __ldg(reinterpret_cast<const uint4*>(h + r * 2 * inter + c));
+      const uint4 uv = __ldg(reinterpret_cast<const uint4*>(h + r * 2 * inter + inter + c));
+      const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w}, uw[4] = {uv.x, uv.y, uv.z, uv.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        f[2 * e] = silu_mul_round_bf16(to_f32(static_cast<uint16_t>(gw[e] & 0xFFFFu), 0),
+                                       to_f32(static_cast<uint16_t>(uw[e] & 0xFFFFu), 0));
+        f[2 * e + 1] = silu_mul_round_bf16(to_f32(static_cast<uint16_t>(gw[e] >> 16), 0),
+                                           to_f32(static_cast<uint16_t>(uw[e] >> 16), 0));
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) f[e] = 0.f;
+    }
+    float amax = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(f[e]));
+#pragma unroll
+    for (int o = 8; o >= 1; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+    amax = fmaxf(amax, 1e-4f);
+    const float inv = inv_scale_448(amax);
+    uint32_t out[2];
+#pragma unroll
+    for (int p = 0; p < 2; ++p)
+      out[p] = cvt_e4m3x2(__fmul_rn(f[4 * p], inv), __fmul_rn(f[4 * p + 1], inv)) |
+               (cvt_e4m3x2(__fmul_rn(f[4 * p + 2], inv), __fmul_rn(f[4 * p + 3], inv)) << 16);
+    if (live) {
+      q[i] = make_uint2(out[0], out[1]);
+      if ((threadIdx.x & 15) == 0) s[i >> 4] = __fdiv_rn(amax, 448.0f);
+    }
+  }
+}
+
 // ------------------------------------------------------------------ 128x128 (weights)
 // Follows per_block_cast_to_fp8 (gemm/FP8/m_grouped_gemm_channel_expert.py:237-245), batched
 // over a leading expert dimension.  One CTA per 128x128 block; the block stays in registers
@@ -318,6 +374,22 @@ int b200quant_act_1x128(const void* x, void* q, float* scales, int64_t rows, int
   const int grid = grid_for((chunks + kActThreads - 1) / kActThreads, 16);
   quant_act_1x128_kernel<<<grid, kActThreads, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(x), static_cast<uint2*>(q), scales, chunks, dtype);
+  B200_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int b200quant_swiglu_act_1x128(const void* h, void* q, float* scales, int64_t rows, int64_t inter, void* stream) {
+  using namespace b200;
+  B200_REQUIRE(rows >= 0 && inter >= 0, "b200quant_swiglu_act_1x128: negative dimension");
+  B200_REQUIRE(inter % 128 == 0, "b200quant_swiglu_act_1x128: inter (%lld) must be a multiple of 128", (long long)inter);
+  if (rows == 0 || inter == 0) return 0;
+  B200_REQUIRE(h && q && scales, "b200quant_swiglu_act_1x128: null pointer");
+  B200_REQUIRE((reinterpret_cast<uintptr_t>(h) & 15) == 0 && (reinterpret_cast<uintptr_t>(q) & 7) == 0,
+               "b200quant_swiglu_act_1x128: h must be 16-byte and q 8-byte aligned");
+  const long long chunks = rows * inter / 8;
+  const int grid = grid_for((chunks + kActThreads - 1) / kActThreads, 16);
+  quant_swiglu_1x128_kernel<<<grid, kActThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint16_t*>(h), static_cast<uint2*>(q), scales, rows, static_cast<int>(inter));
   B200_CUDA(cudaGetLastError());
   return 0;
 }

@@ -1,0 +1,98 @@
+"""Token dispatch / combine for expert parallelism (device-agnostic torch + torch.distributed).
+
+Each rank owns ``experts_per_rank`` consecutive experts.  ``make_plan`` sorts a rank's
+(token, k) routing pairs by destination expert, exchanges the per-expert counts, and records
+how received rows (ordered by source rank, then expert) map to expert-major order, which is
+the row layout the grouped GEMMs consume (``size_per_group`` = rows per local expert).
+``dispatch`` moves row payloads (any dtype, e.g. fp8 bytes and their fp32 scales) to the
+owning ranks; ``combine`` brings per-row results back and sums the top-k contributions of a
+token with the router weights.  The only collectives are all_to_all_single calls; on GPUs the
+process group is NCCL, in the CPU tests it is gloo.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+
+@dataclass
+class DispatchPlan:
+    world: int
+    experts_per_rank: int
+    num_tokens: int
+    top_k: int
+    send_order: torch.Tensor        # [T*k] indices into the flattened (token, k) pairs, sorted by expert
+    send_splits: List[int]          # rows sent to each rank
+    recv_splits: List[int]          # rows received from each rank
+    recv_to_expert_major: torch.Tensor  # [R] permutation: expert-major row i = received row perm[i]
+    size_per_group: torch.Tensor    # [experts_per_rank] rows per local expert (int64, on the data device)
+
+    @property
+    def rows_received(self) -> int:
+        return int(sum(self.recv_splits))
+
+
+def _all_to_all(out: torch.Tensor, inp: torch.Tensor, out_splits, in_splits, group) -> None:
+    if group is None or dist.get_world_size(group) == 1:
+        out.copy_(inp)
+        return
+    dist.all_to_all_single(out, inp, output_split_sizes=out_splits, input_split_sizes=in_splits, group=group)
+
+
+def make_plan(topk_idx: torch.Tensor, num_experts: int, group: Optional[dist.ProcessGroup] = None) -> DispatchPlan:
+    """topk_idx [T, k] (global expert ids of this rank's tokens)."""
+    world = 1 if group is None else dist.get_world_size(group)
+    assert num_experts % world == 0, "experts must divide evenly over the ranks"
+    e_loc = num_experts // world
+    t, k = topk_idx.shape
+    dev = topk_idx.device
+    flat = topk_idx.reshape(-1).to(torch.int64)
+    send_order = torch.argsort(flat, stable=True)
+    counts = torch.bincount(flat, minlength=num_experts)            # rows per destination expert
+    recv_counts = torch.empty_like(counts)                           # [world * e_loc]: from rank r, expert e
+    _all_to_all(recv_counts, counts, None, None, group)
+    send_splits = counts.view(world, e_loc).sum(1).tolist()
+    recv_matrix = recv_counts.view(world, e_loc)
+    recv_splits = recv_matrix.sum(1).tolist()
+    # received rows come as [source rank][local expert][rows]; expert-major wants [expert][source][rows]
+    blocks = recv_matrix.reshape(-1)                                 # block (r, e) sizes in arrival order
+    starts = torch.cumsum(blocks, 0) - blocks
+    order = torch.arange(world * e_loc, device=dev).view(world, e_loc).t().reshape(-1)  # (e, r) order
+    total = int(sum(recv_splits))
+    blk_sizes = blocks[order]
+    blk_starts = starts[order]
+    out_starts = torch.cumsum(blk_sizes, 0) - blk_sizes
+    row_block = torch.repeat_interleave(torch.arange(order.numel(), device=dev), blk_sizes, output_size=total)
+    perm = blk_starts[row_block] + (torch.arange(total, device=dev) - out_starts[row_block])
+    return DispatchPlan(world=world, experts_per_rank=e_loc, num_tokens=t, top_k=k, send_order=send_order,
+                        send_splits=send_splits, recv_splits=recv_splits, recv_to_expert_major=perm,
+                        size_per_group=recv_matrix.sum(0).to(torch.int64))
+
+
+def dispatch(plan: DispatchPlan, rows: torch.Tensor, group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
+    """rows [T, ...] per token -> [R, ...] rows for this rank's experts, expert-major."""
+    token_of_pair = plan.send_order // plan.top_k
+    send = rows[token_of_pair].contiguous()
+    flat = send.view(torch.uint8) if send.dtype in (torch.float8_e4m3fn, torch.float8_e5m2) else send
+    recv = torch.empty((plan.rows_received,) + tuple(flat.shape[1:]), dtype=flat.dtype, device=flat.device)
+    _all_to_all(recv, flat, plan.recv_splits, plan.send_splits, group)
+    out = recv[plan.recv_to_expert_major]
+    return out.view(rows.dtype) if flat.dtype != rows.dtype else out
+
+
+def combine(plan: DispatchPlan, expert_rows: torch.Tensor, topk_weight: torch.Tensor,
+            group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
+    """expert_rows [R, H] (expert-major results) -> [T, H]: sum_k weight[t,k] * result(t,k)."""
+    back = torch.empty_like(expert_rows)
+    back[plan.recv_to_expert_major] = expert_rows                   # arrival order again
+    ret = torch.empty((plan.send_order.numel(), expert_rows.shape[1]), dtype=expert_rows.dtype,
+                      device=expert_rows.device)
+    _all_to_all(ret, back, plan.send_splits, plan.recv_splits, group)
+    pair_rows = torch.empty_like(ret)
+    pair_rows[plan.send_order] = ret                                 # (token, k) order
+    w = topk_weight.reshape(plan.num_tokens, plan.top_k, 1).to(torch.float32)
+    return (pair_rows.view(plan.num_tokens, plan.top_k, -1).to(torch.float32) * w).sum(1).to(expert_rows.dtype)

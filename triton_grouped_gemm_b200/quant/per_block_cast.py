@@ -45,3 +45,20 @@ def per_block_cast_to_fp8(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
                                              _lib.dtype_code(x.dtype), _lib.stream_ptr(x.device))
     _lib.check(rc, "b200quant_w_128x128")
     return q, s
+
+
+def swiglu_per_token_cast_to_fp8(h: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """h [rows, 2*inter] bf16 holding gate | up -> (e4m3 [rows, inter], scales [rows, inter/128]) of
+    bf16(silu(gate) * up), in one pass (inter % 128 == 0)."""
+    assert h.dim() == 2 and h.dtype == torch.bfloat16 and h.is_contiguous()
+    rows, two_i = h.shape
+    inter = two_i // 2
+    assert two_i == 2 * inter and inter % 128 == 0
+    _lib.require_cuda(h)
+    q = torch.empty((rows, inter), device=h.device, dtype=torch.float8_e4m3fn)
+    s = torch.empty((rows, inter // 128), device=h.device, dtype=torch.float32)
+    with torch.cuda.device(h.device):
+        rc = _lib.load().b200quant_swiglu_act_1x128(_lib.ptr(h), _lib.ptr(q), _lib.ptr(s), rows, inter,
+                                                    _lib.stream_ptr(h.device))
+    _lib.check(rc, "b200quant_swiglu_act_1x128")
+    return q, s
