@@ -96,10 +96,15 @@ int b200gemm_m_grouped_masked(const void* lhs, const void* rhs, void* out, const
  * gemm/BF16/k_grouped_gemm.py:62-216).
  *   A [k_total, m_dim], B [k_total, n_dim] row-major; C [G, m_dim, n_dim].
  *   Token ranges: group_start/group_end (int32 [G], both or neither) if given, else the
- *   running prefix of sizes [G].  Requires m_dim % 8 == 0, n_dim % 8 == 0. */
+ *   running prefix of sizes [G].  Requires m_dim % 8 == 0, n_dim % 8 == 0.
+ *   workspace: optional device scratch of b200gemm_k_grouped_workspace_bytes(G) bytes (contents
+ *   need no initialisation).  With it, tiles are claimed dynamically, groups with the most
+ *   tokens first (tile cost varies with the group's token count); NULL = fixed round-robin
+ *   assignment.  Two calls that overlap on the GPU must not share one workspace. */
+long long b200gemm_k_grouped_workspace_bytes(int num_groups);
 int b200gemm_k_grouped(const void* a, const void* b, void* c, const void* sizes, int sizes_is_i64,
                        const int* group_start, const int* group_end, int num_groups, int64_t k_total, int m_dim,
-                       int n_dim, int dtype, int num_sms, void* stream);
+                       int n_dim, int dtype, void* workspace, int64_t workspace_bytes, int num_sms, void* stream);
 
 /* ---- FP8 grouped GEMMs with per-row x per-channel scales ------------------------------- */
 
@@ -116,10 +121,12 @@ int b200gemm_fp8_m_grouped_rowcol(const void* a, const float* a_scale, const voi
  * x_scale[g*m_dim+m] * y_scale[g*n_dim+n] -> bf16.  Replaces matmul + gemm_kernel_tma
  * (gemm/FP8/k_grouped_gemm_channel_expert.py:64-181).  X [m_dim, k_total], Y [n_dim, k_total]
  * fp8, K-major; the scales are group-major in memory; tokens_per_expert[g] must be a multiple
- * of 128 with zero-padded data, as in the reference.  out [G, m_dim, n_dim] bf16. */
+ * of 128 with zero-padded data, as in the reference.  out [G, m_dim, n_dim] bf16.  workspace: as for
+ * b200gemm_k_grouped. */
 int b200gemm_fp8_k_grouped_rowcol(const void* x, const float* x_scale, const void* y, const float* y_scale, void* out,
                                   const void* tokens_per_expert, int sizes_is_i64, int num_groups, int64_t k_total,
-                                  int m_dim, int n_dim, int fmt_x, int fmt_y, int num_sms, void* stream);
+                                  int m_dim, int n_dim, int fmt_x, int fmt_y, void* workspace, int64_t workspace_bytes,
+                                  int num_sms, void* stream);
 
 /* ---- FP8 grouped GEMMs with 1x128 / 128x128 block scales -------------------------------- */
 

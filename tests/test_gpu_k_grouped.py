@@ -99,6 +99,41 @@ def test_explicit_group_ranges_and_fp16_and_alias_module():
     assert torch.equal(out, out2)
 
 
+def _k_grouped_abi(a, b, sizes, workspace):
+    """Direct C-ABI call: workspace=None -> fixed round-robin tiles, tensor -> balanced scheduler."""
+    g, (k_tot, m_dim), n_dim = sizes.numel(), a.shape, b.shape[1]
+    c = torch.empty(g, m_dim, n_dim, device=DEV, dtype=a.dtype)
+    rc = _lib.load().b200gemm_k_grouped(a.data_ptr(), b.data_ptr(), c.data_ptr(), sizes.data_ptr(), 1, None, None, g,
+                                        k_tot, m_dim, n_dim, 0, workspace.data_ptr() if workspace is not None else None,
+                                        workspace.numel() if workspace is not None else 0, -1,
+                                        torch.cuda.current_stream().cuda_stream)
+    _lib.check(rc, "b200gemm_k_grouped")
+    return c
+
+
+def test_balanced_and_round_robin_schedules_agree():
+    """Groups of very different length: the balanced scheduler (scratch buffer, longest groups
+    first) and the fixed assignment must produce the same bits; scratch is reusable as is."""
+    sizes = [900, 3, 0, 64, 2500, 130, 1, 700, 0, 333]
+    gen = torch.Generator().manual_seed(5)
+    k_tot = sum(sizes)
+    a = (torch.randn(k_tot, 512, generator=gen) * 0.5).bfloat16().to(DEV)
+    b = (torch.randn(k_tot, 768, generator=gen) * 0.5).bfloat16().to(DEV)
+    st = torch.tensor(sizes, dtype=torch.int64, device=DEV)
+    need = int(_lib.load().b200gemm_k_grouped_workspace_bytes(len(sizes)))
+    assert need == (64 + 3 * len(sizes)) * 4
+    ws = torch.full((need,), 0xAB, dtype=torch.uint8, device=DEV)  # garbage on purpose: the plan kernel initialises it
+    c_static = _k_grouped_abi(a, b, st, None)
+    c_bal = _k_grouped_abi(a, b, st, ws)
+    c_bal2 = _k_grouped_abi(a, b, st, ws)  # second call on the same scratch
+    assert torch.equal(c_static, c_bal) and torch.equal(c_bal, c_bal2)
+    ref = O.k_grouped_ref(a.cpu(), b.cpu(), sizes, fp32_accumulate_explicit=True)
+    assert O.rdiff(c_bal.cpu().float(), ref.float()) < 2e-4
+    rc = _lib.load().b200gemm_k_grouped(a.data_ptr(), b.data_ptr(), c_bal.data_ptr(), st.data_ptr(), 1, None, None,
+                                        len(sizes), k_tot, 512, 768, 0, ws.data_ptr(), 16, -1, None)
+    assert rc == -1 and "too small" in _lib.last_error()
+
+
 def test_input_checks():
     a = torch.zeros(16, 128, dtype=torch.bfloat16, device=DEV)
     b = torch.zeros(16, 128, dtype=torch.bfloat16, device=DEV)

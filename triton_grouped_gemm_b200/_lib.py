@@ -37,11 +37,11 @@ _SIGNATURES = {
     "b200gemm_m_grouped_masked": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                                   c_int, c_int, c_void_p],
     "b200gemm_k_grouped": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int64, c_int, c_int,
-                           c_int, c_int, c_void_p],
+                           c_int, c_void_p, c_int64, c_int, c_void_p],
     "b200gemm_fp8_m_grouped_rowcol": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64,
                                       c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "b200gemm_fp8_k_grouped_rowcol": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64,
-                                      c_int, c_int, c_int, c_int, c_int, c_void_p],
+                                      c_int, c_int, c_int, c_int, c_void_p, c_int64, c_int, c_void_p],
     "b200gemm_fp8_m_grouped_block": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64,
                                      c_int, c_int, c_int, c_int, c_void_p],
     "b200gemm_fp8_m_grouped_masked_block": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
@@ -53,7 +53,7 @@ _SIGNATURES = {
                                     c_int64, c_int, c_void_p],
 }
 
-EXPORTED_SYMBOLS = tuple(_SIGNATURES) + ("b200gemm_last_error",)
+EXPORTED_SYMBOLS = tuple(_SIGNATURES) + ("b200gemm_last_error", "b200gemm_k_grouped_workspace_bytes")
 
 
 def load():
@@ -78,6 +78,8 @@ def load():
             fn.restype = c_int
         lib.b200gemm_last_error.argtypes = []
         lib.b200gemm_last_error.restype = c_char_p
+        lib.b200gemm_k_grouped_workspace_bytes.argtypes = [c_int]
+        lib.b200gemm_k_grouped_workspace_bytes.restype = ctypes.c_longlong
         _lib = lib
     return _lib
 
@@ -113,6 +115,16 @@ def device_status(clear: bool = True) -> int:
     out = c_uint(0)
     check(load().b200gemm_device_status(ctypes.byref(out), 1 if clear else 0), "b200gemm_device_status")
     return int(out.value)
+
+
+def k_grouped_workspace(num_groups: int, device: torch.device):
+    """Scratch for the balanced K-grouped scheduler, from torch's stream-ordered allocator (a
+    fresh buffer per call, so calls on different streams never share one).  None when the group
+    count exceeds what the scheduler supports (the kernel then assigns tiles round-robin)."""
+    if num_groups > 4096:
+        return None, 0
+    nbytes = int(load().b200gemm_k_grouped_workspace_bytes(num_groups))
+    return torch.empty(nbytes, dtype=torch.uint8, device=device), nbytes
 
 
 def dtype_code(dtype: torch.dtype) -> int:

@@ -12,6 +12,14 @@
 // multiple of 16 and issues only as many K=16 steps as the group has rows for.
 // An empty group writes zeros (the reference's TMA kernel stores its zero accumulator,
 // gemm/BF16/k_grouped_gemm_TMA.py:141,167-170).
+//
+// Tile cost is proportional to the group's token count, which differs by 10x between experts,
+// so a fixed round-robin assignment leaves SMs idle at the end.  With a scratch buffer the
+// kernel runs BALANCED: a one-block plan kernel writes, per group, the first token row, the
+// token count and the groups' order by decreasing token count, and zeroes a tile counter;
+// the producer warp of every CTA then claims tiles with atomicAdd in that order (long tiles
+// first) and hands each claimed tile id to the CTA's other warps through a small shared-memory
+// ring.  Without scratch (workspace == NULL) tiles are assigned round-robin.
 #include "../../include/b200gemm.h"
 #include "common.cuh"
 #include "gemm_tile.cuh"
@@ -25,8 +33,9 @@ struct KGroupedSmem {
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kEpiOffset = kStages * kStageBytes;  // 4 warps x 2 x 4 KB store staging
   static constexpr int kBarOffset = kEpiOffset + 4 * kEpiStageBytesPerWarp;
-  static constexpr int kNumBars = 2 * kStages + 4;
-  static constexpr int kTotal = kBarOffset + kNumBars * 8 + 16;
+  static constexpr int kSchedDepth = 4;                     // tile-id ring of the balanced scheduler
+  static constexpr int kNumBars = 2 * kStages + 4 + 2 * kSchedDepth;
+  static constexpr int kTotal = kBarOffset + kNumBars * 8 + 16 + kSchedDepth * 4;
   static constexpr int kDynamicBytes = kTotal + 1024;
 };
 
@@ -67,19 +76,61 @@ struct TokenRange {
   }
 };
 
+// Scratch layout (int32 words): [0] tile counter, [1..63] unused, then starts[G], tokens[G], order[G].
+constexpr int kPlanHeaderWords = 64;
+__host__ __device__ inline long long k_grouped_scratch_words(int num_groups) {
+  return kPlanHeaderWords + 3ll * num_groups;
+}
+
+__global__ void __launch_bounds__(1024) k_grouped_plan_kernel(const void* __restrict__ sizes, int sizes_i64,
+                                                              const int* __restrict__ group_start,
+                                                              const int* __restrict__ group_end, int num_groups,
+                                                              int* __restrict__ scratch) {
+  int* starts = scratch + kPlanHeaderWords;
+  int* tokens = starts + num_groups;
+  int* order = tokens + num_groups;
+  auto size_of = [&](int g) -> long long {
+    long long v;
+    if (group_start) v = static_cast<long long>(group_end[g]) - group_start[g];
+    else v = sizes_i64 ? static_cast<const long long*>(sizes)[g] : static_cast<long long>(static_cast<const int*>(sizes)[g]);
+    return v < 0 ? 0 : v;
+  };
+  if (threadIdx.x == 0) {
+    scratch[0] = 0;  // tile counter
+    long long run = 0;
+    for (int g = 0; g < num_groups; ++g) {  // G is small (<= 4096): a serial prefix is a few microseconds
+      const long long t = size_of(g);
+      starts[g] = group_start ? group_start[g] : static_cast<int>(run);
+      tokens[g] = static_cast<int>(t);
+      run += t;
+    }
+  }
+  __syncthreads();
+  // rank of every group in the order "more tokens first, ties by index" (stable)
+  for (int g = threadIdx.x; g < num_groups; g += blockDim.x) {
+    const int tg = tokens[g];
+    int rank = 0;
+    for (int h = 0; h < num_groups; ++h) {
+      const int th = tokens[h];
+      rank += (th > tg) || (th == tg && h < g);
+    }
+    order[rank] = g;
+  }
+}
+
 // kFp8 = false: 16-bit A [K_total, M_DIM], B [K_total, N_DIM] (MN-major operands, 64 tokens
 //               per k-block, `in_fmt`: 0 = f16, 1 = bf16).
 // kFp8 = true:  8-bit X [M, K_total], Y [N, K_total] (K-major operands, 128 tokens per
 //               k-block, `in_fmt` = x_fmt | y_fmt << 4 with 0 = e4m3, 1 = e5m2); the epilogue
 //               applies x_scale[g*M+m] * y_scale[g*N+n]; token counts are multiples of 128
 //               with zero padding (gemm/FP8/k_grouped_gemm_channel_expert.py:64-140).
-template <int kBlockN, int kStages, bool kFp8>
+template <int kBlockN, int kStages, bool kFp8, bool kBalanced>
 __global__ void __launch_bounds__(kNumThreads, 1)
 k_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                  const __grid_constant__ CUtensorMap tm_c, void* __restrict__ c_ptr, const void* __restrict__ sizes, int sizes_i64,
                  const int* __restrict__ group_start, const int* __restrict__ group_end, int num_groups, int m_dim,
                  int n_dim, long long k_total, int in_fmt, int out_fp16, const float* __restrict__ a_scale,
-                 const float* __restrict__ b_scale, unsigned* status) {
+                 const float* __restrict__ b_scale, int* __restrict__ scratch, unsigned* status) {
   constexpr int kTokensPerKb = kFp8 ? 128 : kBlockK;
   using L = KGroupedSmem<kBlockN, kStages>;
   extern __shared__ uint8_t smem_raw[];
@@ -92,6 +143,9 @@ k_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   auto tmem_empty_bar = [&](int a) { return bar_base + 8u * (2 * kStages + 2 + a); };
   volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(smem + L::kBarOffset + L::kNumBars * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kBarOffset + L::kNumBars * 8 + 4);
+  auto sched_full_bar = [&](int i) { return bar_base + 8u * (2 * kStages + 4 + i); };
+  auto sched_empty_bar = [&](int i) { return bar_base + 8u * (2 * kStages + 4 + L::kSchedDepth + i); };
+  volatile int* sched_tile = reinterpret_cast<volatile int*>(smem + L::kBarOffset + L::kNumBars * 8 + 16);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -110,6 +164,10 @@ k_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       mbar_init(tmem_full_bar(a), 1);
       mbar_init(tmem_empty_bar(a), 4);
     }
+    for (int i = 0; i < L::kSchedDepth; ++i) {
+      mbar_init(sched_full_bar(i), 1);
+      mbar_init(sched_empty_bar(i), 5);  // MMA warp + 4 epilogue warps
+    }
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -127,12 +185,33 @@ k_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_holder;
 
-  // tile -> (group, m tile, n tile): n fastest, so CTAs running side by side share A chunks
+  // tile -> (group, m tile, n tile): n fastest, so CTAs running side by side share A chunks.
+  // Balanced mode visits the groups in the plan's order (most tokens first).
+  const int* plan_starts = scratch + kPlanHeaderWords;
+  const int* plan_tokens = plan_starts + num_groups;
+  const int* plan_order = plan_tokens + num_groups;
   auto decode = [&](long long tile, int& g, int& mt, int& nt) {
-    g = static_cast<int>(tile / tiles_per_group);
-    const int local = static_cast<int>(tile - static_cast<long long>(g) * tiles_per_group);
+    const int slot = static_cast<int>(tile / tiles_per_group);
+    const int local = static_cast<int>(tile - static_cast<long long>(slot) * tiles_per_group);
+    g = kBalanced ? plan_order[slot] : slot;
     mt = local / n_tiles;
     nt = local - mt * n_tiles;
+  };
+  // i-th tile of this CTA for a consumer role (MMA / epilogue): static round-robin, or the id the
+  // producer warp claimed and published in the ring.  Returns -1 when there is no more work or a
+  // wait ran out.
+  auto consumer_tile = [&](uint32_t i, unsigned role_bit) -> long long {
+    if constexpr (!kBalanced) {
+      const long long t = blockIdx.x + static_cast<long long>(i) * gridDim.x;
+      return t < num_tiles ? t : -1;
+    } else {
+      const int slot = i % L::kSchedDepth;
+      if (!wait_bounded(sched_full_bar(slot), (i / L::kSchedDepth) & 1u, abort_flag, status, role_bit)) return -1;
+      const int t = sched_tile[slot];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(sched_empty_bar(slot));
+      return t < num_tiles ? t : -1;
+    }
   };
 
   if (warp == 0) {
@@ -142,10 +221,36 @@ k_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
-    for (long long tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+    for (uint32_t i = 0; ok; ++i) {
+      long long tile;
+      if constexpr (kBalanced) {
+        // claim the next tile and publish its id (also the end marker) to the other warps
+        int t = 0;
+        if (lane == 0) t = atomicAdd(scratch, 1);
+        t = __shfl_sync(0xFFFFFFFFu, t, 0);
+        const int slot = i % L::kSchedDepth;
+        if (!wait_bounded(sched_empty_bar(slot), ((i / L::kSchedDepth) & 1u) ^ 1u, abort_flag, status,
+                          kDevTimeoutProducer))
+          break;
+        if (lane == 0) {
+          sched_tile[slot] = t;
+          mbar_arrive(sched_full_bar(slot));
+        }
+        __syncwarp();
+        tile = t;
+      } else {
+        tile = blockIdx.x + static_cast<long long>(i) * gridDim.x;
+      }
+      if (tile >= num_tiles) break;
       int g, mt, nt;
       decode(tile, g, mt, nt);
-      const long long tokens = tr.seek(g);
+      long long tokens;
+      if constexpr (kBalanced) {
+        tr.start = plan_starts[g];
+        tokens = plan_tokens[g];
+      } else {
+        tokens = tr.seek(g);
+      }
       const int num_kb = static_cast<int>((tokens + kTokensPerKb - 1) / kTokensPerKb);
       for (int kb = 0; kb < num_kb; ++kb) {
         if (!wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag, status, kDevTimeoutProducer)) {
@@ -188,10 +293,12 @@ k_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     uint32_t phase = 0;
     uint32_t tile_iter = 0;  // counts non-empty tiles only (same rule in the epilogue)
     bool ok = true;
-    for (long long tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+    for (uint32_t i = 0; ok; ++i) {
+      const long long tile = consumer_tile(i, kDevTimeoutMma);
+      if (tile < 0) break;
       int g, mt, nt;
       decode(tile, g, mt, nt);
-      const long long tokens = tr.seek(g);
+      const long long tokens = kBalanced ? static_cast<long long>(plan_tokens[g]) : tr.seek(g);
       if (tokens == 0) continue;
       const int num_kb = static_cast<int>((tokens + kTokensPerKb - 1) / kTokensPerKb);
       const uint32_t acc = tile_iter & 1u;
@@ -257,10 +364,12 @@ k_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     uint8_t* epi_stage = smem + L::kEpiOffset + quarter * kEpiStageBytesPerWarp;
     int epi_sel = 0;
     uint32_t tile_iter = 0;
-    for (long long tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+    for (uint32_t i = 0;; ++i) {
+      const long long tile = consumer_tile(i, kDevTimeoutEpilogue);
+      if (tile < 0) break;
       int g, mt, nt;
       decode(tile, g, mt, nt);
-      const long long tokens = tr.seek(g);
+      const long long tokens = kBalanced ? static_cast<long long>(plan_tokens[g]) : tr.seek(g);
       const int row = mt * kBlockM + quarter * 32 + lane;
       const bool row_ok = row < m_dim;
       uint16_t* c_row = static_cast<uint16_t*>(c_ptr) +
@@ -308,17 +417,44 @@ k_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 
 template <int kBlockN, int kStages, bool kFp8>
 static int launch_k_grouped(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const CUtensorMap& tm_c, void* c,
-                            const void* sizes,
-                            int sizes_is_i64, const int* gs, const int* ge, int num_groups, int m_dim, int n_dim,
-                            long long k_total, int in_fmt, int out_fp16, const float* a_scale, const float* b_scale,
-                            int grid, cudaStream_t stream) {
+                            const void* sizes, int sizes_is_i64, const int* gs, const int* ge, int num_groups,
+                            int m_dim, int n_dim, long long k_total, int in_fmt, int out_fp16, const float* a_scale,
+                            const float* b_scale, int* scratch, int grid, cudaStream_t stream) {
   using L = KGroupedSmem<kBlockN, kStages>;
-  auto kern = k_grouped_kernel<kBlockN, kStages, kFp8>;
-  B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes));
-  kern<<<grid, kNumThreads, L::kDynamicBytes, stream>>>(tm_a, tm_b, tm_c, c, sizes, sizes_is_i64, gs, ge, num_groups, m_dim,
-                                                        n_dim, k_total, in_fmt, out_fp16, a_scale, b_scale,
-                                                        device_status_ptr());
+  unsigned* status = device_status_ptr();
+  if (scratch) {
+    // balanced: plan (starts, token counts, longest-first order, zeroed tile counter), then the GEMM
+    auto kern = k_grouped_kernel<kBlockN, kStages, kFp8, true>;
+    B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes));
+    k_grouped_plan_kernel<<<1, 1024, 0, stream>>>(sizes, sizes_is_i64, gs, ge, num_groups, scratch);
+    B200_CUDA(cudaGetLastError());
+    kern<<<grid, kNumThreads, L::kDynamicBytes, stream>>>(tm_a, tm_b, tm_c, c, sizes, sizes_is_i64, gs, ge, num_groups,
+                                                          m_dim, n_dim, k_total, in_fmt, out_fp16, a_scale, b_scale,
+                                                          scratch, status);
+  } else {
+    auto kern = k_grouped_kernel<kBlockN, kStages, kFp8, false>;
+    B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes));
+    kern<<<grid, kNumThreads, L::kDynamicBytes, stream>>>(tm_a, tm_b, tm_c, c, sizes, sizes_is_i64, gs, ge, num_groups,
+                                                          m_dim, n_dim, k_total, in_fmt, out_fp16, a_scale, b_scale,
+                                                          nullptr, status);
+  }
   B200_CUDA(cudaGetLastError());
+  return 0;
+}
+
+constexpr int kMaxBalancedGroups = 4096;
+
+// validates a caller-provided scratch buffer for the balanced scheduler; nullptr = round-robin
+static int check_scratch(void* workspace, long long workspace_bytes, int num_groups, const char* who, int** out) {
+  *out = nullptr;
+  if (!workspace) return 0;
+  B200_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 3) == 0, "%s: workspace must be 4-byte aligned", who);
+  B200_REQUIRE(num_groups <= kMaxBalancedGroups, "%s: the balanced scheduler supports at most %d groups (got %d)", who,
+               kMaxBalancedGroups, num_groups);
+  const long long need = k_grouped_scratch_words(num_groups) * 4;
+  B200_REQUIRE(workspace_bytes >= need, "%s: workspace of %lld bytes is too small, %lld needed", who, workspace_bytes,
+               need);
+  *out = static_cast<int*>(workspace);
   return 0;
 }
 
@@ -332,11 +468,14 @@ static int pick_block_n(int num_groups, int m_dim, int n_dim, int grid) {
 
 }  // namespace b200
 
-extern "C" int b200gemm_k_grouped(const void* a, const void* b, void* c, const void* sizes, int sizes_is_i64,
-                                  const int* group_start, const int* group_end, int num_groups, int64_t k_total, int m_dim, int n_dim, int dtype, int num_sms,
-                                  void* stream_v) {
-  using namespace b200;
-  const char* who = "b200gemm_k_grouped";
+extern "C" long long b200gemm_k_grouped_workspace_bytes(int num_groups) {
+  return num_groups < 0 ? 0 : b200::k_grouped_scratch_words(num_groups) * 4;
+}
+
+namespace b200 {
+static int k_grouped_bf16(const void* a, const void* b, void* c, const void* sizes, int sizes_is_i64,
+                          const int* group_start, const int* group_end, int num_groups, int64_t k_total, int m_dim,
+                          int n_dim, int dtype, int* scratch, int num_sms, void* stream_v, const char* who) {
   B200_REQUIRE(dtype == 0 || dtype == 1, "%s: dtype must be 0 (bf16) or 1 (fp16), got %d", who, dtype);
   B200_REQUIRE(num_groups >= 0 && k_total >= 0 && m_dim >= 0 && n_dim >= 0, "%s: negative dimension", who);
   if (num_groups == 0 || m_dim == 0 || n_dim == 0) return 0;
@@ -389,19 +528,37 @@ extern "C" int b200gemm_k_grouped(const void* a, const void* b, void* c, const v
   const int bn = pick_block_n(num_groups, m_dim, n_dim, grid);
 #define B200_LAUNCH_K(BN, ST)                                                                                     \
   launch_k_grouped<BN, ST, false>(tm_a, tm_b, tm_c, c, sizes, sizes_is_i64, group_start, group_end, num_groups, m_dim,  \
-                                  n_dim, k_total, in_fmt, dtype, nullptr, nullptr, grid, stream)
+                                  n_dim, k_total, in_fmt, dtype, nullptr, nullptr, scratch, grid, stream)
   if (bn == 64) return B200_LAUNCH_K(64, 8);
   if (bn == 128) return B200_LAUNCH_K(128, 6);
   return B200_LAUNCH_K(256, 4);
 #undef B200_LAUNCH_K
 }
+}  // namespace b200
+
+extern "C" int b200gemm_k_grouped(const void* a, const void* b, void* c, const void* sizes, int sizes_is_i64,
+                                  const int* group_start, const int* group_end, int num_groups, int64_t k_total,
+                                  int m_dim, int n_dim, int dtype, void* workspace, int64_t workspace_bytes,
+                                  int num_sms, void* stream) {
+  int* scratch = nullptr;
+  int rc = b200::check_scratch(workspace, workspace_bytes, num_groups, "b200gemm_k_grouped", &scratch);
+  if (rc) return rc;
+  return b200::k_grouped_bf16(a, b, c, sizes, sizes_is_i64, group_start, group_end, num_groups, k_total, m_dim, n_dim,
+                              dtype, scratch, num_sms, stream, "b200gemm_k_grouped");
+}
 
 extern "C" int b200gemm_fp8_k_grouped_rowcol(const void* x, const float* x_scale, const void* y, const float* y_scale,
                                              void* out, const void* tokens_per_expert, int sizes_is_i64,
                                              int num_groups, int64_t k_total, int m_dim, int n_dim, int fmt_x,
-                                             int fmt_y, int num_sms, void* stream_v) {
+                                             int fmt_y, void* workspace, int64_t workspace_bytes, int num_sms,
+                                             void* stream_v) {
   using namespace b200;
   const char* who = "b200gemm_fp8_k_grouped_rowcol";
+  int* scratch = nullptr;
+  {
+    int rc = check_scratch(workspace, workspace_bytes, num_groups, who, &scratch);
+    if (rc) return rc;
+  }
   B200_REQUIRE((fmt_x == 0 || fmt_x == 1) && (fmt_y == 0 || fmt_y == 1), "%s: fp8 format must be 0 (e4m3) or 1 (e5m2)",
                who);
   B200_REQUIRE(num_groups >= 0 && k_total >= 0 && m_dim >= 0 && n_dim >= 0, "%s: negative dimension", who);
@@ -448,7 +605,7 @@ extern "C" int b200gemm_fp8_k_grouped_rowcol(const void* x, const float* x_scale
   const int in_fmt = fmt_x | (fmt_y << 4);
 #define B200_LAUNCH_K8(BN, ST)                                                                                  \
   launch_k_grouped<BN, ST, true>(tm_x, tm_y, tm_c, out, tokens_per_expert, sizes_is_i64, nullptr, nullptr, num_groups, \
-                                 m_dim, n_dim, k_total, in_fmt, /*out bf16*/ 0, x_scale, y_scale, grid, stream)
+                                 m_dim, n_dim, k_total, in_fmt, /*out bf16*/ 0, x_scale, y_scale, scratch, grid, stream)
   if (bn == 64) return B200_LAUNCH_K8(64, 8);
   if (bn == 128) return B200_LAUNCH_K8(128, 6);
   return B200_LAUNCH_K8(256, 4);

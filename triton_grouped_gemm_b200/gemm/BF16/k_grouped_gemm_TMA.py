@@ -58,10 +58,12 @@ def k_grouped_gemm(A: Tensor, B: Tensor, size_per_group: Tensor, group_start: Op
         ge = group_end.to(torch.int32).contiguous()
     sizes, is64 = _lib.sizes_arg(size_per_group)
     with torch.cuda.device(A.device):
+        ws, ws_bytes = _lib.k_grouped_workspace(num_groups, A.device)
         rc = _lib.load().b200gemm_k_grouped(
             _lib.ptr(A), _lib.ptr(B), _lib.ptr(C), _lib.ptr(sizes), is64,
             _lib.ptr(gs) if gs is not None else None, _lib.ptr(ge) if ge is not None else None,
-            num_groups, K_TOTAL, M_DIM, N_DIM, _dtype_code(A.dtype), int(numSM), _lib.stream_ptr(A.device))
+            num_groups, K_TOTAL, M_DIM, N_DIM, _dtype_code(A.dtype), _lib.ptr(ws) if ws is not None else None,
+            ws_bytes, int(numSM), _lib.stream_ptr(A.device))
     _lib.check(rc, "b200gemm_k_grouped")
     return C
 

@@ -41,8 +41,10 @@ def matmul(x_fp8: torch.Tensor, x_scale: torch.Tensor, y_fp8: torch.Tensor, y_sc
     sizes, is64 = _lib.sizes_arg(tokens_per_expert)
     out = torch.empty((num_groups, M, N), dtype=torch.bfloat16, device=x_fp8.device)
     with torch.cuda.device(x_fp8.device):
+        ws, ws_bytes = _lib.k_grouped_workspace(num_groups, x_fp8.device)
         rc = _lib.load().b200gemm_fp8_k_grouped_rowcol(
             _lib.ptr(x_fp8), _lib.ptr(xs), _lib.ptr(y_fp8), _lib.ptr(ys), _lib.ptr(out), _lib.ptr(sizes), is64,
-            num_groups, K, M, N, fp8_code(x_fp8.dtype), fp8_code(y_fp8.dtype), -1, _lib.stream_ptr(x_fp8.device))
+            num_groups, K, M, N, fp8_code(x_fp8.dtype), fp8_code(y_fp8.dtype),
+            _lib.ptr(ws) if ws is not None else None, ws_bytes, -1, _lib.stream_ptr(x_fp8.device))
     _lib.check(rc, "b200gemm_fp8_k_grouped_rowcol")
     return out
