@@ -106,6 +106,24 @@ int b200gemm_k_grouped(const void* a, const void* b, void* c, const void* sizes,
                        const int* group_start, const int* group_end, int num_groups, int64_t k_total, int m_dim,
                        int n_dim, int dtype, void* workspace, int64_t workspace_bytes, int num_sms, void* stream);
 
+/* The balanced K-grouped GEMM for callers that cannot supply device memory.  It has no
+ * counterpart in the reference.  Written for hosts that may not allocate on the GPU: a runtime
+ * that gave all of HBM to its own pools (a later cudaMalloc fails or is against its rules), or a
+ * latency-critical loop that cannot afford the device-wide synchronisation cudaMalloc implies,
+ * reached from C where no framework allocator is at hand.  Same arguments and results as
+ * b200gemm_k_grouped without the workspace pair: the scheduler's scratch is a fixed array inside
+ * the library (12.5 KB held by every GPU that loads it, for the life of the process).
+ *   - At most 1024 groups; more are rejected with B200GEMM_ERR_INVALID_ARGUMENT.
+ *   - Calls no cudaMalloc / cudaFree and no allocating library routine.
+ *   - The first call on each device looks up the array's device address (once, cached); make
+ *     that first call before starting any stream capture on that device.
+ *   - All calls on a device share the one array.  Nothing needs clearing between calls (each
+ *     call rewrites what it reads), but two calls whose kernels overlap on the GPU - different
+ *     streams, or different host threads - race on it and compute garbage: serialise them. */
+int b200gemm_k_grouped_static_scratch(const void* a, const void* b, void* c, const void* sizes, int sizes_is_i64,
+                                      const int* group_start, const int* group_end, int num_groups, int64_t k_total,
+                                      int m_dim, int n_dim, int dtype, int num_sms, void* stream);
+
 /* ---- FP8 grouped GEMMs with per-row x per-channel scales ------------------------------- */
 
 /* FP8 M-grouped GEMM: C[m, n] = (sum_k A[m,k] * B[g,n,k])_fp32 * a_scale[m] * b_scale[g*n_dim+n].

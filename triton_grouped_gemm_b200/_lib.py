@@ -38,6 +38,8 @@ _SIGNATURES = {
                                   c_int, c_int, c_void_p],
     "b200gemm_k_grouped": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int64, c_int, c_int,
                            c_int, c_void_p, c_int64, c_int, c_void_p],
+    "b200gemm_k_grouped_static_scratch": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int,
+                                          c_int64, c_int, c_int, c_int, c_int, c_void_p],
     "b200gemm_fp8_m_grouped_rowcol": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64,
                                       c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "b200gemm_fp8_k_grouped_rowcol": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64,

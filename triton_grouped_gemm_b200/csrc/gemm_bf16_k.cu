@@ -20,6 +20,8 @@
 // the producer warp of every CTA then claims tiles with atomicAdd in that order (long tiles
 // first) and hands each claimed tile id to the CTA's other warps through a small shared-memory
 // ring.  Without scratch (workspace == NULL) tiles are assigned round-robin.
+#include <mutex>
+
 #include "../../include/b200gemm.h"
 #include "common.cuh"
 #include "gemm_tile.cuh"
@@ -610,4 +612,58 @@ extern "C" int b200gemm_fp8_k_grouped_rowcol(const void* x, const float* x_scale
   if (bn == 128) return B200_LAUNCH_K8(128, 6);
   return B200_LAUNCH_K8(256, 4);
 #undef B200_LAUNCH_K8
+}
+
+// ------------------------------------------------------------------ balanced K-grouped GEMM without caller scratch
+// Some hosts of this library cannot hand it device memory: a serving runtime that reserved the
+// whole HBM for its own pools at start-up (a later cudaMalloc fails or is forbidden by policy),
+// or a latency-critical loop in which cudaMalloc's implicit device-wide synchronisation is not
+// acceptable, called from C where the framework's caching allocator is out of reach.  For them
+// the scheduler's scratch lives in this fixed array, which every GPU that loads the library
+// carries until the process exits: (64 + 3 * 1024) * 4 bytes = 12.5 KB.
+namespace b200 {
+
+constexpr int kStaticScratchMaxGroups = 1024;
+static __device__ __align__(256) int g_k_grouped_static_scratch[kPlanHeaderWords + 3 * kStaticScratchMaxGroups];
+
+// Device address of the array on the current device.  In host code the array's name is only a
+// handle for the runtime, never a pointer a kernel may dereference, so the address is looked up
+// with cudaGetSymbolAddress - once per device, with that device current - and cached.
+static int static_scratch_address(int** out, const char* who) {
+  static std::mutex mu;
+  static int* cached[64] = {nullptr};
+  int dev = 0;
+  B200_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return set_error(kErrUnsupported, "%s: device index %d out of range", who, dev);
+  std::lock_guard<std::mutex> lock(mu);
+  if (!cached[dev]) {
+    int* ptr = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress((void**)&ptr, g_k_grouped_static_scratch);
+    if (e != cudaSuccess || ptr == nullptr)
+      return set_error(kErrCuda, "%s: cudaGetSymbolAddress failed for the static scratch: %s", who,
+                       cudaGetErrorString(e));
+    cached[dev] = ptr;
+  }
+  *out = cached[dev];
+  return 0;
+}
+
+}  // namespace b200
+
+extern "C" int b200gemm_k_grouped_static_scratch(const void* a, const void* b, void* c, const void* sizes,
+                                                 int sizes_is_i64, const int* group_start, const int* group_end,
+                                                 int num_groups, int64_t k_total, int m_dim, int n_dim, int dtype,
+                                                 int num_sms, void* stream) {
+  using namespace b200;
+  const char* who = "b200gemm_k_grouped_static_scratch";
+  B200_REQUIRE(num_groups <= kStaticScratchMaxGroups,
+               "%s: %d groups exceed the %d the built-in scratch holds; use b200gemm_k_grouped with a workspace", who,
+               num_groups, kStaticScratchMaxGroups);
+  int* scratch = nullptr;
+  int rc = static_scratch_address(&scratch, who);
+  if (rc) return rc;
+  // The plan kernel launched inside rewrites every word it later reads (tile counter, starts,
+  // token counts, order), so whatever the previous call left in the array is harmless.
+  return k_grouped_bf16(a, b, c, sizes, sizes_is_i64, group_start, group_end, num_groups, k_total, m_dim, n_dim, dtype,
+                        scratch, num_sms, stream, who);
 }
