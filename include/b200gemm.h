@@ -201,6 +201,20 @@ int b200quant_trans_expand_128x(const void* x, const void* sizes, int sizes_is_i
                                 float* scales, int64_t* padded_sizes_out, int64_t m_rows, int n, int64_t m_expand,
                                 int dtype, void* stream);
 
+/* ---- row movement around the expert GEMMs (expert-parallel MoE layer) --------------------- */
+
+/* dst[i, :] = src[idx[i], :] for i < rows (rows of row_bytes bytes, a multiple of 16; idx int64).
+ * The dispatch-side gather into expert-major order; the reference has this only in its vendored
+ * baseline extension (grouped_gemm/csrc/permute.cu:40-297, moe_permute_topK_kernel). */
+int b200moe_gather_rows(const void* src, const int64_t* idx, void* dst, int64_t rows, int64_t row_bytes,
+                        void* stream);
+
+/* out[t, :] = bf16(sum_k weights[t,k] * y[pos[t,k], :]), fp32 accumulation: the combine-side
+ * weighted sum of a token's top-k expert outputs (baseline counterpart:
+ * grouped_gemm/csrc/permute.cu, moe_recover_topK_kernel).  y, out bf16 with `hidden` columns. */
+int b200moe_combine_topk(const void* y, const int64_t* pos, const float* weights, void* out, int64_t tokens, int top_k,
+                         int hidden, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

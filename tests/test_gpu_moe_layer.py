@@ -41,6 +41,27 @@ def test_swiglu_quant_matches_two_step_reference():
     assert O.rdiff(O.dequant_1x128(q2.cpu(), s2.cpu()), deq) < 2e-3
 
 
+def test_gather_and_combine_kernels_are_exact():
+    from triton_grouped_gemm_b200.ep.dispatch import combine, dispatch, make_plan
+
+    t, e, k, h = 513, 8, 4, 1024
+    idx, w = synthetic_routing(t, e, k, seed=5)
+    gen = torch.Generator().manual_seed(6)
+    x8 = torch.randn(t, h, generator=gen).to(torch.float8_e4m3fn)
+    xs = torch.rand(t, h // 128, generator=gen)
+    plan_c = make_plan(idx, e)
+    plan_g = make_plan(idx.to(DEV), e)
+    # gather of byte rows and of fp32 scale rows: identical to torch indexing on the host
+    assert torch.equal(dispatch(plan_g, x8.to(DEV)).cpu().view(torch.uint8), dispatch(plan_c, x8).view(torch.uint8))
+    assert torch.equal(dispatch(plan_g, xs.to(DEV)).cpu(), dispatch(plan_c, xs))
+    # weighted top-k sum: fp32 accumulation, one rounding -> agrees with the host formula to 1 bf16 ulp
+    y = torch.randn(t * k, h, generator=gen).bfloat16()
+    out_g = combine(plan_g, y.to(DEV), w.to(DEV)).cpu()
+    out_c = combine(plan_c, y, w)
+    assert O.rdiff(out_g.float(), out_c.float()) < 1e-3
+    assert (out_g.float() - out_c.float()).abs().max() <= 2 ** -7 * out_c.float().abs().max()
+
+
 @pytest.mark.parametrize("t,h,inter,e,k", [(96, 256, 128, 4, 2), (300, 512, 256, 8, 3)])
 def test_layer_single_rank_vs_oracle(t, h, inter, e, k):
     gen = torch.Generator().manual_seed(t + e)

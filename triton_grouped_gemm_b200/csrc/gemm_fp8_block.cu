@@ -258,10 +258,11 @@ fp8_block_m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
       unsigned long long acc2[64];
 #pragma unroll
       for (int j = 0; j < 64; ++j) acc2[j] = 0ull;
-      // Software pipeline over 32-column chunks: two tcgen05.ld are kept in flight (t0, t1)
-      // while the previous two chunks are multiplied in, so the TMEM read latency overlaps
-      // the FMAs; the first two chunks of k-block kb+1 are requested before the last FMAs of kb.
-      uint32_t t0[32], t1[32];
+      // Per k-block: 64 columns per tcgen05.ld (two loads cover this thread's 128 columns).  The
+      // loads are not interleaved with the FMAs of the same registers: a plain load / wait /
+      // multiply sequence measured faster than a finer software pipeline; the first load of
+      // k-block kb+1 is requested as soon as its buffer is full, before the loop comes around.
+      uint32_t t[64];
       const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + half * 128;
       // scale of k-block kb: a_scale[row, kb] * b_scale[g, nb, kb].  With staged scales the a
       // part comes from shared memory and the b part (uniform over the warp) from a register
@@ -284,8 +285,7 @@ fp8_block_m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
       float s_next = scale_of(0);
       if (!wait_bounded(tmem_full_bar(it & 1u), (it >> 1) & 1u, abort_flag, status, kDevTimeoutPromote)) break;
       tc_fence_after_sync();
-      tmem_ld_32x32b_x32(t_lane + (it & 1u) * kBlockN, t0);
-      tmem_ld_32x32b_x32(t_lane + (it & 1u) * kBlockN + 32, t1);
+      tmem_ld_32x32b_x64(t_lane + (it & 1u) * kBlockN, t);
       for (int kb = 0; kb < num_kb; ++kb, ++it) {
         const unsigned long long s2 = pack_f32x2(__float_as_uint(s_next), __float_as_uint(s_next));
         const bool more = kb + 1 < num_kb;
@@ -305,11 +305,8 @@ fp8_block_m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
         const uint32_t t_addr = t_lane + buf * kBlockN;
         tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < 16; ++j) fma_f32x2(acc2[j], s2, pack_f32x2(t0[2 * j], t0[2 * j + 1]));
-        tmem_ld_32x32b_x32(t_addr + 64, t0);
-#pragma unroll
-        for (int j = 0; j < 16; ++j) fma_f32x2(acc2[16 + j], s2, pack_f32x2(t1[2 * j], t1[2 * j + 1]));
-        tmem_ld_32x32b_x32(t_addr + 96, t1);
+        for (int j = 0; j < 32; ++j) fma_f32x2(acc2[j], s2, pack_f32x2(t[2 * j], t[2 * j + 1]));
+        tmem_ld_32x32b_x64(t_addr + 64, t);
         tmem_ld_wait();
         // every column of this buffer is in registers now: hand it back to the MMA warp
         tc_fence_before_sync();
@@ -319,7 +316,7 @@ fp8_block_m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
           else mbar_arrive(tmem_empty_bar(buf));
         }
 #pragma unroll
-        for (int j = 0; j < 16; ++j) fma_f32x2(acc2[32 + j], s2, pack_f32x2(t0[2 * j], t0[2 * j + 1]));
+        for (int j = 0; j < 32; ++j) fma_f32x2(acc2[32 + j], s2, pack_f32x2(t[2 * j], t[2 * j + 1]));
         if (more) {
           const uint32_t nit = it + 1;
           if (!wait_bounded(tmem_full_bar(nit & 1u), (nit >> 1) & 1u, abort_flag, status, kDevTimeoutPromote)) {
@@ -327,11 +324,8 @@ fp8_block_m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
             break;
           }
           tc_fence_after_sync();
-          tmem_ld_32x32b_x32(t_lane + (nit & 1u) * kBlockN, t0);
+          tmem_ld_32x32b_x64(t_lane + (nit & 1u) * kBlockN, t);
         }
-#pragma unroll
-        for (int j = 0; j < 16; ++j) fma_f32x2(acc2[48 + j], s2, pack_f32x2(t1[2 * j], t1[2 * j + 1]));
-        if (more) tmem_ld_32x32b_x32(t_lane + ((it + 1) & 1u) * kBlockN + 32, t1);
       }
       if (!ok) break;
       if (scales_by_tma) {

@@ -1,0 +1,115 @@
+// Row movement around the expert GEMMs of an MoE layer (HBM-bound, no arithmetic on the
+// gather side): gather rows into expert-major order for dispatch, and the router-weighted sum
+// of each token's top-k expert outputs for combine.  The reference ships equivalents only in
+// its vendored baseline extension (grouped_gemm/csrc/permute.cu:40-297); these are written for
+// sm_100a: 16-byte vector accesses, one warp per row, several rows in flight per warp.
+#include <cuda_bf16.h>
+
+#include "../../include/b200gemm.h"
+#include "common.cuh"
+
+namespace b200 {
+
+constexpr int kMoeThreads = 256;
+
+// dst[i, :] = src[idx[i], :] for i < rows; row_vecs = row bytes / 16
+__global__ void __launch_bounds__(kMoeThreads)
+gather_rows_kernel(const uint4* __restrict__ src, const long long* __restrict__ idx, uint4* __restrict__ dst,
+                   long long rows, int row_vecs) {
+  const int lane = threadIdx.x & 31;
+  const long long warp = (static_cast<long long>(blockIdx.x) * kMoeThreads + threadIdx.x) >> 5;
+  const long long warps = (static_cast<long long>(gridDim.x) * kMoeThreads) >> 5;
+  for (long long r = warp; r < rows; r += warps) {
+    const uint4* s = src + idx[r] * row_vecs;
+    uint4* d = dst + r * row_vecs;
+    int v = lane;
+    for (; v + 96 < row_vecs; v += 128) {  // four independent 16-byte loads in flight per lane
+      const uint4 a = __ldg(s + v), b = __ldg(s + v + 32), c = __ldg(s + v + 64), e = __ldg(s + v + 96);
+      d[v] = a;
+      d[v + 32] = b;
+      d[v + 64] = c;
+      d[v + 96] = e;
+    }
+    for (; v < row_vecs; v += 32) d[v] = __ldg(s + v);
+  }
+}
+
+// out[t, :] = bf16( sum_k w[t,k] * y[pos[t,k], :] ), fp32 accumulation in k order
+__global__ void __launch_bounds__(kMoeThreads)
+combine_topk_kernel(const uint4* __restrict__ y, const long long* __restrict__ pos, const float* __restrict__ w,
+                    uint4* __restrict__ out, long long tokens, int top_k, int row_vecs) {
+  const int lane = threadIdx.x & 31;
+  const long long warp = (static_cast<long long>(blockIdx.x) * kMoeThreads + threadIdx.x) >> 5;
+  const long long warps = (static_cast<long long>(gridDim.x) * kMoeThreads) >> 5;
+  for (long long t = warp; t < tokens; t += warps) {
+    for (int v = lane; v < row_vecs; v += 32) {
+      float acc[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+      for (int k = 0; k < top_k; ++k) {
+        const uint4 q = __ldg(y + pos[t * top_k + k] * row_vecs + v);
+        const float wk = w[t * top_k + k];
+        const uint32_t p[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          acc[2 * e] = fmaf(wk, __uint_as_float(p[e] << 16), acc[2 * e]);
+          acc[2 * e + 1] = fmaf(wk, __uint_as_float(p[e] & 0xFFFF0000u), acc[2 * e + 1]);
+        }
+      }
+      uint32_t o[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * e], acc[2 * e + 1]);
+        o[e] = *reinterpret_cast<uint32_t*>(&h);
+      }
+      out[t * row_vecs + v] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+  }
+}
+
+}  // namespace b200
+
+extern "C" {
+
+int b200moe_gather_rows(const void* src, const int64_t* idx, void* dst, int64_t rows, int64_t row_bytes,
+                        void* stream) {
+  using namespace b200;
+  B200_REQUIRE(rows >= 0 && row_bytes >= 0, "b200moe_gather_rows: negative size");
+  if (rows == 0 || row_bytes == 0) return 0;
+  B200_REQUIRE(src && idx && dst, "b200moe_gather_rows: null pointer");
+  B200_REQUIRE(row_bytes % 16 == 0 && row_bytes / 16 < (1ll << 30), "b200moe_gather_rows: row_bytes (%lld) must be a multiple of 16",
+               (long long)row_bytes);
+  B200_REQUIRE((reinterpret_cast<uintptr_t>(src) & 15) == 0 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0,
+               "b200moe_gather_rows: src and dst must be 16-byte aligned");
+  const int sms = sm_count();
+  B200_REQUIRE(sms > 0, "b200moe_gather_rows: no CUDA device");
+  long long blocks = (rows + kMoeThreads / 32 - 1) / (kMoeThreads / 32);
+  if (blocks > 16ll * sms) blocks = 16ll * sms;
+  gather_rows_kernel<<<static_cast<int>(blocks), kMoeThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(src), reinterpret_cast<const long long*>(idx), static_cast<uint4*>(dst), rows,
+      static_cast<int>(row_bytes / 16));
+  B200_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int b200moe_combine_topk(const void* y, const int64_t* pos, const float* weights, void* out, int64_t tokens, int top_k,
+                         int hidden, void* stream) {
+  using namespace b200;
+  B200_REQUIRE(tokens >= 0 && top_k > 0 && hidden >= 0, "b200moe_combine_topk: bad size");
+  if (tokens == 0 || hidden == 0) return 0;
+  B200_REQUIRE(y && pos && weights && out, "b200moe_combine_topk: null pointer");
+  B200_REQUIRE(hidden % 8 == 0, "b200moe_combine_topk: hidden (%d) must be a multiple of 8", hidden);
+  B200_REQUIRE((reinterpret_cast<uintptr_t>(y) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0,
+               "b200moe_combine_topk: y and out must be 16-byte aligned");
+  const int sms = sm_count();
+  B200_REQUIRE(sms > 0, "b200moe_combine_topk: no CUDA device");
+  long long blocks = (tokens + kMoeThreads / 32 - 1) / (kMoeThreads / 32);
+  if (blocks > 16ll * sms) blocks = 16ll * sms;
+  combine_topk_kernel<<<static_cast<int>(blocks), kMoeThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(y), reinterpret_cast<const long long*>(pos), weights, static_cast<uint4*>(out), tokens,
+      top_k, hidden / 8);
+  B200_CUDA(cudaGetLastError());
+  return 0;
+}
+
+}  // extern "C"

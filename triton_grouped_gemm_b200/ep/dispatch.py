@@ -36,6 +36,22 @@ class DispatchPlan:
         return int(sum(self.recv_splits))
 
 
+def _gather_rows(rows: torch.Tensor, idx: torch.Tensor) -> torch.Tensor:
+    """rows[idx] for 2-D rows; on CUDA through the library's gather kernel (no fallback needed on
+    CPU tensors: those are the gloo tests of the host logic)."""
+    if rows.is_cuda and rows.dim() == 2 and rows.is_contiguous() and (rows.shape[1] * rows.element_size()) % 16 == 0:
+        from .. import _lib
+
+        out = torch.empty((idx.numel(), rows.shape[1]), dtype=rows.dtype, device=rows.device)
+        idx64 = idx.to(torch.int64).contiguous()
+        with torch.cuda.device(rows.device):
+            rc = _lib.load().b200moe_gather_rows(rows.data_ptr(), idx64.data_ptr(), out.data_ptr(), idx64.numel(),
+                                                 rows.shape[1] * rows.element_size(), _lib.stream_ptr(rows.device))
+        _lib.check(rc, "b200moe_gather_rows")
+        return out
+    return rows[idx]
+
+
 def _all_to_all(out: torch.Tensor, inp: torch.Tensor, out_splits, in_splits, group) -> None:
     if group is None or dist.get_world_size(group) == 1:
         out.copy_(inp)
@@ -76,23 +92,42 @@ def make_plan(topk_idx: torch.Tensor, num_experts: int, group: Optional[dist.Pro
 def dispatch(plan: DispatchPlan, rows: torch.Tensor, group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
     """rows [T, ...] per token -> [R, ...] rows for this rank's experts, expert-major."""
     token_of_pair = plan.send_order // plan.top_k
-    send = rows[token_of_pair].contiguous()
-    flat = send.view(torch.uint8) if send.dtype in (torch.float8_e4m3fn, torch.float8_e5m2) else send
-    recv = torch.empty((plan.rows_received,) + tuple(flat.shape[1:]), dtype=flat.dtype, device=flat.device)
-    _all_to_all(recv, flat, plan.recv_splits, plan.send_splits, group)
-    out = recv[plan.recv_to_expert_major]
-    return out.view(rows.dtype) if flat.dtype != rows.dtype else out
+    src = rows.view(torch.uint8) if rows.dtype in (torch.float8_e4m3fn, torch.float8_e5m2) else rows
+    send = _gather_rows(src, token_of_pair)
+    if plan.world == 1:
+        out = send  # one rank: the send order already is expert-major
+    else:
+        recv = torch.empty((plan.rows_received,) + tuple(send.shape[1:]), dtype=send.dtype, device=send.device)
+        _all_to_all(recv, send, plan.recv_splits, plan.send_splits, group)
+        out = _gather_rows(recv, plan.recv_to_expert_major)
+    return out.view(rows.dtype) if src.dtype != rows.dtype else out
 
 
 def combine(plan: DispatchPlan, expert_rows: torch.Tensor, topk_weight: torch.Tensor,
             group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
     """expert_rows [R, H] (expert-major results) -> [T, H]: sum_k weight[t,k] * result(t,k)."""
-    back = torch.empty_like(expert_rows)
-    back[plan.recv_to_expert_major] = expert_rows                   # arrival order again
-    ret = torch.empty((plan.send_order.numel(), expert_rows.shape[1]), dtype=expert_rows.dtype,
-                      device=expert_rows.device)
-    _all_to_all(ret, back, plan.send_splits, plan.recv_splits, group)
-    pair_rows = torch.empty_like(ret)
-    pair_rows[plan.send_order] = ret                                 # (token, k) order
+    if plan.world == 1:
+        ret = expert_rows                                             # already in send order
+    else:
+        inv = torch.empty_like(plan.recv_to_expert_major)
+        inv[plan.recv_to_expert_major] = torch.arange(inv.numel(), device=inv.device)
+        back = _gather_rows(expert_rows, inv)                         # arrival order again
+        ret = torch.empty((plan.send_order.numel(), expert_rows.shape[1]), dtype=expert_rows.dtype,
+                          device=expert_rows.device)
+        _all_to_all(ret, back, plan.send_splits, plan.recv_splits, group)
+    # position of pair (t, k) among the returned rows
+    pos = torch.empty_like(plan.send_order)
+    pos[plan.send_order] = torch.arange(pos.numel(), device=pos.device)
+    if ret.is_cuda and ret.dtype == torch.bfloat16 and ret.shape[1] % 8 == 0:
+        from .. import _lib
+
+        out = torch.empty((plan.num_tokens, ret.shape[1]), dtype=ret.dtype, device=ret.device)
+        w32 = topk_weight.reshape(-1).to(torch.float32).contiguous()
+        with torch.cuda.device(ret.device):
+            rc = _lib.load().b200moe_combine_topk(ret.data_ptr(), pos.data_ptr(), w32.data_ptr(), out.data_ptr(),
+                                                  plan.num_tokens, plan.top_k, ret.shape[1], _lib.stream_ptr(ret.device))
+        _lib.check(rc, "b200moe_combine_topk")
+        return out
+    pair_rows = ret[pos]                                              # (token, k) order
     w = topk_weight.reshape(plan.num_tokens, plan.top_k, 1).to(torch.float32)
     return (pair_rows.view(plan.num_tokens, plan.top_k, -1).to(torch.float32) * w).sum(1).to(expert_rows.dtype)
