@@ -43,6 +43,8 @@ WORKLOADS = {
     "fp8_block_m_grouped_gate_up": ("fp8_block", 4096, 3072, True),
     "fp8_block_m_grouped_down": ("fp8_block", 1536, 4096, True),
     "quant_act_1x128": ("quant_act", 4096, 0, True),
+    # transposing 128x128 quantiser with per-expert expansion: input [rows, 4096] bf16
+    "quant_trans_expand_128x": ("quant_trans", 4096, 0, True),
     # expert-parallel FP8 MoE layer: K = hidden 4096, N = intermediate 1536, 128 experts, top-8,
     # --rows = routed rows per GPU (tokens per GPU = rows / 8); NCCL all-to-all dispatch + combine
     "moe_ep_fp8": ("moe_ep", 4096, 1536, True),
@@ -172,7 +174,7 @@ def make_inputs(kind, k, n, trans_b, sizes, device, seed):
         return {"a": randn((m, k), 0.02), "b": randn((m, n), 0.02)}
     if kind == "fp8_block":
         return {"x": randn((m, k), 1.0), "w": randn((g, n, k), 0.02, chunk_rows=4)}
-    if kind == "quant_act":
+    if kind in ("quant_act", "quant_trans"):
         return {"x": randn((m, k), 1.0)}
     if kind in ("moe_ep", "moe_decode"):
         # sizes = this rank's local-expert placeholder vector; k = hidden, n = intermediate
@@ -188,6 +190,9 @@ def algorithmic_work(kind, k, n, sizes):
         return 2.0 * rows * n * k, "flop"  # M_DIM=k, N_DIM=n, K_total=rows
     if kind == "quant_act":
         return rows * k * 3.0 + rows * (k // 128) * 4.0, "byte"
+    if kind == "quant_trans":
+        m_expand = rows + 128 * sizes.numel() - rows % 128
+        return rows * k * 2.0 + k * m_expand * 1.0 + (k // 128) * (m_expand // 128) * 4.0, "byte"
     if kind in ("moe_ep", "moe_decode"):
         # gate+up [2n x k] and down [k x n] GEMMs for every routed / valid row
         return 2.0 * rows * (2 * n * k + k * n), "flop"
@@ -225,6 +230,11 @@ def build_step(kind, k, n, trans_b, sizes_dev, inp):
 
         x = inp["x"]
         return (lambda: inp.__setitem__("c", per_token_cast_to_fp8(x))), 1
+    if kind == "quant_trans":
+        from triton_grouped_gemm_b200.quant.trans_per_block_quant_expand_128x import trans_per_block_quant_expand_128x
+
+        x = inp["x"]
+        return (lambda: inp.__setitem__("c", trans_per_block_quant_expand_128x(x, sizes_dev))), 1
     if kind in ("moe_ep", "moe_decode"):
         import torch.distributed as dist
 
@@ -290,6 +300,9 @@ def cpu_reference_step(kind, k, n, trans_b, sizes, budget_work, seed=7):
     elif kind == "quant_act":
         x = torch.randn(m, k, generator=gen).bfloat16()
         fn = lambda: O.per_token_cast_to_fp8(x)  # noqa: E731
+    elif kind == "quant_trans":
+        x = torch.randn(m, k, generator=gen).bfloat16()
+        fn = lambda: O.trans_quant_expand_ref(x, ps)  # noqa: E731
     elif kind in ("moe_ep", "moe_decode"):
         # the whole layer on a small token sample routed over 8 experts (fp32 loops on the host)
         tokens, e_s = 256, 8
@@ -310,7 +323,7 @@ def cpu_reference_step(kind, k, n, trans_b, sizes, budget_work, seed=7):
 
 
 def unit_of(kind):
-    return ("TFLOP/s", 1e12) if kind != "quant_act" else ("GB/s", 1e9)
+    return ("TFLOP/s", 1e12) if kind not in ("quant_act", "quant_trans") else ("GB/s", 1e9)
 
 
 def run_reference(args):
@@ -348,13 +361,14 @@ def metric_name(kind):
     return {"m_grouped": "grouped-GEMM TFLOP/s (BF16 M-grouped)", "k_grouped": "grouped-GEMM TFLOP/s (BF16 K-grouped)",
             "fp8_block": "grouped-GEMM TFLOP/s (FP8 block-scaled M-grouped)",
             "quant_act": "per-block quantiser GB/s (1x128 e4m3)",
+            "quant_trans": "per-block quantiser GB/s (transposing 128x128 e4m3 with expansion)",
             "moe_ep": "expert-parallel FP8 MoE layer, grouped-GEMM TFLOP/s incl. dispatch/combine",
             "moe_decode": "FP8 MoE decode (masked layout), grouped-GEMM TFLOP/s"}[kind]
 
 
 def dtype_name(kind):
     return {"m_grouped": "bf16", "k_grouped": "bf16", "fp8_block": "fp8_e4m3", "quant_act": "bf16->fp8_e4m3",
-            "moe_ep": "fp8_e4m3", "moe_decode": "fp8_e4m3"}[kind]
+            "quant_trans": "bf16->fp8_e4m3", "moe_ep": "fp8_e4m3", "moe_decode": "fp8_e4m3"}[kind]
 
 
 def config_of(name, kind, k, n, trans_b, sizes, gpus):
@@ -565,6 +579,20 @@ def run_e2e(args, kind, k, n, trans_b, sizes, inp, dev, use_dist, _unused, work)
         def one():
             d = {kk: v.to(dev, non_blocking=True) for kk, v in host.items()}
             out_host.copy_(layer.decode(d["x8"], d["xs"], d["s"], DECODE_M_MAX), non_blocking=True)
+    elif kind == "quant_trans":
+        from triton_grouped_gemm_b200.quant.trans_per_block_quant_expand_128x import trans_per_block_quant_expand_128x
+
+        host = {"x": inp["x"].cpu().pin_memory(), "s": sizes.pin_memory()}
+        q0, s0, _ = inp["c"]
+        out_host = torch.empty(q0.shape, dtype=torch.uint8).pin_memory()
+        s_host = torch.empty(s0.shape, dtype=torch.float32).pin_memory()
+
+        def one():
+            q, sc, _ = trans_per_block_quant_expand_128x(host["x"].to(dev, non_blocking=True),
+                                                         host["s"].to(dev, non_blocking=True))
+            out_host.copy_(q.view(torch.uint8), non_blocking=True)
+            s_host.copy_(sc, non_blocking=True)
+        host["_extra_out"] = s_host
     else:
         from triton_grouped_gemm_b200.quant.per_block_cast import per_token_cast_to_fp8
 

@@ -92,6 +92,20 @@ def test_trans_quant_vs_oracle(sizes, n):
         assert pad.cpu().tolist() == pad_ref.tolist()
 
 
+def test_trans_quant_large_random_is_bit_exact():
+    """4M elements with block magnitudes spread over 60 binades: every byte must match the host's
+    fp32 division + clamp + cast (the kernel divides with a reciprocal and one correction step)."""
+    gen = torch.Generator().manual_seed(77)
+    rows, n = 4096, 1024
+    x = torch.randn(rows, n, generator=gen)
+    mag = torch.exp2(torch.randint(-30, 30, (rows // 128, 1, n // 128, 1), generator=gen).float())
+    x = (x.view(rows // 128, 128, n // 128, 128) * mag).view(rows, n).bfloat16()
+    t = torch.tensor([1024, 0, 777, 2295])
+    q_ref, s_ref, _ = O.trans_quant_expand_ref(x, t)
+    q, s, _ = trans_per_block_quant_expand_128x(x.to(DEV), t.to(DEV))
+    _assert_same(q, s, q_ref, s_ref)
+
+
 def test_trans_quant_all_zero_block_gives_reference_nan_bytes():
     x = torch.randn(256, 128).to(torch.bfloat16)
     x[128:256] = 0  # second 128x128 block of the only expert is all zero -> scale 0, 0/0
