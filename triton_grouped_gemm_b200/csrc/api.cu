@@ -76,6 +76,13 @@ int encode_tmap(CUtensorMap* out, CUtensorMapDataType dtype, int rank, const voi
                 const uint64_t* strides_bytes, const uint32_t* box, CUtensorMapSwizzle swz, const char* what) {
   auto fn = get_encode_fn();
   if (!fn) return set_error(kErrDriverEntry, "cuTensorMapEncodeTiled is not available from this driver");
+  // The encode function is a raw driver call and needs a current context.  A host thread that has
+  // only inherited "the current device" (e.g. an autograd worker thread) may not have one bound
+  // yet; re-selecting the current device binds its primary context to this thread.
+  {
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaSetDevice(dev);
+  }
   cuuint64_t gdim[5];
   cuuint64_t gstr[5];
   cuuint32_t bdim[5];

@@ -1,0 +1,52 @@
+"""Differentiable grouped GEMM: forward and input gradient through the M-grouped kernel, weight
+gradient through the K-grouped kernel.
+
+The reference keeps forward (``m_grouped_gemm``) and weight gradient (``k_grouped_gemm``) as
+separate operators; its vendored baseline wraps the cuBLAS loop in an autograd function
+(grouped_gemm/grouped_gemm/ops.py:12-42).  This is the same wrapper over the B200 kernels:
+
+    trans_b=False, B [G, K, N]:  C = A B_g      dA = dC B_g^T (M-grouped, trans_b=True)
+                                 dB_g = A_g^T dC_g                (K-grouped) -> [G, K, N]
+    trans_b=True,  B [G, N, K]:  C = A B_g^T    dA = dC B_g   (M-grouped, trans_b=False)
+                                 dB_g = dC_g^T A_g                (K-grouped) -> [G, N, K]
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .BF16.k_grouped_gemm_TMA import k_grouped_gemm
+from .BF16.m_grouped_gemm_TMA import _m_grouped_gemm_launch
+
+
+class _GroupedGemm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, a, b, size_per_group, trans_b):
+        n = b.shape[1] if trans_b else b.shape[2]
+        c = a.new_empty(a.shape[0], n)
+        _m_grouped_gemm_launch(a.contiguous(), b.contiguous(), c, size_per_group, trans_b)
+        ctx.save_for_backward(a, b, size_per_group)
+        ctx.trans_b = trans_b
+        return c
+
+    @staticmethod
+    def backward(ctx, grad):
+        a, b, size_per_group = ctx.saved_tensors
+        grad = grad.contiguous()
+        da = db = None
+        if ctx.needs_input_grad[0]:
+            da = a.new_empty(a.shape)
+            _m_grouped_gemm_launch(grad, b.contiguous(), da, size_per_group, not ctx.trans_b)
+        if ctx.needs_input_grad[1]:
+            sizes = size_per_group if size_per_group.dtype in (torch.int32, torch.int64) else size_per_group.long()
+            if ctx.trans_b:
+                db = k_grouped_gemm(grad, a.contiguous(), sizes)   # [G, N, K]
+            else:
+                db = k_grouped_gemm(a.contiguous(), grad, sizes)   # [G, K, N]
+        return da, db, None, None
+
+
+def grouped_gemm(a: torch.Tensor, b: torch.Tensor, size_per_group: torch.Tensor, trans_b: bool = False):
+    """``C[rows of g] = a[rows of g] @ (b[g].T if trans_b else b[g])`` with gradients for a and b.
+    Rows of ``a`` beyond ``sum(size_per_group)`` get no output and no gradient (uninitialised)."""
+    return _GroupedGemm.apply(a, b, size_per_group, trans_b)
