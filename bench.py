@@ -528,18 +528,15 @@ def run_e2e(args, kind, k, n, trans_b, sizes, inp, dev, use_dist, _unused, work)
     """Host inputs (pinned) -> device -> operator -> host result, every step."""
     steps = max(1, min(args.steps, args.e2e_steps))
     if kind == "m_grouped":
-        from triton_grouped_gemm_b200.gemm.BF16.m_grouped_gemm_TMA import m_grouped_gemm
+        # the library's host-operand entry point: chunked H2D / GEMM / D2H pipeline on three streams
+        from triton_grouped_gemm_b200.host import m_grouped_gemm_host
 
         host = {"a": inp["a"].cpu().pin_memory(), "b": inp["b"].cpu().pin_memory(), "s": sizes.pin_memory()}
         out_host = torch.empty(inp["a"].shape[0], n, dtype=torch.bfloat16).pin_memory()
-        del inp["c"]
+        del inp["c"], inp["a"], inp["b"]
 
         def one():
-            a = host["a"].to(dev, non_blocking=True)
-            b = host["b"].to(dev, non_blocking=True)
-            s = host["s"].to(dev, non_blocking=True)
-            c = m_grouped_gemm(a, b, s, trans_b)
-            out_host.copy_(c, non_blocking=True)
+            m_grouped_gemm_host(host["a"], host["b"], host["s"], trans_b, out_host=out_host, device=dev)
     elif kind == "k_grouped":
         from triton_grouped_gemm_b200.gemm.BF16.k_grouped_gemm_TMA import k_grouped_gemm
 
