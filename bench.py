@@ -42,6 +42,11 @@ WORKLOADS = {
     "bf16_k_grouped_wgrad": ("k_grouped", 2048, 768, False),
     "fp8_block_m_grouped_gate_up": ("fp8_block", 4096, 3072, True),
     "fp8_block_m_grouped_down": ("fp8_block", 1536, 4096, True),
+    # FP8 with per-row x per-channel scales (e4m3 x e4m3), M-grouped and K-grouped (tokens padded to 128)
+    "fp8_rowcol_m_grouped": ("fp8_rowcol", 4096, 3072, True),
+    "fp8_rowcol_k_grouped": ("fp8_rowcol_k", 2048, 768, False),
+    # masked layout: 128 slots of 4096 rows, ~1/4 of them valid (the reference's masked benchmark)
+    "bf16_masked_m_grouped": ("masked", 2048, 1536, True),
     "quant_act_1x128": ("quant_act", 4096, 0, True),
     # transposing 128x128 quantiser with per-expert expansion: input [rows, 4096] bf16
     "quant_trans_expand_128x": ("quant_trans", 4096, 0, True),
@@ -74,7 +79,7 @@ def measured_peaks():
 class ClockSampler:
     """Samples nvidia-smi SM clocks and throttle reasons while the timed region runs."""
 
-    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+    QUERY = ("timestamp,index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
@@ -88,7 +93,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except Exception:
             self.proc = None
             return
@@ -99,7 +104,9 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.lines.append(line.strip())
 
-    def stop(self):
+    def stop(self, t_begin=None, t_end=None):
+        """Summarise the samples; with wall-clock bounds only those taken inside the timed region
+        (if there are any) are used for the median clock and the throttle reasons."""
         if not self.proc:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -107,22 +114,27 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except Exception:
             self.proc.kill()
-        clocks, maxes, reasons = [], [], set()
+        import datetime
+
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        rows = []
         for ln in self.lines:
             parts = [p.strip() for p in ln.split(",")]
-            if len(parts) < 9:
+            if len(parts) < 10:
                 continue
             try:
-                clocks.append(float(parts[1]))
-                maxes.append(float(parts[2]))
+                ts = datetime.datetime.strptime(parts[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                rows.append((ts, float(parts[2]), float(parts[3]), float(parts[4]),
+                             [n for n, v in zip(names, parts[6:10]) if v.lower().startswith("active")]))
             except ValueError:
                 continue
-            for name, val in zip(names, parts[5:9]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        return {"sm_mhz": statistics.median(clocks) if clocks else None,
-                "sm_max_mhz": max(maxes) if maxes else None, "reasons": sorted(reasons), "samples": len(clocks)}
+        inside = [r for r in rows if t_begin is not None and t_begin - 0.02 <= r[0] <= t_end + 0.02]
+        use = inside or rows
+        reasons = sorted({n for r in use for n in r[4]})
+        return {"sm_mhz": statistics.median([r[1] for r in use]) if use else None,
+                "sm_max_mhz": max([r[2] for r in use]) if use else None,
+                "power_w": statistics.median([r[3] for r in use]) if use else None,
+                "reasons": reasons, "samples": len(use), "samples_in_timed_region": len(inside)}
 
 
 def dist_env():
@@ -176,6 +188,20 @@ def make_inputs(kind, k, n, trans_b, sizes, device, seed):
         return {"x": randn((m, k), 1.0), "w": randn((g, n, k), 0.02, chunk_rows=4)}
     if kind in ("quant_act", "quant_trans"):
         return {"x": randn((m, k), 1.0)}
+    if kind == "fp8_rowcol":
+        a8 = (randn((m, k), 100.0).float().clamp(-400, 400)).to(torch.float8_e4m3fn)
+        b8 = (randn((g, n, k), 100.0, chunk_rows=4).float().clamp(-400, 400)).to(torch.float8_e4m3fn)
+        return {"a8": a8, "a_s": torch.rand(m, device=device, generator=gen) * 0.01 + 1e-3, "b8": b8,
+                "b_s": torch.rand(g * n, device=device, generator=gen) * 0.01 + 1e-3}
+    if kind == "fp8_rowcol_k":
+        # x [M=k, K_total], y [N=n, K_total]; scales group-major [G, M] / [G, N]
+        x8 = (randn((k, m), 50.0, chunk_rows=256).float().clamp(-400, 400)).to(torch.float8_e4m3fn)
+        y8 = (randn((n, m), 50.0, chunk_rows=256).float().clamp(-400, 400)).to(torch.float8_e4m3fn)
+        return {"x8": x8, "y8": y8, "xs": (torch.rand(g, k, device=device, generator=gen) * 0.01 + 1e-3).t(),
+                "ys": (torch.rand(g, n, device=device, generator=gen) * 0.01 + 1e-3).t()}
+    if kind == "masked":
+        e = 4096
+        return {"a": randn((g * e, k), 0.02), "b": randn((g, n, k), 0.02, chunk_rows=8)}
     if kind in ("moe_ep", "moe_decode"):
         # sizes = this rank's local-expert placeholder vector; k = hidden, n = intermediate
         return {"w13": randn((g, 2 * n, k), 0.02, chunk_rows=2), "w2": randn((g, k, n), 0.02, chunk_rows=2)}
@@ -184,7 +210,7 @@ def make_inputs(kind, k, n, trans_b, sizes, device, seed):
 
 def algorithmic_work(kind, k, n, sizes):
     rows = int(sizes.sum())
-    if kind in ("m_grouped", "fp8_block"):
+    if kind in ("m_grouped", "fp8_block", "fp8_rowcol", "fp8_rowcol_k", "masked"):
         return 2.0 * rows * n * k, "flop"
     if kind == "k_grouped":
         return 2.0 * rows * n * k, "flop"  # M_DIM=k, N_DIM=n, K_total=rows
@@ -230,6 +256,25 @@ def build_step(kind, k, n, trans_b, sizes_dev, inp):
 
         x = inp["x"]
         return (lambda: inp.__setitem__("c", per_token_cast_to_fp8(x))), 1
+    if kind == "fp8_rowcol":
+        from triton_grouped_gemm_b200.gemm.FP8.m_grouped_gemm_channel_expert import gmm_fp8_act_per_channel_w_per_expert as op
+
+        a8, a_s, b8, b_s = inp["a8"], inp["a_s"], inp["b8"], inp["b_s"]
+        s32 = sizes_dev.to(torch.int32)
+        return (lambda: inp.__setitem__("c", op(a8, a_s, b8, b_s, s32, torch.bfloat16))), 1
+    if kind == "fp8_rowcol_k":
+        from triton_grouped_gemm_b200.gemm.FP8.k_grouped_gemm_channel_expert import matmul
+
+        x8, y8, xs, ys = inp["x8"], inp["y8"], inp["xs"], inp["ys"]
+        s32 = sizes_dev.to(torch.int32)
+        return (lambda: inp.__setitem__("c", matmul(x8, xs, y8, ys, s32, k, n, x8.shape[1], s32.numel()))), 1
+    if kind == "masked":
+        from triton_grouped_gemm_b200.gemm.BF16.m_grouped_gemm_masked_TMA import m_grouped_gemm_masked
+
+        a, b = inp["a"], inp["b"]
+        out = torch.empty(a.shape[0], n, device=a.device, dtype=a.dtype)
+        inp["c"] = out
+        return (lambda: m_grouped_gemm_masked(a, b, out, sizes_dev, 4096, True)), 1
     if kind == "quant_trans":
         from triton_grouped_gemm_b200.quant.trans_per_block_quant_expand_128x import trans_per_block_quant_expand_128x
 
@@ -360,6 +405,9 @@ def run_reference(args):
 def metric_name(kind):
     return {"m_grouped": "grouped-GEMM TFLOP/s (BF16 M-grouped)", "k_grouped": "grouped-GEMM TFLOP/s (BF16 K-grouped)",
             "fp8_block": "grouped-GEMM TFLOP/s (FP8 block-scaled M-grouped)",
+            "fp8_rowcol": "grouped-GEMM TFLOP/s (FP8 row x channel scales, M-grouped)",
+            "fp8_rowcol_k": "grouped-GEMM TFLOP/s (FP8 row x channel scales, K-grouped)",
+            "masked": "grouped-GEMM TFLOP/s (BF16 masked M-grouped)",
             "quant_act": "per-block quantiser GB/s (1x128 e4m3)",
             "quant_trans": "per-block quantiser GB/s (transposing 128x128 e4m3 with expansion)",
             "moe_ep": "expert-parallel FP8 MoE layer, grouped-GEMM TFLOP/s incl. dispatch/combine",
@@ -367,7 +415,8 @@ def metric_name(kind):
 
 
 def dtype_name(kind):
-    return {"m_grouped": "bf16", "k_grouped": "bf16", "fp8_block": "fp8_e4m3", "quant_act": "bf16->fp8_e4m3",
+    return {"m_grouped": "bf16", "k_grouped": "bf16", "fp8_block": "fp8_e4m3", "fp8_rowcol": "fp8_e4m3",
+            "fp8_rowcol_k": "fp8_e4m3", "masked": "bf16", "quant_act": "bf16->fp8_e4m3",
             "quant_trans": "bf16->fp8_e4m3", "moe_ep": "fp8_e4m3", "moe_decode": "fp8_e4m3"}[kind]
 
 
@@ -400,6 +449,10 @@ def run_b200(args):
     kind, k, n, trans_b = WORKLOADS[args.workload]
     sizes = (moe_sizes(kind, world, rank, args.rows) if kind in ("moe_ep", "moe_decode")
              else rank_sizes(world, rank, args.rows, args.experts))
+    if kind == "masked":  # valid rows per 4096-row slot, ~1/4 full, every fifth slot empty
+        gen_m = torch.Generator().manual_seed(ROUTING_SEED + rank)
+        sizes = torch.randint(0, 2049, (sizes.numel(),), generator=gen_m, dtype=torch.int64)
+        sizes[::5] = 0
     sizes_dev = sizes.to(dev)
     inp = make_inputs(kind, k, n, trans_b, sizes, dev, seed=100 + rank)
     step, launches = build_step(kind, k, n, trans_b, sizes_dev, inp)
@@ -424,6 +477,7 @@ def run_b200(args):
     # ---- device-timed region: exactly `steps` steps, one CUDA event pair per step
     evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
     barrier()
+    t_epoch_begin = time.time()
     t_wall = time.perf_counter()
     for s_ev, e_ev in evs:
         s_ev.record()
@@ -433,7 +487,7 @@ def run_b200(args):
     t_wall = time.perf_counter() - t_wall
     per_step = [s.elapsed_time(e) for s, e in evs]
     total_ms = evs[0][0].elapsed_time(evs[-1][1])
-    clocks = sampler.stop() if sampler else None
+    clocks = sampler.stop(t_epoch_begin, t_epoch_begin + t_wall) if sampler else None
     status = _lib.device_status()
     if status:
         raise RuntimeError(f"device status word = {status:#x} (a bounded wait ran out)")
@@ -475,7 +529,7 @@ def run_b200(args):
         # a multi-kernel step (MoE layer) is judged as a whole: flops of its GEMMs over the step time
         launch_ms = statistics.mean(per_step) / (1 if kind in ("moe_ep", "moe_decode") else launches)
         if unit == "TFLOP/s":
-            fp8 = kind in ("fp8_block", "moe_ep", "moe_decode")
+            fp8 = kind in ("fp8_block", "moe_ep", "moe_decode", "fp8_rowcol", "fp8_rowcol_k")
             peak = peaks["bf16"] * (2.0 if fp8 else 1.0)
             achieved = work / (launch_ms * 1e-3) / 1e12
             # DRAM bytes per launch from the ncu capture of the 82 560-row case of this kernel
