@@ -93,14 +93,35 @@ def test_trans_quant_vs_oracle(sizes, n):
 
 
 def test_trans_quant_large_random_is_bit_exact():
-    """4M elements with block magnitudes spread over 60 binades: every byte must match the host's
-    fp32 division + clamp + cast (the kernel divides with a reciprocal and one correction step)."""
+    """32M elements with block magnitudes spread over 60 binades: every byte must match the host's
+    fp32 division + clamp + cast.  The kernel brackets each quotient between two directed-rounding
+    products and only divides where the bracket straddles an e4m3 rounding boundary; at this size
+    about a hundred elements take that route."""
     gen = torch.Generator().manual_seed(77)
-    rows, n = 4096, 1024
+    rows, n = 16384, 2048
     x = torch.randn(rows, n, generator=gen)
     mag = torch.exp2(torch.randint(-30, 30, (rows // 128, 1, n // 128, 1), generator=gen).float())
     x = (x.view(rows // 128, 128, n // 128, 128) * mag).view(rows, n).bfloat16()
-    t = torch.tensor([1024, 0, 777, 2295])
+    t = torch.tensor([1024, 0, 777, 2295 + 12288])
+    q_ref, s_ref, _ = O.trans_quant_expand_ref(x, t)
+    q, s, _ = trans_per_block_quant_expand_128x(x.to(DEV), t.to(DEV))
+    _assert_same(q, s, q_ref, s_ref)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_trans_quant_extreme_blocks_and_signed_zeros(dtype):
+    """Blocks whose scale is tiny, huge or subnormal, exact e4m3 ties, and negative zeros."""
+    gen = torch.Generator().manual_seed(5)
+    rows, n = 1024, 512
+    x = torch.randn(rows, n, generator=gen)
+    lo, hi = (-125, 121) if dtype == torch.bfloat16 else (-22, 13)
+    mag = torch.exp2(torch.randint(lo, hi, (rows // 128, 1, n // 128, 1), generator=gen).float())
+    x = (x.view(rows // 128, 128, n // 128, 128) * mag).view(rows, n).to(dtype)
+    # one block with scale exactly 1 and values on e4m3 rounding ties
+    x[:128, :128] = torch.tensor([1.0625, -1.1875, 0.0009765625, 17.0, -0.0, 0.0, 448.0, -26.0]).repeat(128, 16).to(dtype)
+    x[128:256, 128:256][::2] = -0.0
+    assert torch.isfinite(x.float()).all()
+    t = torch.tensor([300, 724])
     q_ref, s_ref, _ = O.trans_quant_expand_ref(x, t)
     q, s, _ = trans_per_block_quant_expand_128x(x.to(DEV), t.to(DEV))
     _assert_same(q, s, q_ref, s_ref)

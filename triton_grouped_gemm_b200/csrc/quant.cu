@@ -237,11 +237,82 @@ quant_w_128x128_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ q, 
 // 0/0 = NaN bytes exactly like the torch code on the host (0xff).
 constexpr int kTqPitch = 132;  // bytes per staged row: 33 words -> conflict-free column reads
 
+// Largest |x| of eight 16-bit floats as raw bits (sign cleared).  For bf16 and fp16 alike the
+// magnitude order of non-NaN values is the unsigned order of these bits, and every NaN pattern
+// sorts above infinity, so one integer maximum also tells whether a NaN or Inf was present.
+__device__ __forceinline__ uint32_t abs_bits_max8(const uint4& v, uint32_t m) {
+  constexpr uint32_t kAbs = 0x7FFF7FFFu;
+  m = __vimax3_u16x2(m, v.x & kAbs, v.y & kAbs);
+  return __vimax3_u16x2(m, v.z & kAbs, v.w & kAbs);
+}
+
+// Slow, always-exact form of one 8-element chunk: IEEE division per element.
+// torch.clamp propagates NaN; the host's 0/0 is the negative quiet NaN -> byte 0xff.
+__device__ __noinline__ uint2 trans_quant_chunk_exact(uint4 v, float scale, int is_fp16) {
+  const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
+  uint32_t out[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    float f[4];
+    f[0] = to_f32(static_cast<uint16_t>(wv[2 * h] & 0xFFFFu), is_fp16);
+    f[1] = to_f32(static_cast<uint16_t>(wv[2 * h] >> 16), is_fp16);
+    f[2] = to_f32(static_cast<uint16_t>(wv[2 * h + 1] & 0xFFFFu), is_fp16);
+    f[3] = to_f32(static_cast<uint16_t>(wv[2 * h + 1] >> 16), is_fp16);
+    uint32_t b[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float d = __fdiv_rn(f[i], scale);
+      b[i] = (d != d) ? 0xFFu : (cvt_e4m3x2(fminf(fmaxf(d, -448.0f), 448.0f), 0.f) & 0xFFu);
+    }
+    out[h] = b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24);
+  }
+  return make_uint2(out[0], out[1]);
+}
+
+// Fast form of one chunk, used when the block's scale and reciprocals are normal numbers and
+// the block holds no NaN/Inf.  With rd <= 1/scale <= ru (directed-rounding reciprocals),
+//   lo = RD(|x| * rd)  <=  RN(|x| / scale)  <=  RU(|x| * ru) = hi,
+// and clamping and the e4m3 conversion are monotonic and odd, so when lo and hi convert to
+// the same byte that byte (with x's sign) is the reference's.  An e4m3 rounding boundary
+// falls between lo and hi for a few elements per million; `mismatch` reports those and the
+// caller redoes the chunk with the exact division.
+template <bool kFp16>
+__device__ __forceinline__ uint2 trans_quant_chunk_fast(const uint4& v, float rd, float ru, uint32_t& mismatch) {
+  const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
+  uint32_t out[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    float a[4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const uint32_t w = wv[2 * h + i] & 0x7FFF7FFFu;
+      if (kFp16) {
+        const float2 t = __half22float2(*reinterpret_cast<const __half2*>(&w));
+        a[2 * i] = t.x;
+        a[2 * i + 1] = t.y;
+      } else {
+        a[2 * i] = __uint_as_float(w << 16);
+        a[2 * i + 1] = __uint_as_float(w & 0xFFFF0000u);
+      }
+    }
+    const uint32_t lo = cvt_e4m3x2(__fmul_rd(a[0], rd), __fmul_rd(a[1], rd)) |
+                        (cvt_e4m3x2(__fmul_rd(a[2], rd), __fmul_rd(a[3], rd)) << 16);
+    const uint32_t hi = cvt_e4m3x2(__fmul_ru(a[0], ru), __fmul_ru(a[1], ru)) |
+                        (cvt_e4m3x2(__fmul_ru(a[2], ru), __fmul_ru(a[3], ru)) << 16);
+    mismatch |= lo ^ hi;
+    // sign bits: byte i of the result takes bit 15 / 31 of the 16-bit inputs
+    const uint32_t signs = __byte_perm(wv[2 * h], wv[2 * h + 1], 0x7531) & 0x80808080u;
+    out[h] = lo | signs;
+  }
+  return make_uint2(out[0], out[1]);
+}
+
+template <bool kFp16>
 __global__ void __launch_bounds__(kBlkThreads)
 quant_trans_expand_kernel(const uint16_t* __restrict__ x, const void* __restrict__ sizes, int sizes_i64,
                           int num_groups, uint8_t* __restrict__ q, float* __restrict__ s,
-                          long long* __restrict__ padded_sizes_out, int n, long long m_expand, int is_fp16) {
-  __shared__ float red[kBlkThreads / 32];
+                          long long* __restrict__ padded_sizes_out, int n, long long m_expand) {
+  __shared__ uint32_t red[kBlkThreads / 32];
   __shared__ __align__(16) uint8_t stage[128 * kTqPitch];
   const int n_tiles = n / 128;
   const int m_tiles_total = static_cast<int>(m_expand / 128);
@@ -250,6 +321,7 @@ quant_trans_expand_kernel(const uint16_t* __restrict__ x, const void* __restrict
   const int tc = (threadIdx.x & 15) * 8;
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  constexpr uint32_t kInfBits = kFp16 ? 0x7C00u : 0x7F80u;
 
   if (padded_sizes_out && blockIdx.x == 0) {
     for (int g = threadIdx.x; g < num_groups; g += kBlkThreads) {
@@ -281,40 +353,61 @@ quant_trans_expand_kernel(const uint16_t* __restrict__ x, const void* __restrict
     const long long row0 = w.tile_row0(mt);
     const long long row_end = w.group_row_end();
     uint4 v[8];
-    float amax = 0.f;
+    uint32_t mx2 = 0;
 #pragma unroll
     for (int p = 0; p < 8; ++p) {
       const long long r = row0 + p * 16 + tr;
       v[p] = (r < row_end) ? __ldg(reinterpret_cast<const uint4*>(x + r * n + nt * 128 + tc)) : make_uint4(0, 0, 0, 0);
-      amax = fmaxf(amax, abs_max8(v[p], is_fp16));
+      mx2 = abs_bits_max8(v[p], mx2);
     }
-    amax = block_max_256(amax, red);
-    const float scale = __fdiv_rn(amax, 448.0f);
-    if (threadIdx.x == 0) s[static_cast<long long>(nt) * scale_cols + mt] = scale;
-    // quantise, stage as bytes [local row][column]
+    // block maximum of the raw magnitude bits
+    uint32_t mx = __reduce_max_sync(0xFFFFFFFFu, max(mx2 & 0xFFFFu, mx2 >> 16));
+    __syncthreads();  // protects `red` and `stage` against the previous tile
+    if (lane == 0) red[warp] = mx;
+    __syncthreads();
+    mx = red[0];
 #pragma unroll
-    for (int p = 0; p < 8; ++p) {
-      const uint32_t wv[4] = {v[p].x, v[p].y, v[p].z, v[p].w};
-      uint32_t out[2];
+    for (int i = 1; i < kBlkThreads / 32; ++i) mx = max(mx, red[i]);
+
+    uint32_t* dst0 = reinterpret_cast<uint32_t*>(stage + tr * kTqPitch + tc);
+    const float amax_fast = to_f32(static_cast<uint16_t>(mx), kFp16);
+    // fast block: no NaN/Inf anywhere, scale and its reciprocals comfortably normal
+    if (mx < kInfBits && amax_fast >= 0x1p-100f && amax_fast <= 0x1p100f) {
+      const float scale = __fdiv_rn(amax_fast, 448.0f);
+      if (threadIdx.x == 0) s[static_cast<long long>(nt) * scale_cols + mt] = scale;
+      const float rd = __frcp_rd(scale), ru = __frcp_ru(scale);
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        float f[4];
-        f[0] = to_f32(static_cast<uint16_t>(wv[2 * h] & 0xFFFFu), is_fp16);
-        f[1] = to_f32(static_cast<uint16_t>(wv[2 * h] >> 16), is_fp16);
-        f[2] = to_f32(static_cast<uint16_t>(wv[2 * h + 1] & 0xFFFFu), is_fp16);
-        f[3] = to_f32(static_cast<uint16_t>(wv[2 * h + 1] >> 16), is_fp16);
-        uint32_t b[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float d = __fdiv_rn(f[i], scale);
-          // torch.clamp propagates NaN; the host's 0/0 is the negative quiet NaN -> byte 0xff
-          b[i] = (d != d) ? 0xFFu : (cvt_e4m3x2(fminf(fmaxf(d, -448.0f), 448.0f), 0.f) & 0xFFu);
-        }
-        out[h] = b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24);
+      for (int p = 0; p < 8; ++p) {
+        uint32_t mismatch = 0;
+        uint2 o = trans_quant_chunk_fast<kFp16>(v[p], rd, ru, mismatch);
+        if (mismatch) o = trans_quant_chunk_exact(v[p], scale, kFp16);
+        uint32_t* dst = dst0 + p * 16 * (kTqPitch / 4);
+        dst[0] = o.x;
+        dst[1] = o.y;
       }
-      uint32_t* dst = reinterpret_cast<uint32_t*>(stage + (p * 16 + tr) * kTqPitch + tc);
-      dst[0] = out[0];
-      dst[1] = out[1];
+    } else {
+      // NaN/Inf in the block, an all-zero block or an extreme scale: per-element IEEE division
+      // with the fp32 maximum taken by fmaxf
+      float amax = 0.f;
+#pragma unroll
+      for (int p = 0; p < 8; ++p) amax = fmaxf(amax, abs_max8(v[p], kFp16));
+#pragma unroll
+      for (int o = 16; o >= 1; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+      __shared__ float redf[kBlkThreads / 32];
+      if (lane == 0) redf[warp] = amax;
+      __syncthreads();
+      amax = redf[0];
+#pragma unroll
+      for (int i = 1; i < kBlkThreads / 32; ++i) amax = fmaxf(amax, redf[i]);
+      const float scale = __fdiv_rn(amax, 448.0f);
+      if (threadIdx.x == 0) s[static_cast<long long>(nt) * scale_cols + mt] = scale;
+#pragma unroll
+      for (int p = 0; p < 8; ++p) {
+        const uint2 o = trans_quant_chunk_exact(v[p], scale, kFp16);
+        uint32_t* dst = dst0 + p * 16 * (kTqPitch / 4);
+        dst[0] = o.x;
+        dst[1] = o.y;
+      }
     }
     __syncthreads();
     // transposed write-out: lane (a = lane%8, b = lane/8) gathers a 4x4 byte block
@@ -345,7 +438,6 @@ quant_trans_expand_kernel(const uint16_t* __restrict__ x, const void* __restrict
       *reinterpret_cast<uint32_t*>(o + 2 * m_expand) = c2;
       *reinterpret_cast<uint32_t*>(o + 3 * m_expand) = c3;
     }
-    __syncthreads();
   }
 }
 
@@ -426,9 +518,14 @@ int b200quant_trans_expand_128x(const void* x, const void* sizes, int sizes_is_i
   B200_REQUIRE(m_expand / 128 < (1ll << 30), "b200quant_trans_expand_128x: m_expand too large");
   const long long tiles = (m_expand / 128) * (n / 128);
   const int grid = grid_for(tiles, 4);
-  quant_trans_expand_kernel<<<grid, kBlkThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const uint16_t*>(x), sizes, sizes_is_i64, num_groups, static_cast<uint8_t*>(q), scales,
-      reinterpret_cast<long long*>(padded_sizes_out), n, m_expand, dtype);
+  if (dtype == 1)
+    quant_trans_expand_kernel<true><<<grid, kBlkThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint16_t*>(x), sizes, sizes_is_i64, num_groups, static_cast<uint8_t*>(q), scales,
+        reinterpret_cast<long long*>(padded_sizes_out), n, m_expand);
+  else
+    quant_trans_expand_kernel<false><<<grid, kBlkThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint16_t*>(x), sizes, sizes_is_i64, num_groups, static_cast<uint8_t*>(q), scales,
+        reinterpret_cast<long long*>(padded_sizes_out), n, m_expand);
   B200_CUDA(cudaGetLastError());
   return 0;
 }
