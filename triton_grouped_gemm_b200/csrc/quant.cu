@@ -269,40 +269,43 @@ __device__ __noinline__ uint2 trans_quant_chunk_exact(uint4 v, float scale, int 
   return make_uint2(out[0], out[1]);
 }
 
-// Fast form of one chunk, used when the block's scale and reciprocals are normal numbers and
-// the block holds no NaN/Inf.  With rd <= 1/scale <= ru (directed-rounding reciprocals),
-//   lo = RD(|x| * rd)  <=  RN(|x| / scale)  <=  RU(|x| * ru) = hi,
-// and clamping and the e4m3 conversion are monotonic and odd, so when lo and hi convert to
-// the same byte that byte (with x's sign) is the reference's.  An e4m3 rounding boundary
-// falls between lo and hi for a few elements per million; `mismatch` reports those and the
-// caller redoes the chunk with the exact division.
+// Fast form of one chunk, used when the block holds no NaN/Inf and its scale is far from the
+// ends of the fp32 range.  With r = RN(1/scale) computed once per block,
+//   q0 = RN(x * r),  e = RN(x - scale * q0),  q1 = RN(q0 + e * r)      (two fused multiply-adds)
+// is the correctly rounded quotient RN(x / scale): checked exhaustively on the host for every
+// pair of 8-bit (bf16) and 11-bit (fp16) significands of x and of the block maximum that
+// `scale = RN(amax / 448)` derives from (tests/test_trans_quant_division.py); rounding
+// depends on the significands only while nothing underflows, which the caller's range check
+// guarantees for every quotient that does not convert to zero anyway.  The saturating
+// conversion then equals the reference's clamp + cast.
 template <bool kFp16>
-__device__ __forceinline__ uint2 trans_quant_chunk_fast(const uint4& v, float rd, float ru, uint32_t& mismatch) {
+__device__ __forceinline__ uint2 trans_quant_chunk_fast(const uint4& v, float scale, float r) {
   const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
+  const float neg_scale = -scale;
   uint32_t out[2];
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
-    float a[4];
+    float q[4];
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
-      const uint32_t w = wv[2 * h + i] & 0x7FFF7FFFu;
+      const uint32_t w = wv[2 * h + i];
+      float x0, x1;
       if (kFp16) {
         const float2 t = __half22float2(*reinterpret_cast<const __half2*>(&w));
-        a[2 * i] = t.x;
-        a[2 * i + 1] = t.y;
+        x0 = t.x;
+        x1 = t.y;
       } else {
-        a[2 * i] = __uint_as_float(w << 16);
-        a[2 * i + 1] = __uint_as_float(w & 0xFFFF0000u);
+        x0 = __uint_as_float(w << 16);
+        x1 = __uint_as_float(w & 0xFFFF0000u);
       }
+      const float a0 = __fmul_rn(x0, r), a1 = __fmul_rn(x1, r);
+      q[2 * i] = __fmaf_rn(__fmaf_rn(neg_scale, a0, x0), r, a0);
+      q[2 * i + 1] = __fmaf_rn(__fmaf_rn(neg_scale, a1, x1), r, a1);
     }
-    const uint32_t lo = cvt_e4m3x2(__fmul_rd(a[0], rd), __fmul_rd(a[1], rd)) |
-                        (cvt_e4m3x2(__fmul_rd(a[2], rd), __fmul_rd(a[3], rd)) << 16);
-    const uint32_t hi = cvt_e4m3x2(__fmul_ru(a[0], ru), __fmul_ru(a[1], ru)) |
-                        (cvt_e4m3x2(__fmul_ru(a[2], ru), __fmul_ru(a[3], ru)) << 16);
-    mismatch |= lo ^ hi;
-    // sign bits: byte i of the result takes bit 15 / 31 of the 16-bit inputs
+    // x = -0 gives q1 = +0 (the residual of a negative zero is +0); the reference keeps the sign,
+    // so take every byte's sign bit from x (bit 15 / 31 of the 16-bit inputs; a no-op otherwise)
     const uint32_t signs = __byte_perm(wv[2 * h], wv[2 * h + 1], 0x7531) & 0x80808080u;
-    out[h] = lo | signs;
+    out[h] = cvt_e4m3x2(q[0], q[1]) | (cvt_e4m3x2(q[2], q[3]) << 16) | signs;
   }
   return make_uint2(out[0], out[1]);
 }
@@ -371,16 +374,14 @@ quant_trans_expand_kernel(const uint16_t* __restrict__ x, const void* __restrict
 
     uint32_t* dst0 = reinterpret_cast<uint32_t*>(stage + tr * kTqPitch + tc);
     const float amax_fast = to_f32(static_cast<uint16_t>(mx), kFp16);
-    // fast block: no NaN/Inf anywhere, scale and its reciprocals comfortably normal
-    if (mx < kInfBits && amax_fast >= 0x1p-100f && amax_fast <= 0x1p100f) {
+    // fast block: no NaN/Inf anywhere, scale and its reciprocal far from the ends of the range
+    if (mx < kInfBits && amax_fast >= 0x1p-60f && amax_fast <= 0x1p100f) {
       const float scale = __fdiv_rn(amax_fast, 448.0f);
       if (threadIdx.x == 0) s[static_cast<long long>(nt) * scale_cols + mt] = scale;
-      const float rd = __frcp_rd(scale), ru = __frcp_ru(scale);
+      const float r = __frcp_rn(scale);
 #pragma unroll
       for (int p = 0; p < 8; ++p) {
-        uint32_t mismatch = 0;
-        uint2 o = trans_quant_chunk_fast<kFp16>(v[p], rd, ru, mismatch);
-        if (mismatch) o = trans_quant_chunk_exact(v[p], scale, kFp16);
+        const uint2 o = trans_quant_chunk_fast<kFp16>(v[p], scale, r);
         uint32_t* dst = dst0 + p * 16 * (kTqPitch / 4);
         dst[0] = o.x;
         dst[1] = o.y;
