@@ -235,10 +235,20 @@ fp8_block_m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
     // this thread's row inside a staged scale tile: 128 bytes per row, 16-byte chunks XOR-ed
     // with (row % 8) by the 128-byte swizzle
     const int srow = quarter * 32 + lane;
-    const uint8_t* scale_tiles = smem + L::kScaleOffset + srow * 128;
+    const uint32_t scale_tiles = smem_base + L::kScaleOffset + srow * 128;
+    // volatile: the load must be issued where it is written (a k-block ahead of its use), not
+    // sunk to the use, where its latency would sit on the promotion warps' critical path
     auto staged_a_scale = [&](uint32_t sb, int kbl) -> float {
-      return *reinterpret_cast<const float*>(scale_tiles + sb * L::kScaleTileBytes +
-                                             ((((kbl >> 2) ^ (srow & 7)) << 4) | ((kbl & 3) << 2)));
+      float v;
+      asm volatile("ld.shared.f32 %0, [%1];"
+                   : "=f"(v)
+                   : "r"(scale_tiles + sb * L::kScaleTileBytes + ((((kbl >> 2) ^ (srow & 7)) << 4) | ((kbl & 3) << 2))));
+      return v;
+    };
+    auto bcast_lane = [&](float v, int src) -> float {
+      float r;
+      asm volatile("shfl.sync.idx.b32 %0, %1, %2, 0x1f, 0xffffffff;" : "=f"(r) : "f"(v), "r"(src));
+      return r;
     };
     bool ok = true;
     for (int tile = first_tile; ok; tile += tile_step) {
@@ -277,33 +287,40 @@ fp8_block_m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
         ++scale_it;
         return true;
       };
-      auto scale_of = [&](int kb) -> float {
-        if (scales_by_tma) return staged_a_scale(sb, kb & 31) * __shfl_sync(0xFFFFFFFFu, bs_reg, kb & 31);
-        return __ldg(as_row + kb) * __ldg(bs_blk + kb);
+      // the two factors of k-block kb's scale; multiplied when the k-block is reached
+      auto scale_parts = [&](int kb, float& fa, float& fb) {
+        if (scales_by_tma) {
+          fa = staged_a_scale(sb, kb & 31);
+          fb = bcast_lane(bs_reg, kb & 31);
+        } else {
+          fa = __ldg(as_row + kb);
+          fb = __ldg(bs_blk + kb);
+        }
       };
       if (scales_by_tma && !begin_segment(0)) break;
-      float s_next = scale_of(0);
+      float fa_next, fb_next;
+      scale_parts(0, fa_next, fb_next);
       if (!wait_bounded(tmem_full_bar(it & 1u), (it >> 1) & 1u, abort_flag, status, kDevTimeoutPromote)) break;
       tc_fence_after_sync();
       tmem_ld_32x32b_x64(t_lane + (it & 1u) * kBlockN, t);
       for (int kb = 0; kb < num_kb; ++kb, ++it) {
-        const unsigned long long s2 = pack_f32x2(__float_as_uint(s_next), __float_as_uint(s_next));
+        const float s_cur = fa_next * fb_next;
+        const unsigned long long s2 = pack_f32x2(__float_as_uint(s_cur), __float_as_uint(s_cur));
         const bool more = kb + 1 < num_kb;
-        if (more) {
-          if (scales_by_tma && ((kb + 1) & 31) == 0) {
-            // last use of this scale tile is behind us: hand it back, move to the next one
-            __syncwarp();
-            if (lane == 0) mbar_arrive(scale_empty_bar(sb));
-            if (!begin_segment(kb + 1)) {
-              ok = false;
-              break;
-            }
+        if (more && scales_by_tma && ((kb + 1) & 31) == 0) {
+          // last use of this scale tile is behind us: hand it back, move to the next one
+          __syncwarp();
+          if (lane == 0) mbar_arrive(scale_empty_bar(sb));
+          if (!begin_segment(kb + 1)) {
+            ok = false;
+            break;
           }
-          s_next = scale_of(kb + 1);
         }
         const uint32_t buf = it & 1u;
         const uint32_t t_addr = t_lane + buf * kBlockN;
         tmem_ld_wait();
+        // request the next k-block's scale factors now; this k-block's FMAs cover their latency
+        if (more) scale_parts(kb + 1, fa_next, fb_next);
 #pragma unroll
         for (int j = 0; j < 32; ++j) fma_f32x2(acc2[j], s2, pack_f32x2(t[2 * j], t[2 * j + 1]));
         tmem_ld_32x32b_x64(t_addr + 64, t);
