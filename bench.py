@@ -342,6 +342,22 @@ def cpu_reference_step(kind, k, n, trans_b, sizes, budget_work, seed=7):
         b8 = torch.stack([q for q, _ in qs])
         b_s = torch.stack([s for _, s in qs])
         fn = lambda: O.fp8_block_m_grouped_ref(a8, a_s, b8, b_s, ps)  # noqa: E731
+    elif kind == "fp8_rowcol":
+        a8 = (torch.randn(m, k, generator=gen) * 100).clamp(-400, 400).to(torch.float8_e4m3fn)
+        b8 = (torch.randn(g, n, k, generator=gen) * 100).clamp(-400, 400).to(torch.float8_e4m3fn)
+        a_s, b_s = torch.rand(m, generator=gen) * 0.01 + 1e-3, torch.rand(g * n, generator=gen) * 0.01 + 1e-3
+        fn = lambda: O.fp8_rowcol_m_grouped_ref(a8, a_s, b8, b_s, ps, torch.bfloat16)  # noqa: E731
+    elif kind == "fp8_rowcol_k":
+        x8 = (torch.randn(k, m, generator=gen) * 50).clamp(-400, 400).to(torch.float8_e4m3fn)
+        y8 = (torch.randn(n, m, generator=gen) * 50).clamp(-400, 400).to(torch.float8_e4m3fn)
+        xs, ys = (torch.rand(g, k, generator=gen) * 0.01 + 1e-3).t(), (torch.rand(g, n, generator=gen) * 0.01 + 1e-3).t()
+        fn = lambda: O.fp8_rowcol_k_grouped_ref(x8, xs, y8, ys, ps, k, n, g)  # noqa: E731
+    elif kind == "masked":
+        e = 4096
+        a = (torch.randn(g * e, k, generator=gen) * 0.02).bfloat16()
+        b = (torch.randn(g, n, k, generator=gen) * 0.02).bfloat16()
+        out0 = torch.zeros(g * e, n, dtype=torch.bfloat16)
+        fn = lambda: O.m_grouped_masked_ref(a, b, out0, ps, e)  # noqa: E731
     elif kind == "quant_act":
         x = torch.randn(m, k, generator=gen).bfloat16()
         fn = lambda: O.per_token_cast_to_fp8(x)  # noqa: E731
@@ -614,6 +630,25 @@ def run_e2e(args, kind, k, n, trans_b, sizes, inp, dev, use_dist, _unused, work)
             d = {kk: v.to(dev, non_blocking=True) for kk, v in host.items()}
             c = m_grouped_fp8_block_scaled((d["a8"], d["a_s"]), (d["b8"], d["b_s"]), d["s"])
             out_host.copy_(c, non_blocking=True)
+    elif kind in ("fp8_rowcol", "fp8_rowcol_k", "masked"):
+        # generic: every operand from pinned host memory, the operator, the result back to the host
+        names = [kk for kk, v in inp.items() if isinstance(v, torch.Tensor) and kk != "c"]
+        # scale matrices of the K-grouped workload are transposed views of group-major memory
+        transposed = {kk for kk in names if not inp[kk].is_contiguous()}
+        host = {kk: (inp[kk].t().contiguous() if kk in transposed else inp[kk]).cpu().pin_memory() for kk in names}
+        host["s"] = sizes.pin_memory()
+        out_host = torch.empty(inp["c"].shape, dtype=inp["c"].dtype).pin_memory()
+        for kk in names + ["c"]:
+            del inp[kk]
+
+        def one():
+            d = {}
+            for kk in names:
+                t = host[kk].to(dev, non_blocking=True)
+                d[kk] = t.t() if kk in transposed else t
+            fn, _ = build_step(kind, k, n, trans_b, host["s"].to(dev, non_blocking=True), d)
+            fn()
+            out_host.copy_(d["c"], non_blocking=True)
     elif kind == "moe_ep":
         layer = inp["layer"]
         host = {"x": inp["x"].cpu().pin_memory(), "idx": inp["idx"].cpu().pin_memory(), "w": inp["w"].cpu().pin_memory()}
