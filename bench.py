@@ -470,6 +470,10 @@ def run_b200(args):
         sizes = torch.randint(0, 2049, (sizes.numel(),), generator=gen_m, dtype=torch.int64)
         sizes[::5] = 0
     sizes_dev = sizes.to(dev)
+    if args.cta_pair != -1:
+        from triton_grouped_gemm_b200 import _lib
+
+        _lib.load().b200gemm_set_cta_pair(args.cta_pair)
     inp = make_inputs(kind, k, n, trans_b, sizes, dev, seed=100 + rank)
     step, launches = build_step(kind, k, n, trans_b, sizes_dev, inp)
     work, _ = algorithmic_work(kind, k, n, sizes)
@@ -722,6 +726,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--rows", type=int, default=TOTAL_ROWS, help="routed rows per GPU (default: the benchmark's 655360)")
     ap.add_argument("--experts", type=int, default=NUM_EXPERTS, help="experts over all GPUs (default 128)")
+    ap.add_argument("--cta-pair", type=int, default=-1, choices=[-1, 0, 1],
+                    help="kernel form: -1 chosen by problem size (default), 0 single-CTA tiles, 1 CTA pairs")
     ap.add_argument("--profile", action="store_true",
                     help="for ncu captures: honour --warmup as given, skip the host-buffer and CPU legs")
     args = ap.parse_args()

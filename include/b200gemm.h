@@ -50,9 +50,10 @@ int b200gemm_sm_count(void);
 /* Tuning override for the 16-bit M-grouped kernels: 0 = pick the tile width (64 / 128 / 256
  * output columns) from the problem size, otherwise force that width.  Process-wide. */
 int b200gemm_set_block_n(int block_n);
-/* Tuning override: the M-grouped kernels exist in a single-CTA form (128-row tiles) and a
- * CTA-pair form (two SMs share a 256 x 256 tile).  -1 = choose by problem size, 0 = never use
- * the pair form, 1 = use it whenever it is implemented for the call.  Process-wide. */
+/* Tuning override: the M-grouped kernels, and the K-grouped kernels when they run with a
+ * workspace, exist in a single-CTA form (128-row tiles) and a CTA-pair form (two SMs share a
+ * 256 x 256 tile).  -1 = choose by problem size, 0 = never use the pair form, 1 = use it
+ * whenever it is implemented for the call.  Process-wide. */
 int b200gemm_set_cta_pair(int mode);
 /* Number of CTAs (2 per cluster) a persistent launch of the CTA-pair kernel keeps resident on
  * the current device; 0 if it cannot be determined. */

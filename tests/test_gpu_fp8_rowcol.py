@@ -87,9 +87,12 @@ def test_m_grouped_rowcol_reference_test_shape_family():
     assert (out.float() - full).abs().max() / full.abs().max() < 0.1
 
 
+@pytest.mark.parametrize("pair", [-1, 1, 0], ids=["auto", "pair", "single"])
 @pytest.mark.parametrize("dt_a,dt_b", [(E4, E4), (E5, E4)])
-@pytest.mark.parametrize("tokens,m,n", [([128], 128, 256), ([256, 0, 128, 512], 256, 384), ([128, 128], 136, 72)])
-def test_k_grouped_rowcol(tokens, m, n, dt_a, dt_b):
+@pytest.mark.parametrize("tokens,m,n", [([128], 128, 256), ([256, 0, 128, 512], 256, 384), ([128, 128], 136, 72),
+                                        ([1024, 128, 0, 384, 2048], 512, 768)])
+def test_k_grouped_rowcol(tokens, m, n, dt_a, dt_b, pair):
+    _lib.load().b200gemm_set_cta_pair(pair)
     gen = torch.Generator().manual_seed(m + n + len(tokens))
     g, k_tot = len(tokens), sum(tokens)
     x8 = (torch.randn(m, k_tot, generator=gen) * 50).to(dt_a)

@@ -14,9 +14,13 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 
-@pytest.fixture(autouse=True)
-def _status_clean():
+@pytest.fixture(autouse=True, params=[-1, 1, 0], ids=["auto", "pair", "single"])
+def _kernel_form(request):
+    """Every case runs with the tile form chosen by size, with CTA pairs (256 x 256 tiles, used
+    whenever the call has a workspace) forced, and with them switched off."""
+    _lib.load().b200gemm_set_cta_pair(request.param)
     yield
+    _lib.load().b200gemm_set_cta_pair(-1)
     assert _lib.device_status() == 0
 
 

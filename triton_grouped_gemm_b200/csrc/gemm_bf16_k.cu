@@ -18,8 +18,11 @@
 // kernel runs BALANCED: a one-block plan kernel writes, per group, the first token row, the
 // token count and the groups' order by decreasing token count, and zeroes a tile counter;
 // the producer warp of every CTA then claims tiles with atomicAdd in that order (long tiles
-// first) and hands each claimed tile id to the CTA's other warps through a small shared-memory
-// ring.  Without scratch (workspace == NULL) tiles are assigned round-robin.
+// first) and hands each claimed tile - id, group, token count, first token row - to the CTA's
+// other warps through a small shared-memory ring, so that only the producer pays the latency of
+// the atomic and of the plan look-ups, and it pays it one tile ahead, in steps spread over the
+// k-blocks of the tile it is loading.  Without scratch (workspace == NULL) tiles are assigned
+// round-robin.
 #include <mutex>
 
 #include "../../include/b200gemm.h"
@@ -37,7 +40,7 @@ struct KGroupedSmem {
   static constexpr int kBarOffset = kEpiOffset + 4 * kEpiStageBytesPerWarp;
   static constexpr int kSchedDepth = 4;                     // tile-id ring of the balanced scheduler
   static constexpr int kNumBars = 2 * kStages + 4 + 2 * kSchedDepth;
-  static constexpr int kTotal = kBarOffset + kNumBars * 8 + 16 + kSchedDepth * 4;
+  static constexpr int kTotal = kBarOffset + kNumBars * 8 + 16 + kSchedDepth * 16;  // ring of int4 entries
   static constexpr int kDynamicBytes = kTotal + 1024;
 };
 
@@ -79,7 +82,6 @@ struct TokenRange {
 };
 
 // Scratch layout (int32 words): [0] tile counter, [1..63] unused, then starts[G], tokens[G], order[G].
-constexpr int kPlanHeaderWords = 64;
 __host__ __device__ inline long long k_grouped_scratch_words(int num_groups) {
   return kPlanHeaderWords + 3ll * num_groups;
 }
@@ -147,7 +149,7 @@ k_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kBarOffset + L::kNumBars * 8 + 4);
   auto sched_full_bar = [&](int i) { return bar_base + 8u * (2 * kStages + 4 + i); };
   auto sched_empty_bar = [&](int i) { return bar_base + 8u * (2 * kStages + 4 + L::kSchedDepth + i); };
-  volatile int* sched_tile = reinterpret_cast<volatile int*>(smem + L::kBarOffset + L::kNumBars * 8 + 16);
+  volatile int4* sched_info = reinterpret_cast<volatile int4*>(smem + L::kBarOffset + L::kNumBars * 8 + 16);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -187,33 +189,47 @@ k_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_holder;
 
-  // tile -> (group, m tile, n tile): n fastest, so CTAs running side by side share A chunks.
+  // tile -> (group slot, m tile, n tile): n fastest, so CTAs running side by side share A chunks.
   // Balanced mode visits the groups in the plan's order (most tokens first).
   const int* plan_starts = scratch + kPlanHeaderWords;
   const int* plan_tokens = plan_starts + num_groups;
   const int* plan_order = plan_tokens + num_groups;
-  auto decode = [&](long long tile, int& g, int& mt, int& nt) {
-    const int slot = static_cast<int>(tile / tiles_per_group);
+  struct TileInfo {
+    long long tile;  // -1: no more work (or a wait ran out)
+    int g;
+    long long tokens, start;
+  };
+  auto split_tile = [&](long long tile, int& slot, int& mt, int& nt) {
+    slot = static_cast<int>(tile / tiles_per_group);
     const int local = static_cast<int>(tile - static_cast<long long>(slot) * tiles_per_group);
-    g = kBalanced ? plan_order[slot] : slot;
     mt = local / n_tiles;
     nt = local - mt * n_tiles;
   };
-  // i-th tile of this CTA for a consumer role (MMA / epilogue): static round-robin, or the id the
-  // producer warp claimed and published in the ring.  Returns -1 when there is no more work or a
-  // wait ran out.
-  auto consumer_tile = [&](uint32_t i, unsigned role_bit) -> long long {
+  // i-th tile of this CTA for a consumer role (MMA / epilogue): static round-robin with the
+  // role's own running prefix over the sizes, or the entry the producer warp published.
+  auto consumer_tile = [&](uint32_t i, unsigned role_bit, TokenRange& tr) -> TileInfo {
+    TileInfo ti;
     if constexpr (!kBalanced) {
       const long long t = blockIdx.x + static_cast<long long>(i) * gridDim.x;
-      return t < num_tiles ? t : -1;
+      ti.tile = t < num_tiles ? t : -1;
+      if (ti.tile >= 0) {
+        ti.g = static_cast<int>(t / tiles_per_group);
+        ti.tokens = tr.seek(ti.g);
+        ti.start = tr.start;
+      }
     } else {
       const int slot = i % L::kSchedDepth;
-      if (!wait_bounded(sched_full_bar(slot), (i / L::kSchedDepth) & 1u, abort_flag, status, role_bit)) return -1;
-      const int t = sched_tile[slot];
+      ti.tile = -1;
+      if (!wait_bounded(sched_full_bar(slot), (i / L::kSchedDepth) & 1u, abort_flag, status, role_bit)) return ti;
+      const int t = sched_info[slot].x;
+      ti.g = sched_info[slot].y;
+      ti.tokens = sched_info[slot].z;
+      ti.start = sched_info[slot].w;
       __syncwarp();
       if (lane == 0) mbar_arrive(sched_empty_bar(slot));
-      return t < num_tiles ? t : -1;
+      ti.tile = t < num_tiles ? t : -1;
     }
+    return ti;
   };
 
   if (warp == 0) {
@@ -223,34 +239,58 @@ k_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
+    // Balanced mode: the claim of the next tile (an atomic, ~1 us) and its two dependent plan
+    // look-ups are issued one step per k-block while this tile's loads stream, with volatile
+    // instructions so that each sits where it is written and its latency passes before the
+    // following step needs the result.
+    int nx_t = 0, nx_slot = 0, nx_g = 0, nx_tokens = 0, nx_start = 0, nx_step = 3;
+    auto prefetch_step = [&]() {
+      if (nx_step == 0) {
+        if (lane == 0) asm volatile("atom.global.add.u32 %0, [%1], 1;" : "=r"(nx_t) : "l"(scratch) : "memory");
+      } else if (nx_step == 1) {
+        nx_t = __shfl_sync(0xFFFFFFFFu, nx_t, 0);
+        nx_slot = static_cast<int>(nx_t / tiles_per_group);
+        if (nx_t < num_tiles) asm volatile("ld.global.nc.s32 %0, [%1];" : "=r"(nx_g) : "l"(plan_order + nx_slot));
+      } else if (nx_step == 2) {
+        if (nx_t < num_tiles) {
+          asm volatile("ld.global.nc.s32 %0, [%1];" : "=r"(nx_tokens) : "l"(plan_tokens + nx_g));
+          asm volatile("ld.global.nc.s32 %0, [%1];" : "=r"(nx_start) : "l"(plan_starts + nx_g));
+        }
+      }
+      ++nx_step;
+    };
+    if constexpr (kBalanced) nx_step = 0;
     for (uint32_t i = 0; ok; ++i) {
       long long tile;
+      int g, mt, nt;
+      long long tokens;
       if constexpr (kBalanced) {
-        // claim the next tile and publish its id (also the end marker) to the other warps
-        int t = 0;
-        if (lane == 0) t = atomicAdd(scratch, 1);
-        t = __shfl_sync(0xFFFFFFFFu, t, 0);
+        while (nx_step < 3) prefetch_step();  // first tile, or a tile with fewer than three k-blocks
+        // publish the claimed tile (also the end marker) to the other warps
         const int slot = i % L::kSchedDepth;
         if (!wait_bounded(sched_empty_bar(slot), ((i / L::kSchedDepth) & 1u) ^ 1u, abort_flag, status,
                           kDevTimeoutProducer))
           break;
         if (lane == 0) {
-          sched_tile[slot] = t;
+          sched_info[slot].x = nx_t;
+          sched_info[slot].y = nx_g;
+          sched_info[slot].z = nx_tokens;
+          sched_info[slot].w = nx_start;
           mbar_arrive(sched_full_bar(slot));
         }
         __syncwarp();
-        tile = t;
+        tile = nx_t;
+        if (tile >= num_tiles) break;
+        int slot_g;
+        split_tile(tile, slot_g, mt, nt);
+        g = nx_g;
+        tokens = nx_tokens;
+        tr.start = nx_start;
+        nx_step = 0;
       } else {
         tile = blockIdx.x + static_cast<long long>(i) * gridDim.x;
-      }
-      if (tile >= num_tiles) break;
-      int g, mt, nt;
-      decode(tile, g, mt, nt);
-      long long tokens;
-      if constexpr (kBalanced) {
-        tr.start = plan_starts[g];
-        tokens = plan_tokens[g];
-      } else {
+        if (tile >= num_tiles) break;
+        split_tile(tile, g, mt, nt);
         tokens = tr.seek(g);
       }
       const int num_kb = static_cast<int>((tokens + kTokensPerKb - 1) / kTokensPerKb);
@@ -277,6 +317,9 @@ k_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           }
         }
         __syncwarp();
+        if constexpr (kBalanced) {
+          if (nx_step < 3) prefetch_step();
+        }
         if (++stage == kStages) {
           stage = 0;
           phase ^= 1u;
@@ -296,11 +339,9 @@ k_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     uint32_t tile_iter = 0;  // counts non-empty tiles only (same rule in the epilogue)
     bool ok = true;
     for (uint32_t i = 0; ok; ++i) {
-      const long long tile = consumer_tile(i, kDevTimeoutMma);
-      if (tile < 0) break;
-      int g, mt, nt;
-      decode(tile, g, mt, nt);
-      const long long tokens = kBalanced ? static_cast<long long>(plan_tokens[g]) : tr.seek(g);
+      const TileInfo ti = consumer_tile(i, kDevTimeoutMma, tr);
+      if (ti.tile < 0) break;
+      const long long tokens = ti.tokens;
       if (tokens == 0) continue;
       const int num_kb = static_cast<int>((tokens + kTokensPerKb - 1) / kTokensPerKb);
       const uint32_t acc = tile_iter & 1u;
@@ -367,11 +408,12 @@ k_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     int epi_sel = 0;
     uint32_t tile_iter = 0;
     for (uint32_t i = 0;; ++i) {
-      const long long tile = consumer_tile(i, kDevTimeoutEpilogue);
-      if (tile < 0) break;
-      int g, mt, nt;
-      decode(tile, g, mt, nt);
-      const long long tokens = kBalanced ? static_cast<long long>(plan_tokens[g]) : tr.seek(g);
+      const TileInfo ti = consumer_tile(i, kDevTimeoutEpilogue, tr);
+      if (ti.tile < 0) break;
+      int slot_g, mt, nt;
+      split_tile(ti.tile, slot_g, mt, nt);
+      const int g = ti.g;
+      const long long tokens = ti.tokens;
       const int row = mt * kBlockM + quarter * 32 + lane;
       const bool row_ok = row < m_dim;
       uint16_t* c_row = static_cast<uint16_t*>(c_ptr) +
@@ -460,6 +502,22 @@ static int check_scratch(void* workspace, long long workspace_bytes, int num_gro
   return 0;
 }
 
+// CTA pairs (256 x 256 tiles, gemm_k_pair.cu) need the balanced scheduler's scratch and enough
+// tiles for every pair of SMs; the tuning knob can force them on or off
+static bool want_k_pair(const int* scratch, int num_groups, int m_dim, int n_dim, int grid) {
+  if (!scratch || grid < 2 || g_cta_pair_mode == 0) return false;
+  if (g_cta_pair_mode == 1) return true;
+  const long long tiles = static_cast<long long>(num_groups) * ((m_dim + 255) / 256) * ((n_dim + 255) / 256);
+  return m_dim >= 256 && n_dim >= 256 && tiles >= grid;
+}
+
+static int launch_plan(const void* sizes, int sizes_is_i64, const int* gs, const int* ge, int num_groups, int* scratch,
+                       cudaStream_t stream) {
+  k_grouped_plan_kernel<<<1, 1024, 0, stream>>>(sizes, sizes_is_i64, gs, ge, num_groups, scratch);
+  B200_CUDA(cudaGetLastError());
+  return 0;
+}
+
 // tile width: 256 output columns unless that leaves SMs without a tile
 static int pick_block_n(int num_groups, int m_dim, int n_dim, int grid) {
   const long long m_tiles = static_cast<long long>(num_groups) * ((m_dim + 127) / 128);
@@ -527,6 +585,12 @@ static int k_grouped_bf16(const void* a, const void* b, void* c, const void* siz
     if (rc) return rc;
   }
   const int in_fmt = dtype == 1 ? 0 : 1;  // UMMA kind::f16 operand format: 0 = f16, 1 = bf16
+  if (want_k_pair(scratch, num_groups, m_dim, n_dim, grid)) {
+    int rc = launch_plan(sizes, sizes_is_i64, group_start, group_end, num_groups, scratch, stream);
+    if (rc) return rc;
+    return launch_k_grouped_pair<false>(tm_a, tm_b, tm_c, c, num_groups, m_dim, n_dim, in_fmt, dtype, nullptr, nullptr,
+                                        scratch, grid, stream);
+  }
   const int bn = pick_block_n(num_groups, m_dim, n_dim, grid);
 #define B200_LAUNCH_K(BN, ST)                                                                                     \
   launch_k_grouped<BN, ST, false>(tm_a, tm_b, tm_c, c, sizes, sizes_is_i64, group_start, group_end, num_groups, m_dim,  \
@@ -577,7 +641,8 @@ extern "C" int b200gemm_fp8_k_grouped_rowcol(const void* x, const float* x_scale
   const int sms = sm_count();
   B200_REQUIRE(sms > 0, "%s: no CUDA device", who);
   const int grid = (num_sms > 0 && num_sms < sms) ? num_sms : sms;
-  const int bn = pick_block_n(num_groups, m_dim, n_dim, grid);
+  const bool pair = want_k_pair(scratch, num_groups, m_dim, n_dim, grid);
+  const int bn = pair ? 128 : pick_block_n(num_groups, m_dim, n_dim, grid);  // pair: 128 rows of Y per CTA
   CUtensorMap tm_x, tm_y;
   {
     const uint64_t dims[2] = {static_cast<uint64_t>(k_total), static_cast<uint64_t>(m_dim)};
@@ -605,6 +670,12 @@ extern "C" int b200gemm_fp8_k_grouped_rowcol(const void* x, const float* x_scale
     if (rc) return rc;
   }
   const int in_fmt = fmt_x | (fmt_y << 4);
+  if (pair) {
+    int rc = launch_plan(tokens_per_expert, sizes_is_i64, nullptr, nullptr, num_groups, scratch, stream);
+    if (rc) return rc;
+    return launch_k_grouped_pair<true>(tm_x, tm_y, tm_c, out, num_groups, m_dim, n_dim, in_fmt, /*out bf16*/ 0, x_scale,
+                                       y_scale, scratch, grid, stream);
+  }
 #define B200_LAUNCH_K8(BN, ST)                                                                                  \
   launch_k_grouped<BN, ST, true>(tm_x, tm_y, tm_c, out, tokens_per_expert, sizes_is_i64, nullptr, nullptr, num_groups, \
                                  m_dim, n_dim, k_total, in_fmt, /*out bf16*/ 0, x_scale, y_scale, scratch, grid, stream)

@@ -137,6 +137,17 @@ int launch_m_grouped_pair(const CUtensorMap& tm_a, const CUtensorMap& tm_b, cons
                           const void* sizes, int sizes_is_i64, int num_groups, int masked_stride, int n, int k,
                           int in_fmt, int out_fp16, const float* a_scale, const float* b_scale, int want_ctas,
                           cudaStream_t stream);
+// Scratch of the balanced K-grouped scheduler (int32 words): [0] tile counter, [1..63] unused,
+// then starts[G], tokens[G], order[G] (written by the plan kernel in gemm_bf16_k.cu).
+constexpr int kPlanHeaderWords = 64;
+
+// CTA-pair variant of the balanced K-grouped kernels, 256 x 256 tiles (gemm_k_pair.cu).  The plan
+// kernel must already be queued on `stream`.  16-bit: tm_a / tm_b 64 x 64 boxes over
+// [K_TOTAL, M_DIM] / [K_TOTAL, N_DIM]; fp8: 128-byte x 128-row boxes over [M, K_TOTAL] / [N, K_TOTAL].
+template <bool kFp8>
+int launch_k_grouped_pair(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const CUtensorMap& tm_c, void* c,
+                          int num_groups, int m_dim, int n_dim, int in_fmt, int out_fp16, const float* a_scale,
+                          const float* b_scale, int* scratch, int want_ctas, cudaStream_t stream);
 // -1 = use the pair kernel when the problem is large enough, 0 = never, 1 = whenever possible
 extern int g_cta_pair_mode;
 int pair_kernel_grid();

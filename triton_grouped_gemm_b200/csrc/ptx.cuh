@@ -56,6 +56,29 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar, uint32_t cta_r
       : "memory");
 }
 
+// same, with cluster-scope release: orders this thread's earlier writes (including stores to the
+// peer's shared memory) before the arrival; for the few arrivals per tile that publish data
+__device__ __forceinline__ void mbar_arrive_cluster_release(uint32_t bar, uint32_t cta_rank) {
+  asm volatile(
+      "{\n\t"
+      ".reg .b32 remote;\n\t"
+      "mapa.shared::cluster.u32 remote, %0, %1;\n\t"
+      "mbarrier.arrive.release.cluster.shared::cluster.b64 _, [remote];\n\t"
+      "}" ::"r"(bar), "r"(cta_rank)
+      : "memory");
+}
+
+// 16-byte store into the same-offset shared-memory location of CTA `cta_rank` of the cluster
+__device__ __forceinline__ void st_shared_cluster_v4(uint32_t addr, uint32_t cta_rank, int x, int y, int z, int w) {
+  asm volatile(
+      "{\n\t"
+      ".reg .b32 remote;\n\t"
+      "mapa.shared::cluster.u32 remote, %0, %1;\n\t"
+      "st.shared::cluster.v4.s32 [remote], {%2, %3, %4, %5};\n\t"
+      "}" ::"r"(addr), "r"(cta_rank), "r"(x), "r"(y), "r"(z), "r"(w)
+      : "memory");
+}
+
 // shared::cluster address of `addr` (a shared::cta address of this CTA) in CTA `cta_rank`
 __device__ __forceinline__ uint32_t mapa_u32(uint32_t addr, uint32_t cta_rank) {
   uint32_t r;
