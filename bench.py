@@ -225,6 +225,9 @@ def algorithmic_work(kind, k, n, sizes):
     raise ValueError(kind)
 
 
+EP_CHUNKS = 4  # set from --ep-chunks
+
+
 def build_step(kind, k, n, trans_b, sizes_dev, inp):
     """Returns (fn, launches_per_step).  fn() runs one step on the current stream."""
     import triton_grouped_gemm_b200 as pkg  # noqa: F401
@@ -290,7 +293,8 @@ def build_step(kind, k, n, trans_b, sizes_dev, inp):
         world = dist.get_world_size() if dist.is_initialized() else 1
         rank = dist.get_rank() if dist.is_initialized() else 0
         dev = inp["w13"].device
-        layer = Fp8MoELayer(inp.pop("w13"), inp.pop("w2"), NUM_EXPERTS if kind == "moe_ep" else sizes_dev.numel(), group)
+        layer = Fp8MoELayer(inp.pop("w13"), inp.pop("w2"), NUM_EXPERTS if kind == "moe_ep" else sizes_dev.numel(), group,
+                            chunks=EP_CHUNKS)
         inp["layer"] = layer
         gen = torch.Generator(device=dev).manual_seed(500 + rank)
         if kind == "moe_ep":
@@ -470,6 +474,8 @@ def run_b200(args):
         sizes = torch.randint(0, 2049, (sizes.numel(),), generator=gen_m, dtype=torch.int64)
         sizes[::5] = 0
     sizes_dev = sizes.to(dev)
+    global EP_CHUNKS
+    EP_CHUNKS = args.ep_chunks
     if args.cta_pair != -1:
         from triton_grouped_gemm_b200 import _lib
 
@@ -726,6 +732,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--rows", type=int, default=TOTAL_ROWS, help="routed rows per GPU (default: the benchmark's 655360)")
     ap.add_argument("--experts", type=int, default=NUM_EXPERTS, help="experts over all GPUs (default 128)")
+    ap.add_argument("--ep-chunks", type=int, default=4,
+                    help="moe_ep_fp8 with more than one GPU: groups of local experts whose exchange overlaps the GEMMs")
     ap.add_argument("--cta-pair", type=int, default=-1, choices=[-1, 0, 1],
                     help="kernel form: -1 chosen by problem size (default), 0 single-CTA tiles, 1 CTA pairs")
     ap.add_argument("--profile", action="store_true",

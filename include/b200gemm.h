@@ -163,6 +163,17 @@ int b200gemm_fp8_m_grouped_block(const void* a, const float* a_scale, const void
                                  const void* sizes, int sizes_is_i64, int num_groups, int64_t m_rows, int n, int k,
                                  int rows_padded, int num_sms, void* stream);
 
+/* Same GEMM with an indirection from row groups to weight matrices: group g (its
+ * size_per_group[g] rows, compact) is multiplied by b[group_to_b[g]], b holding num_b matrices.
+ * An expert-parallel layer uses it to consume rows in the order an all-to-all delivers them
+ * ([source rank][local expert] blocks, each its own group) without permuting them into
+ * expert-major order first.  group_to_b: int32 [num_groups] on the device, values in
+ * [0, num_b) (clamped).  No counterpart in the reference (it has no multi-GPU path). */
+int b200gemm_fp8_m_grouped_block_mapped(const void* a, const float* a_scale, const void* b, const float* b_scale,
+                                        void* c, const void* sizes, int sizes_is_i64, int num_groups,
+                                        const int* group_to_b, int num_b, int64_t m_rows, int n, int k, int num_sms,
+                                        void* stream);
+
 /* Masked-layout twin (decode): rows [g*expected_m, g*expected_m + masked_m[g]) of out.  No
  * reference counterpart as a kernel; it combines the masked layout of
  * gemm/BF16/m_grouped_gemm_masked_TMA.py:164-250 with the block-scaled contract above. */

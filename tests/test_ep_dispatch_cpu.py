@@ -82,3 +82,62 @@ def test_two_gloo_ranks():
             p.join(120)
             assert p.exitcode == 0
         assert results.get(0) is True and results.get(1) is True
+
+
+def _chunked_worker(rank, world, port, results):
+    """The pipelined layer's exchange (chunked plan, asynchronous all-to-alls) with a toy expert
+    function, against the direct per-token computation."""
+    from triton_grouped_gemm_b200.ep.dispatch import dispatch_chunk_async, make_chunked_plan
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        t, e, k, h, chunks = 31 + 7 * rank, 8, 3, 8, 2
+        idx, w = synthetic_routing(t, e, k, seed=20 + rank)
+        gen = torch.Generator().manual_seed(200 + rank)
+        x = torch.randn(t, h, generator=gen)
+        tag = torch.arange(t, dtype=torch.float32)[:, None] + 1000.0 * rank  # second payload: token identity
+        plan = make_chunked_plan(idx, e, dist.group.WORLD, chunks)
+        e_loc = e // world
+        ec = e_loc // chunks
+        assert plan.send_offsets[-1] == t * k and len(plan.send_splits) == chunks
+        ret = torch.empty(t * k, h)
+        ok = True
+        for c in range(chunks):
+            (rx, rtag), works, _keep = dispatch_chunk_async(plan, c, (x, tag), dist.group.WORLD)
+            for wk in works:
+                wk.wait()
+            perm = plan.recv_to_expert_major[c]
+            rows, tags = rx[perm], rtag[perm]
+            sizes = plan.size_per_group[c]
+            ok &= int(sizes.sum()) == rows.shape[0]
+            # both payloads travelled together: the tag's source rank owns a token whose x row matches
+            y = _expert_fn(rows, sizes, rank * e_loc + c * ec)
+            inv = torch.empty_like(perm)
+            inv[perm] = torch.arange(perm.numel())
+            lo, hi = plan.send_offsets[c], plan.send_offsets[c + 1]
+            dist.all_to_all_single(ret[lo:hi], y[inv], output_split_sizes=plan.send_splits[c],
+                                   input_split_sizes=plan.recv_splits[c])
+        pos = torch.empty_like(plan.send_order)
+        pos[plan.send_order] = torch.arange(t * k)
+        out = (ret[pos].view(t, k, h) * w[:, :, None]).sum(1)
+        ok &= torch.allclose(out, _reference(x, idx, w), atol=1e-5)
+        results[rank] = bool(ok)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_gloo_ranks_chunked_pipeline_plan():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    with ctx.Manager() as mgr:
+        results = mgr.dict()
+        procs = [ctx.Process(target=_chunked_worker, args=(r, 2, port, results)) for r in range(2)]
+        for p in procs:
+            p.start()
+        for p in procs:
+            p.join(120)
+            assert p.exitcode == 0
+        assert results.get(0) is True and results.get(1) is True

@@ -183,3 +183,28 @@ def test_full_size_properties():
         ref = O.fp8_block_m_grouped_ref(a[0][s:s + rows].cpu(), a[1][s:s + rows].cpu(), b[0][g:g + 1].cpu(),
                                         b[1][g:g + 1].cpu(), [rows])
         assert O.rdiff(c1[s:s + rows].float().cpu(), ref.float()) < TOL
+
+
+@pytest.mark.parametrize("pair", [0, 1])
+def test_group_to_weight_map(pair):
+    """Row blocks in arbitrary order, each mapped to one of the weight matrices (the layout an
+    all-to-all delivers: [source rank][expert] blocks).  Same result as gathering every
+    expert's rows together first."""
+    _lib.load().b200gemm_set_cta_pair(pair)
+    n, k, num_b = 384, 512, 3
+    block_sizes = [70, 0, 300, 129, 5, 0, 256, 33]        # 8 blocks
+    block_expert = [0, 1, 2, 0, 1, 2, 2, 0]
+    m = sum(block_sizes)
+    a8, a_s, b8, b_s = _quantised(m, num_b, n, k, seed=17)
+    out = m_grouped_fp8_block_scaled((a8.to(DEV), a_s.to(DEV)), (b8.to(DEV), b_s.to(DEV)),
+                                     torch.tensor(block_sizes, device=DEV),
+                                     group_to_b=torch.tensor(block_expert, dtype=torch.int32, device=DEV)).cpu()
+    # oracle: treat every block as a group of its own with a copy of its expert's weights
+    b8_blocks = torch.stack([b8[e] for e in block_expert])
+    b_s_blocks = torch.stack([b_s[e] for e in block_expert])
+    ref = O.fp8_block_m_grouped_ref(a8, a_s, b8_blocks, b_s_blocks, block_sizes)
+    assert O.rdiff(out.float(), ref.float()) < 5e-4
+    # identical bits to the unmapped kernel on the expanded weights
+    out2 = m_grouped_fp8_block_scaled((a8.to(DEV), a_s.to(DEV)), (b8_blocks.to(DEV), b_s_blocks.to(DEV)),
+                                      torch.tensor(block_sizes, device=DEV)).cpu()
+    assert torch.equal(out, out2)

@@ -46,6 +46,8 @@ _SIGNATURES = {
                                       c_int, c_int, c_int, c_int, c_void_p, c_int64, c_int, c_void_p],
     "b200gemm_fp8_m_grouped_block": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64,
                                      c_int, c_int, c_int, c_int, c_void_p],
+    "b200gemm_fp8_m_grouped_block_mapped": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                            c_void_p, c_int, c_int64, c_int, c_int, c_int, c_void_p],
     "b200gemm_fp8_m_grouped_masked_block": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                             c_int, c_int, c_int, c_int, c_void_p],
     "b200moe_gather_rows": [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p],

@@ -60,8 +60,15 @@ fp8_block_m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                            const __grid_constant__ CUtensorMap tm_c, const __grid_constant__ CUtensorMap tm_as,
                            int scales_by_tma, __nv_bfloat16* __restrict__ c_ptr, const float* __restrict__ a_scale,
                            const float* __restrict__ b_scale, const void* __restrict__ sizes, int sizes_i64,
-                           int num_groups, int masked_stride, int n, int k, unsigned* status) {
+                           int num_groups, int masked_stride, int n, int k, const int* __restrict__ b_map,
+                           int num_b, unsigned* status) {
   using L = Fp8BlockCfg<kBlockN, kPair>;
+  // weight matrix of row group g: b[b_map[g]] (clamped into range), or b[g] without a map
+  auto weight_of = [&](int g) -> int {
+    if (!b_map) return g;
+    const int v = __ldg(b_map + g);
+    return v < 0 ? 0 : (v >= num_b ? num_b - 1 : v);
+  };
   constexpr int kStages = L::kStages;
   constexpr int kCtas = kPair ? 2 : 1;
   constexpr int kTileM = kBlockM * kCtas;
@@ -134,7 +141,7 @@ fp8_block_m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
       if (!w.seek(mt)) break;
       const int row0 = static_cast<int>(w.tile_row0(mt)) + static_cast<int>(rank) * kBlockM;
       const int col0 = nt * kBlockN + static_cast<int>(rank) * L::kBRows;
-      const int g = w.g;
+      const int g = weight_of(w.g);
       for (int kb = 0; kb < num_kb; ++kb) {
         if (scales_by_tma && (kb & 31) == 0) {
           // a_scale[rows of this CTA, 32 k-blocks] -> shared memory, one tile per 32 k-blocks
@@ -263,7 +270,7 @@ fp8_block_m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
       const float* as_row = a_scale + (row_ok ? row : 0) * static_cast<long long>(num_kb);
       int nb = col_base >> 7;
       if (nb >= n_blocks) nb = n_blocks - 1;  // columns past n: results are discarded
-      const float* bs_blk = b_scale + (static_cast<long long>(w.g) * n_blocks + nb) * num_kb;
+      const float* bs_blk = b_scale + (static_cast<long long>(weight_of(w.g)) * n_blocks + nb) * num_kb;
       // 128 fp32 accumulators as 64 packed pairs (fma.rn.f32x2: two lanes per instruction)
       unsigned long long acc2[64];
 #pragma unroll
@@ -412,7 +419,8 @@ fp8_block_m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
 template <int kBlockN, bool kPair>
 static int launch_fp8_block(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const CUtensorMap& tm_c,
                             const CUtensorMap& tm_as, int scales_by_tma, void* c, const float* a_scale, const float* b_scale, const void* sizes, int sizes_is_i64,
-                            int num_groups, int masked_stride, int n, int k, int grid, cudaStream_t stream) {
+                            int num_groups, int masked_stride, int n, int k, const int* b_map, int num_b, int grid,
+                            cudaStream_t stream) {
   using L = Fp8BlockCfg<kBlockN, kPair>;
   auto kern = fp8_block_m_grouped_kernel<kBlockN, kPair>;
   B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes));
@@ -456,12 +464,12 @@ static int launch_fp8_block(const CUtensorMap& tm_a, const CUtensorMap& tm_b, co
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     B200_CUDA(cudaLaunchKernelEx(&cfg, kern, tm_a, tm_b, tm_c, tm_as, scales_by_tma, static_cast<__nv_bfloat16*>(c), a_scale, b_scale, sizes,
-                                 sizes_is_i64, num_groups, masked_stride, n, k, device_status_ptr()));
+                                 sizes_is_i64, num_groups, masked_stride, n, k, b_map, num_b, device_status_ptr()));
   } else {
     kern<<<grid, L::kThreads, L::kDynamicBytes, stream>>>(tm_a, tm_b, tm_c, tm_as, scales_by_tma,
                                                           static_cast<__nv_bfloat16*>(c), a_scale,
                                                           b_scale, sizes, sizes_is_i64, num_groups, masked_stride, n,
-                                                          k, device_status_ptr());
+                                                          k, b_map, num_b, device_status_ptr());
   }
   B200_CUDA(cudaGetLastError());
   return 0;
@@ -469,7 +477,10 @@ static int launch_fp8_block(const CUtensorMap& tm_a, const CUtensorMap& tm_b, co
 
 static int fp8_block_common(const void* a, const float* a_scale, const void* b, const float* b_scale, void* c,
                             const void* sizes, int sizes_is_i64, int num_groups, int64_t m_rows, int masked_stride,
-                            int n, int k, int num_sms, void* stream_v, const char* who) {
+                            int n, int k, int num_sms, void* stream_v, const char* who, const int* b_map = nullptr,
+                            int num_b = 0) {
+  if (!b_map) num_b = num_groups;
+  B200_REQUIRE(num_b > 0 || num_groups == 0, "%s: num_b must be positive when a group-to-weight map is given", who);
   B200_REQUIRE(num_groups >= 0 && m_rows >= 0 && n >= 0 && k >= 0, "%s: negative dimension", who);
   if (num_groups == 0 || m_rows == 0 || n == 0) return 0;
   B200_REQUIRE(k > 0, "%s: k must be positive", who);
@@ -502,7 +513,7 @@ static int fp8_block_common(const void* a, const float* a_scale, const void* b, 
     if (rc) return rc;
   }
   {
-    const uint64_t dims[3] = {static_cast<uint64_t>(k), static_cast<uint64_t>(n), static_cast<uint64_t>(num_groups)};
+    const uint64_t dims[3] = {static_cast<uint64_t>(k), static_cast<uint64_t>(n), static_cast<uint64_t>(num_b)};
     const uint64_t strides[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(k) * n};
     const uint32_t box[3] = {128, static_cast<uint32_t>(b_box_rows), 1};
     int rc = encode_tmap(&tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, b, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -532,12 +543,12 @@ static int fp8_block_common(const void* a, const float* a_scale, const void* b, 
   }
   if (pair)
     return launch_fp8_block<256, true>(tm_a, tm_b, tm_c, tm_as, scales_by_tma, c, a_scale, b_scale, sizes, sizes_is_i64, num_groups,
-                                       masked_stride, n, k, grid, stream);
+                                       masked_stride, n, k, b_map, num_b, grid, stream);
   if (block_n == 256)
     return launch_fp8_block<256, false>(tm_a, tm_b, tm_c, tm_as, scales_by_tma, c, a_scale, b_scale, sizes, sizes_is_i64, num_groups,
-                                        masked_stride, n, k, grid, stream);
+                                        masked_stride, n, k, b_map, num_b, grid, stream);
   return launch_fp8_block<128, false>(tm_a, tm_b, tm_c, tm_as, scales_by_tma, c, a_scale, b_scale, sizes, sizes_is_i64, num_groups,
-                                      masked_stride, n, k, grid, stream);
+                                      masked_stride, n, k, b_map, num_b, grid, stream);
 }
 
 }  // namespace b200
@@ -549,6 +560,16 @@ int b200gemm_fp8_m_grouped_block(const void* a, const float* a_scale, const void
                                  int rows_padded, int num_sms, void* stream) {
   return b200::fp8_block_common(a, a_scale, b, b_scale, c, sizes, sizes_is_i64, num_groups, m_rows,
                                 rows_padded ? -1 : 0, n, k, num_sms, stream, "b200gemm_fp8_m_grouped_block");
+}
+
+int b200gemm_fp8_m_grouped_block_mapped(const void* a, const float* a_scale, const void* b, const float* b_scale,
+                                        void* c, const void* sizes, int sizes_is_i64, int num_groups,
+                                        const int* group_to_b, int num_b, int64_t m_rows, int n, int k, int num_sms,
+                                        void* stream) {
+  if (!group_to_b)
+    return b200::set_error(b200::kErrInvalidArgument, "b200gemm_fp8_m_grouped_block_mapped: group_to_b is null");
+  return b200::fp8_block_common(a, a_scale, b, b_scale, c, sizes, sizes_is_i64, num_groups, m_rows, 0, n, k, num_sms,
+                                stream, "b200gemm_fp8_m_grouped_block_mapped", group_to_b, num_b);
 }
 
 int b200gemm_fp8_m_grouped_masked_block(const void* a, const float* a_scale, const void* b, const float* b_scale,

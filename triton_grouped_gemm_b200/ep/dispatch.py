@@ -89,6 +89,97 @@ def make_plan(topk_idx: torch.Tensor, num_experts: int, group: Optional[dist.Pro
                         size_per_group=recv_matrix.sum(0).to(torch.int64))
 
 
+@dataclass
+class ChunkedPlan:
+    """Routing of one step split into ``chunks`` groups of local experts (chunk c = local experts
+    [c*ec, (c+1)*ec) on EVERY rank), so that the exchange of chunk c+1 can run beside the expert
+    GEMMs of chunk c.  Rows are sent chunk-major: chunk, destination rank, expert."""
+    world: int
+    experts_per_rank: int
+    chunks: int
+    num_tokens: int
+    top_k: int
+    send_order: torch.Tensor            # [T*k] indices into the flattened (token, k) pairs, chunk-major
+    send_offsets: List[int]             # [chunks + 1] row offsets of the chunks in send order
+    send_splits: List[List[int]]        # [chunks][world] rows sent to each rank
+    recv_splits: List[List[int]]        # [chunks][world] rows received from each rank
+    recv_to_expert_major: List[torch.Tensor]  # per chunk: expert-major row i = received row perm[i]
+    size_per_group: List[torch.Tensor]  # per chunk: [ec] rows per local expert of the chunk (int64)
+    block_sizes: List[torch.Tensor]     # per chunk: [world*ec] rows of each (source rank, expert) block, arrival order
+    block_expert: List[torch.Tensor]    # per chunk: [world*ec] local expert (0..e_loc) of each block, int32
+
+
+def make_chunked_plan(topk_idx: torch.Tensor, num_experts: int, group: Optional[dist.ProcessGroup],
+                      chunks: int, with_permutation: bool = True) -> ChunkedPlan:
+    """Like ``make_plan`` for ``chunks`` expert groups at once; one host synchronisation.
+    ``with_permutation=False`` skips the expert-major permutations (callers that feed the
+    received blocks to the GEMM as they arrive do not need them)."""
+    world = 1 if group is None else dist.get_world_size(group)
+    assert num_experts % world == 0, "experts must divide evenly over the ranks"
+    e_loc = num_experts // world
+    assert e_loc % chunks == 0, "chunks must divide the experts of a rank"
+    ec = e_loc // chunks
+    t, k = topk_idx.shape
+    dev = topk_idx.device
+    flat = topk_idx.reshape(-1).to(torch.int64)
+    rank_of = flat // e_loc
+    local = flat - rank_of * e_loc
+    chunk_of = local // ec
+    key = chunk_of * (world * ec) + rank_of * ec + (local - chunk_of * ec)
+    send_order = torch.argsort(key, stable=True)
+    counts = torch.bincount(flat, minlength=num_experts)                      # [world * e_loc]
+    recv_counts = torch.empty_like(counts)                                     # from rank r, local expert e
+    _all_to_all(recv_counts, counts, None, None, group)
+    send_m = counts.view(world, chunks, ec).sum(-1).t().contiguous()           # [chunks, world]
+    recv_3 = recv_counts.view(world, chunks, ec)
+    recv_m = recv_3.sum(-1).t().contiguous()                                   # [chunks, world]
+    both = torch.stack([send_m, recv_m]).cpu()                                 # the one host sync
+    send_splits, recv_splits = both[0].tolist(), both[1].tolist()
+    send_offsets = [0]
+    for c in range(chunks):
+        send_offsets.append(send_offsets[-1] + int(sum(send_splits[c])))
+    perms, sizes, block_sizes, block_expert = [], [], [], []
+    for c in range(chunks):
+        recv_matrix = recv_3[:, c, :]                                          # [world, ec]
+        block_sizes.append(recv_matrix.reshape(-1).to(torch.int64).contiguous())
+        block_expert.append((torch.arange(ec, device=dev, dtype=torch.int32) + c * ec).repeat(world).contiguous())
+        sizes.append(recv_matrix.sum(0).to(torch.int64))
+        if not with_permutation:
+            perms.append(None)
+            continue
+        blocks = recv_matrix.reshape(-1)
+        starts = torch.cumsum(blocks, 0) - blocks
+        order = torch.arange(world * ec, device=dev).view(world, ec).t().reshape(-1)
+        total = int(sum(recv_splits[c]))
+        blk_sizes = blocks[order]
+        blk_starts = starts[order]
+        out_starts = torch.cumsum(blk_sizes, 0) - blk_sizes
+        row_block = torch.repeat_interleave(torch.arange(order.numel(), device=dev), blk_sizes, output_size=total)
+        perms.append(blk_starts[row_block] + (torch.arange(total, device=dev) - out_starts[row_block]))
+    return ChunkedPlan(world=world, experts_per_rank=e_loc, chunks=chunks, num_tokens=t, top_k=k,
+                       send_order=send_order, send_offsets=send_offsets, send_splits=send_splits,
+                       recv_splits=recv_splits, recv_to_expert_major=perms, size_per_group=sizes,
+                       block_sizes=block_sizes, block_expert=block_expert)
+
+
+def dispatch_chunk_async(plan: ChunkedPlan, c: int, payloads, group):
+    """Starts the exchange of chunk ``c`` for every tensor of ``payloads`` ([T, ...] per token).
+    Returns (received tensors in arrival order, work handles, tensors to keep alive)."""
+    lo, hi = plan.send_offsets[c], plan.send_offsets[c + 1]
+    token_of_pair = plan.send_order[lo:hi] // plan.top_k
+    total = int(sum(plan.recv_splits[c]))
+    recvs, works, keep = [], [], []
+    for rows in payloads:
+        src = rows.view(torch.uint8) if rows.dtype in (torch.float8_e4m3fn, torch.float8_e5m2) else rows
+        send = _gather_rows(src, token_of_pair)
+        recv = torch.empty((total,) + tuple(send.shape[1:]), dtype=send.dtype, device=send.device)
+        works.append(dist.all_to_all_single(recv, send, output_split_sizes=plan.recv_splits[c],
+                                            input_split_sizes=plan.send_splits[c], group=group, async_op=True))
+        recvs.append(recv)
+        keep.append(send)
+    return recvs, works, keep
+
+
 def dispatch(plan: DispatchPlan, rows: torch.Tensor, group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
     """rows [T, ...] per token -> [R, ...] rows for this rank's experts, expert-major."""
     token_of_pair = plan.send_order // plan.top_k

@@ -16,13 +16,18 @@ import torch.distributed as dist
 
 from ..gemm.FP8.m_grouped_gemm_block_scaled import m_grouped_fp8_block_scaled, m_grouped_fp8_block_scaled_masked
 from ..quant.per_block_cast import per_block_cast_to_fp8, per_token_cast_to_fp8, swiglu_per_token_cast_to_fp8
-from .dispatch import combine, dispatch, make_plan
+from .dispatch import combine, dispatch, dispatch_chunk_async, make_chunked_plan, make_plan
 
 
 class Fp8MoELayer:
     def __init__(self, w13: torch.Tensor, w2: torch.Tensor, num_experts: int,
-                 group: Optional[dist.ProcessGroup] = None):
-        """w13 [E_local, 2*I, H] (gate rows then up rows), w2 [E_local, H, I], bf16, this rank's experts."""
+                 group: Optional[dist.ProcessGroup] = None, chunks: int = 4, comm_sms: int = 16):
+        """w13 [E_local, 2*I, H] (gate rows then up rows), w2 [E_local, H, I], bf16, this rank's experts.
+        With more than one rank the expert GEMMs consume rows in the order the all-to-all delivers
+        them (every [source rank][expert] block is a row group of its own, mapped to its expert's
+        weights), so nothing is permuted on the expert side.  ``chunks`` > 1 pipelines the step
+        over groups of local experts: the all-to-alls of neighbouring chunks run beside the expert
+        GEMMs, which then leave ``comm_sms`` SMs to the collective's kernels."""
         assert w13.dim() == 3 and w2.dim() == 3 and w13.shape[0] == w2.shape[0]
         self.group = group
         self.num_experts = num_experts
@@ -31,21 +36,71 @@ class Fp8MoELayer:
         assert w2.shape == (self.e_local, self.hidden, self.inter)
         self.w13 = per_block_cast_to_fp8(w13.contiguous())
         self.w2 = per_block_cast_to_fp8(w2.contiguous())
+        world = 1 if group is None else dist.get_world_size(group)
+        while chunks > 1 and self.e_local % chunks:
+            chunks -= 1
+        self.world = world
+        self.chunks = chunks if world > 1 else 1
+        self.comm_sms = comm_sms
 
-    def experts(self, x8: torch.Tensor, xs: torch.Tensor, size_per_group: torch.Tensor) -> torch.Tensor:
-        """Rows already grouped by local expert: [R, H] fp8 + scales -> [R, H] bf16."""
-        h = m_grouped_fp8_block_scaled((x8, xs), self.w13, size_per_group)
+    def experts(self, x8: torch.Tensor, xs: torch.Tensor, size_per_group: torch.Tensor,
+                group_to_expert: Optional[torch.Tensor] = None, num_sms: int = -1) -> torch.Tensor:
+        """Rows grouped by local expert: [R, H] fp8 + scales -> [R, H] bf16.  With
+        ``group_to_expert`` (int32) the row groups are arbitrary blocks, block i using the
+        weights of local expert ``group_to_expert[i]``."""
+        h = m_grouped_fp8_block_scaled((x8, xs), self.w13, size_per_group, num_sms=num_sms,
+                                       group_to_b=group_to_expert)
         a8, a_s = swiglu_per_token_cast_to_fp8(h)
-        return m_grouped_fp8_block_scaled((a8, a_s), self.w2, size_per_group)
+        return m_grouped_fp8_block_scaled((a8, a_s), self.w2, size_per_group, num_sms=num_sms,
+                                          group_to_b=group_to_expert)
 
     def forward(self, x: torch.Tensor, topk_idx: torch.Tensor, topk_weight: torch.Tensor) -> torch.Tensor:
         """x [T, H] bf16, topk_idx/topk_weight [T, k] -> [T, H] bf16."""
         x8, xs = per_token_cast_to_fp8(x.contiguous())
+        if self.world > 1:
+            return self._forward_pipelined(x8, xs, topk_idx, topk_weight)
         plan = make_plan(topk_idx, self.num_experts, self.group)
         r8 = dispatch(plan, x8, self.group)
         rs = dispatch(plan, xs, self.group)
         y = self.experts(r8.contiguous(), rs.contiguous(), plan.size_per_group)
         return combine(plan, y, topk_weight, self.group)
+
+    def _forward_pipelined(self, x8, xs, topk_idx, topk_weight) -> torch.Tensor:
+        """More than one rank.  Chunk c's GEMMs run while chunk c+1 is being dispatched and chunk
+        c-1 combined (the collectives are asynchronous on the process group's own stream)."""
+        from .. import _lib
+
+        plan = make_chunked_plan(topk_idx, self.num_experts, self.group, self.chunks, with_permutation=False)
+        sms = _lib.load().b200gemm_sm_count()
+        gemm_sms = sms - self.comm_sms if (self.chunks > 1 and 0 < self.comm_sms < sms - 2) else -1
+        total_pairs = plan.send_order.numel()
+        ret = torch.empty((total_pairs, self.hidden), dtype=torch.bfloat16, device=x8.device)
+        pending = []
+        nxt = dispatch_chunk_async(plan, 0, (x8, xs), self.group)
+        for c in range(self.chunks):
+            recvs, works, keep = nxt
+            nxt = dispatch_chunk_async(plan, c + 1, (x8, xs), self.group) if c + 1 < self.chunks else None
+            for w in works:
+                w.wait()
+            # rows stay in arrival order: [source rank][expert of the chunk] blocks
+            y = self.experts(recvs[0].view(torch.float8_e4m3fn), recvs[1], plan.block_sizes[c],
+                             group_to_expert=plan.block_expert[c], num_sms=gemm_sms)
+            lo, hi = plan.send_offsets[c], plan.send_offsets[c + 1]
+            pending.append((dist.all_to_all_single(ret[lo:hi], y, output_split_sizes=plan.send_splits[c],
+                                                   input_split_sizes=plan.recv_splits[c], group=self.group,
+                                                   async_op=True), y, keep, recvs))
+        for w, *_ in pending:
+            w.wait()
+        # position of pair (t, k) among the returned rows (send order is chunk-major)
+        pos = torch.empty_like(plan.send_order)
+        pos[plan.send_order] = torch.arange(total_pairs, device=pos.device)
+        out = torch.empty((plan.num_tokens, self.hidden), dtype=torch.bfloat16, device=x8.device)
+        w32 = topk_weight.reshape(-1).to(torch.float32).contiguous()
+        with torch.cuda.device(x8.device):
+            rc = _lib.load().b200moe_combine_topk(ret.data_ptr(), pos.data_ptr(), w32.data_ptr(), out.data_ptr(),
+                                                  plan.num_tokens, plan.top_k, self.hidden, _lib.stream_ptr(x8.device))
+        _lib.check(rc, "b200moe_combine_topk")
+        return out
 
     def decode(self, x8: torch.Tensor, xs: torch.Tensor, masked_m: torch.Tensor, m_max: int,
                out: Optional[torch.Tensor] = None) -> torch.Tensor:

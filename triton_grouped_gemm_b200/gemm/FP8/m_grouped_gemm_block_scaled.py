@@ -40,13 +40,32 @@ def _check_pairs(a: Pair, b: Pair):
 
 
 def m_grouped_fp8_block_scaled(a: Pair, b: Pair, size_per_group: Tensor, *, out: Optional[Tensor] = None,
-                               rows_padded: bool = False) -> Tensor:
+                               rows_padded: bool = False, num_sms: int = -1,
+                               group_to_b: Optional[Tensor] = None) -> Tensor:
     """``rows_padded=False``: rows of ``a`` are compact (sum(size_per_group) rows used).
     ``rows_padded=True``: each group's rows are padded to a multiple of 128 (DeepGEMM's
-    contiguous layout); padding rows of ``out`` are not written."""
+    contiguous layout); padding rows of ``out`` are not written.  ``num_sms`` > 0 limits the
+    persistent grid (e.g. to leave SMs to a collective running beside the GEMM).
+    ``group_to_b`` (int32, one entry per row group): row group i uses ``b[group_to_b[i]]``; the
+    number of row groups is then ``size_per_group.numel()``, independent of ``b.shape[0]``."""
     a8, a_s, b8, b_s, m, n, k, g = _check_pairs(a, b)
-    assert size_per_group.numel() == g
     _lib.require_cuda(size_per_group)
+    if group_to_b is not None:
+        assert not rows_padded, "group_to_b works on compact rows"
+        assert group_to_b.dtype == torch.int32 and group_to_b.is_contiguous()
+        assert group_to_b.numel() == size_per_group.numel()
+        _lib.require_cuda(group_to_b)
+        if out is None:
+            out = torch.empty((m, n), device=a8.device, dtype=torch.bfloat16)
+        assert out.shape == (m, n) and out.dtype == torch.bfloat16 and out.is_contiguous()
+        sizes, is64 = _lib.sizes_arg(size_per_group)
+        with torch.cuda.device(a8.device):
+            rc = _lib.load().b200gemm_fp8_m_grouped_block_mapped(
+                _lib.ptr(a8), _lib.ptr(a_s), _lib.ptr(b8), _lib.ptr(b_s), _lib.ptr(out), _lib.ptr(sizes), is64,
+                size_per_group.numel(), _lib.ptr(group_to_b), g, m, n, k, int(num_sms), _lib.stream_ptr(a8.device))
+        _lib.check(rc, "b200gemm_fp8_m_grouped_block_mapped")
+        return out
+    assert size_per_group.numel() == g
     if out is None:
         out = torch.empty((m, n), device=a8.device, dtype=torch.bfloat16)
     assert out.shape == (m, n) and out.dtype == torch.bfloat16 and out.is_contiguous()
@@ -54,7 +73,7 @@ def m_grouped_fp8_block_scaled(a: Pair, b: Pair, size_per_group: Tensor, *, out:
     with torch.cuda.device(a8.device):
         rc = _lib.load().b200gemm_fp8_m_grouped_block(
             _lib.ptr(a8), _lib.ptr(a_s), _lib.ptr(b8), _lib.ptr(b_s), _lib.ptr(out), _lib.ptr(sizes), is64, g, m, n, k,
-            1 if rows_padded else 0, -1, _lib.stream_ptr(a8.device))
+            1 if rows_padded else 0, int(num_sms), _lib.stream_ptr(a8.device))
     _lib.check(rc, "b200gemm_fp8_m_grouped_block")
     return out
 
