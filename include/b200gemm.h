@@ -227,6 +227,21 @@ int b200moe_gather_rows(const void* src, const int64_t* idx, void* dst, int64_t 
 int b200moe_combine_topk(const void* y, const int64_t* pos, const float* weights, void* out, int64_t tokens, int top_k,
                          int hidden, void* stream);
 
+/* ---- integer layouts on the device ------------------------------------------------------- */
+
+/* gemm/layout.py:61-71 make_group_starts: exclusive prefix of the group sizes (padded != 0: of the
+ * sizes rounded up to block_m).  sizes int32/int64 [num_groups] on the device -> out int32. */
+int b200layout_group_starts(const void* sizes, int sizes_is_i64, int num_groups, int padded, int block_m, int* out,
+                            void* stream);
+/* gemm/layout.py:100-120 make_deep_gemm_psum_layout: per group the end offset of its real rows in
+ * padded-row coordinates. */
+int b200layout_psum(const void* sizes, int sizes_is_i64, int num_groups, int block_m, int* out, void* stream);
+/* gemm/layout.py:73-98 make_deep_gemm_grouped_layout: one int32 per padded row, the group id on
+ * real rows and -1 on padding rows.  out holds total_padded_rows entries (the caller computes
+ * that sum; rows beyond it are not written). */
+int b200layout_grouped_rows(const void* sizes, int sizes_is_i64, int num_groups, int block_m, int* out,
+                            int64_t total_padded_rows, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

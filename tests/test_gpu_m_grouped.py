@@ -247,3 +247,22 @@ def test_host_operand_pipeline_matches_single_launch():
         out = m_grouped_gemm_host(a, b, sizes, True, chunks=chunks)
         torch.cuda.synchronize()
         assert torch.equal(out, ref)
+
+
+def test_device_layout_builders_match_host_layouts():
+    """gemm.layout on CUDA sizes (library kernels) against the same functions on host sizes."""
+    from triton_grouped_gemm_b200.gemm import layout as L
+
+    for sizes in ([5, 0, 128, 129, 1, 300], [128] * 7, [0, 0, 3], list(range(0, 700, 7))):
+        for dt in (torch.int32, torch.int64):
+            host = torch.tensor(sizes, dtype=dt)
+            dev = host.to(DEV)
+            for block_m in (128, 64):
+                assert L.make_group_starts(dev, block_m=block_m).cpu().tolist() == L.make_group_starts(host, block_m=block_m).tolist()
+                assert (L.make_group_starts(dev, padded=True, block_m=block_m).cpu().tolist()
+                        == L.make_group_starts(host, padded=True, block_m=block_m).tolist())
+                assert (L.make_deep_gemm_psum_layout(dev, block_m=block_m).cpu().tolist()
+                        == L.make_deep_gemm_psum_layout(host, block_m=block_m).tolist())
+                a = L.make_deep_gemm_grouped_layout(dev, block_m=block_m).cpu()
+                b = L.make_deep_gemm_grouped_layout(host, block_m=block_m)
+                assert a.dtype == b.dtype and torch.equal(a, b)

@@ -50,6 +50,9 @@ _SIGNATURES = {
                                             c_void_p, c_int, c_int64, c_int, c_int, c_int, c_void_p],
     "b200gemm_fp8_m_grouped_masked_block": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                             c_int, c_int, c_int, c_int, c_void_p],
+    "b200layout_group_starts": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    "b200layout_psum": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
+    "b200layout_grouped_rows": [c_void_p, c_int, c_int, c_int, c_void_p, c_int64, c_void_p],
     "b200moe_gather_rows": [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p],
     "b200moe_combine_topk": [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p],
     "b200quant_act_1x128": [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_void_p],

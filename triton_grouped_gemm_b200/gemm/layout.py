@@ -1,8 +1,9 @@
 """Integer layouts of grouped GEMM problems (mirror of the reference's gemm/layout.py:11-126).
 
 Same names, arguments, results and ValueErrors as the reference.  Two differences in how the
-results are produced: the per-row and psum layouts are built with tensor ops on the device
-that holds the sizes (the reference loops over ``.tolist()`` on the host), and
+results are produced: for sizes on a CUDA device the group starts, the per-row and the psum
+layouts come from the library's layout kernels (the reference loops over ``.tolist()`` on the
+host; host tensors are handled with tensor ops, as integer host helpers), and
 ``device_group_metadata`` gives the kernels' view of a size vector for debugging -- the CUDA
 kernels themselves derive all of this on the fly from ``size_per_group``.
 """
@@ -64,9 +65,32 @@ def make_grouped_layout(size_per_group: SizesLike, block_m: int = 128) -> Groupe
     return GroupedLayout(starts=_exclusive_cumsum(padded).contiguous(), sizes=sizes, padded_sizes=padded.contiguous())
 
 
+def _on_device(sizes: torch.Tensor) -> bool:
+    return sizes.is_cuda
+
+
+def _sizes_ptr(sizes: torch.Tensor):
+    """(contiguous int32/int64 tensor, is_int64) for the C ABI."""
+    if sizes.dtype not in (torch.int32, torch.int64):
+        sizes = sizes.to(torch.int64)
+    return sizes.contiguous(), int(sizes.dtype == torch.int64)
+
+
 def make_group_starts(size_per_group: SizesLike, *, padded: bool = False, block_m: int = 128,
                       dtype: torch.dtype = torch.int32) -> torch.Tensor:
     sizes = as_group_sizes(size_per_group, dtype=dtype)
+    if _on_device(sizes) and dtype == torch.int32:
+        from .. import _lib
+
+        if block_m <= 0:
+            raise ValueError(f"alignment must be positive, got {block_m}")
+        s, is64 = _sizes_ptr(sizes)
+        out = torch.empty(s.numel(), dtype=torch.int32, device=s.device)
+        with torch.cuda.device(s.device):
+            rc = _lib.load().b200layout_group_starts(s.data_ptr(), is64, s.numel(), int(padded), int(block_m),
+                                                     out.data_ptr(), _lib.stream_ptr(s.device))
+        _lib.check(rc, "b200layout_group_starts")
+        return out
     if padded:
         sizes = round_up_to_alignment(sizes, block_m)
     return _exclusive_cumsum(sizes).contiguous()
@@ -77,6 +101,16 @@ def make_deep_gemm_grouped_layout(size_per_group: SizesLike, *, block_m: int = 1
     sizes = as_group_sizes(size_per_group, device=device, dtype=torch.int32)
     padded = round_up_to_alignment(sizes, block_m).to(torch.int64)
     total = int(padded.sum().item())
+    if _on_device(sizes):
+        from .. import _lib
+
+        s, is64 = _sizes_ptr(sizes)
+        out = torch.empty(total, dtype=torch.int32, device=s.device)
+        with torch.cuda.device(s.device):
+            rc = _lib.load().b200layout_grouped_rows(s.data_ptr(), is64, s.numel(), int(block_m), out.data_ptr(), total,
+                                                     _lib.stream_ptr(s.device))
+        _lib.check(rc, "b200layout_grouped_rows")
+        return out
     ids = torch.arange(sizes.numel(), device=sizes.device, dtype=torch.int32)
     row_group = torch.repeat_interleave(ids, padded, output_size=total)
     starts = _exclusive_cumsum(padded)
@@ -88,6 +122,18 @@ def make_deep_gemm_grouped_layout(size_per_group: SizesLike, *, block_m: int = 1
 def make_deep_gemm_psum_layout(size_per_group: SizesLike, *, block_m: int = 128, device=None) -> torch.Tensor:
     """Per expert: the end offset of its real rows in padded-M coordinates."""
     sizes = as_group_sizes(size_per_group, device=device, dtype=torch.int32)
+    if _on_device(sizes):
+        from .. import _lib
+
+        if block_m <= 0:
+            raise ValueError(f"alignment must be positive, got {block_m}")
+        s, is64 = _sizes_ptr(sizes)
+        out = torch.empty(s.numel(), dtype=torch.int32, device=s.device)
+        with torch.cuda.device(s.device):
+            rc = _lib.load().b200layout_psum(s.data_ptr(), is64, s.numel(), int(block_m), out.data_ptr(),
+                                             _lib.stream_ptr(s.device))
+        _lib.check(rc, "b200layout_psum")
+        return out
     padded = round_up_to_alignment(sizes, block_m)
     return (_exclusive_cumsum(padded) + sizes).to(torch.int32).contiguous()
 
