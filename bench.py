@@ -395,6 +395,12 @@ def run_reference(args):
     rank, world, _ = dist_env()
     if rank != 0:
         return
+    # torchrun exports OMP_NUM_THREADS=1 to its workers; the reference arm is the only CPU work of
+    # the job (the other ranks have exited), so give it every core the process may run on
+    try:
+        torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
+    except (AttributeError, OSError):
+        torch.set_num_threads(max(1, os.cpu_count() or 1))
     kind, k, n, trans_b = WORKLOADS[args.workload]
     sizes = (moe_sizes(kind, max(args.gpus, 1), 0, args.rows) if kind in ("moe_ep", "moe_decode")
              else rank_sizes(max(args.gpus, 1), 0, args.rows, args.experts))
