@@ -58,7 +58,7 @@ def sha(t: torch.Tensor) -> str:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="root of a checkout of DeepLink-org/Triton_Grouped_GEMM")
     args = ap.parse_args()
     ref = Path(args.reference)
     sys.path.insert(0, str(ref))
