@@ -92,11 +92,16 @@ quant_act_1x128_kernel(const uint4* __restrict__ x, uint2* __restrict__ q, float
 
 // ------------------------------------------------------------------ SwiGLU + 1x128 (between the two expert GEMMs)
 // h [rows, 2*inter] holds gate | up (the gate+up GEMM's output).  act = bf16(silu(gate) * up)
-// with silu(x) = x / (1 + exp(-x)) evaluated in fp32 from the 16-bit inputs; act is then
-// quantised exactly like act_1x128 above (same bytes and scales as running
-// per_token_cast_to_fp8 on the rounded activation).  Saves writing and re-reading act.
+// with silu(x) = x / (1 + exp(-x)) evaluated in fp32 (fast exponential and quotient) from the
+// 16-bit inputs; act is then quantised exactly like act_1x128 above (same bytes and scales as
+// running per_token_cast_to_fp8 on the rounded activation).  Saves writing and re-reading act.
 __device__ __forceinline__ float silu_mul_round_bf16(float g, float u) {
-  const float act = __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))), u);
+  // silu has no reference bit pattern to reproduce (the torch oracle rounds the activation to
+  // bf16, which absorbs a 2^-21 relative error in all but ~1e-4 of the elements), so the
+  // exponential and the quotient use the special-function unit: ex2.approx and rcp.approx
+  // instead of ~25 instructions of IEEE expf and division per element, which kept this kernel
+  // at half of the memory roofline.  g << 0: exp(-g) = inf, g / inf = -0.
+  const float act = __fmul_rn(__fdividef(g, 1.0f + __expf(-g)), u);
   return __bfloat162float(__float2bfloat16_rn(act));
 }
 
@@ -107,25 +112,35 @@ quant_swiglu_1x128_kernel(const uint16_t* __restrict__ h, uint2* __restrict__ q,
   const long long num_chunks = rows * chunks_per_row;
   const long long stride = static_cast<long long>(gridDim.x) * kActThreads;
   long long i = static_cast<long long>(blockIdx.x) * kActThreads + threadIdx.x;
+  // (row, chunk in row) of chunk i, advanced by the constant stride with a carry instead of a
+  // 64-bit division per chunk
+  long long r = i / chunks_per_row;
+  long long c = i - r * chunks_per_row;
+  const long long dr = stride / chunks_per_row;
+  const long long dc = stride - dr * chunks_per_row;
+  // loop bound taken at the warp's first chunk: all lanes run the same trip count for the shuffles
   for (; i - (threadIdx.x & 31) < num_chunks; i += stride) {
     const bool live = i < num_chunks;
     float f[8];
     if (live) {
-      const long long r = i / chunks_per_row;
-      const long long c = (i - r * chunks_per_row) * 8;
-      const uint4 gv = __ldg(reinterpret_cast<const uint4*>(h + r * 2 * inter + c));
-      const uint4 uv = __ldg(reinterpret_cast<const uint4*>(h + r * 2 * inter + inter + c));
+      const uint16_t* row_ptr = h + r * 2 * inter + c * 8;
+      const uint4 gv = __ldg(reinterpret_cast<const uint4*>(row_ptr));
+      const uint4 uv = __ldg(reinterpret_cast<const uint4*>(row_ptr + inter));
       const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w}, uw[4] = {uv.x, uv.y, uv.z, uv.w};
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        f[2 * e] = silu_mul_round_bf16(to_f32(static_cast<uint16_t>(gw[e] & 0xFFFFu), 0),
-                                       to_f32(static_cast<uint16_t>(uw[e] & 0xFFFFu), 0));
-        f[2 * e + 1] = silu_mul_round_bf16(to_f32(static_cast<uint16_t>(gw[e] >> 16), 0),
-                                           to_f32(static_cast<uint16_t>(uw[e] >> 16), 0));
+        f[2 * e] = silu_mul_round_bf16(__uint_as_float(gw[e] << 16), __uint_as_float(uw[e] << 16));
+        f[2 * e + 1] = silu_mul_round_bf16(__uint_as_float(gw[e] & 0xFFFF0000u), __uint_as_float(uw[e] & 0xFFFF0000u));
       }
     } else {
 #pragma unroll
       for (int e = 0; e < 8; ++e) f[e] = 0.f;
+    }
+    r += dr;
+    c += dc;
+    if (c >= chunks_per_row) {
+      c -= chunks_per_row;
+      ++r;
     }
     float amax = 0.f;
 #pragma unroll
