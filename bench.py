@@ -226,6 +226,7 @@ def algorithmic_work(kind, k, n, sizes):
 
 
 EP_CHUNKS = 4  # set from --ep-chunks
+EP_TRANSPORT = "p2p"  # set from --ep-transport
 
 
 def build_step(kind, k, n, trans_b, sizes_dev, inp):
@@ -294,7 +295,8 @@ def build_step(kind, k, n, trans_b, sizes_dev, inp):
         rank = dist.get_rank() if dist.is_initialized() else 0
         dev = inp["w13"].device
         layer = Fp8MoELayer(inp.pop("w13"), inp.pop("w2"), NUM_EXPERTS if kind == "moe_ep" else sizes_dev.numel(), group,
-                            chunks=EP_CHUNKS)
+                            chunks=EP_CHUNKS, transport=EP_TRANSPORT if kind == "moe_ep" else "nccl",
+                            tokens_per_rank=ROWS_USED[0] // TOP_K, top_k=TOP_K)
         inp["layer"] = layer
         gen = torch.Generator(device=dev).manual_seed(500 + rank)
         if kind == "moe_ep":
@@ -480,8 +482,9 @@ def run_b200(args):
         sizes = torch.randint(0, 2049, (sizes.numel(),), generator=gen_m, dtype=torch.int64)
         sizes[::5] = 0
     sizes_dev = sizes.to(dev)
-    global EP_CHUNKS
+    global EP_CHUNKS, EP_TRANSPORT
     EP_CHUNKS = args.ep_chunks
+    EP_TRANSPORT = args.ep_transport
     if args.cta_pair != -1:
         from triton_grouped_gemm_b200 import _lib
 
@@ -740,6 +743,9 @@ def main():
     ap.add_argument("--experts", type=int, default=NUM_EXPERTS, help="experts over all GPUs (default 128)")
     ap.add_argument("--ep-chunks", type=int, default=4,
                     help="moe_ep_fp8 with more than one GPU: groups of local experts whose exchange overlaps the GEMMs")
+    ap.add_argument("--ep-transport", choices=["p2p", "nccl"], default="p2p",
+                    help="moe_ep_fp8 with more than one GPU: rows move by kernels over peer memory (p2p) or by "
+                         "NCCL all-to-all (nccl)")
     ap.add_argument("--cta-pair", type=int, default=-1, choices=[-1, 0, 1],
                     help="kernel form: -1 chosen by problem size (default), 0 single-CTA tiles, 1 CTA pairs")
     ap.add_argument("--profile", action="store_true",

@@ -227,6 +227,32 @@ int b200moe_gather_rows(const void* src, const int64_t* idx, void* dst, int64_t 
 int b200moe_combine_topk(const void* y, const int64_t* pos, const float* weights, void* out, int64_t tokens, int top_k,
                          int hidden, void* stream);
 
+/* The same row movers over the buffers of several ranks (peer memory mapped into this process):
+ * dst_bases[dst_rank[i]][dst_row[i], :] = src[src_idx[i], :], and
+ * out[t, :] = bf16(sum_k weights[t,k] * src_bases[pair_rank[t,k]][pair_row[t,k], :]).
+ * dst_bases / src_bases: HOST arrays of `world` (<= 16) device pointers, each buffer holding
+ * capacity_rows rows; ranks and rows are bounds-checked on the device (a bad index sets bit 5 of
+ * the status word and is skipped).  They replace the all-to-alls of an expert-parallel layer:
+ * the caller synchronises the ranks between writing and reading (e.g. a barrier collective).
+ * No counterpart in the reference. */
+int b200moe_scatter_rows_multi(const void* src, const int64_t* src_idx, void* const* dst_bases, const int* dst_rank,
+                               const int64_t* dst_row, int64_t rows, int64_t row_bytes, int world,
+                               int64_t capacity_rows, void* stream);
+int b200moe_combine_topk_multi(const void* const* src_bases, const int* pair_rank, const int64_t* pair_row,
+                               const float* weights, void* out, int64_t tokens, int top_k, int hidden, int world,
+                               int64_t capacity_rows, void* stream);
+
+/* Buffers other processes of the node can address, for the peer-memory row movers above.
+ * alloc: cudaMalloc on the current device, zero-filled.  export: 64-byte CUDA IPC handle of a
+ * buffer from alloc.  open: maps another process's buffer for the CURRENT device of the calling
+ * process (peer access to the owning device is enabled); the returned pointer is valid in kernels
+ * of that device.  close / free undo open / alloc.  No counterpart in the reference. */
+int b200ipc_alloc(int64_t bytes, void** out);
+int b200ipc_free(void* p);
+int b200ipc_export(const void* p, void* handle64);
+int b200ipc_open(const void* handle64, void** out);
+int b200ipc_close(void* p);
+
 /* ---- integer layouts on the device ------------------------------------------------------- */
 
 /* gemm/layout.py:61-71 make_group_starts: exclusive prefix of the group sizes (padded != 0: of the

@@ -266,3 +266,32 @@ def test_device_layout_builders_match_host_layouts():
                 a = L.make_deep_gemm_grouped_layout(dev, block_m=block_m).cpu()
                 b = L.make_deep_gemm_grouped_layout(host, block_m=block_m)
                 assert a.dtype == b.dtype and torch.equal(a, b)
+
+
+def test_launch_is_cuda_graph_capturable():
+    """The entry points never synchronise or allocate, and group sizes stay on the device, so a
+    captured launch can be replayed after the sizes and the operands changed in place."""
+    from triton_grouped_gemm_b200.gemm.BF16.m_grouped_gemm_TMA import _m_grouped_gemm_launch
+
+    gen = torch.Generator().manual_seed(9)
+    g, n, k, m = 6, 256, 192, 1024
+    a = (torch.randn(m, k, generator=gen) * 0.5).bfloat16().to(DEV)
+    b = (torch.randn(g, n, k, generator=gen) * 0.5).bfloat16().to(DEV)
+    c = torch.zeros(m, n, dtype=torch.bfloat16, device=DEV)
+    sizes = torch.tensor([100, 0, 300, 24, 200, 400], dtype=torch.int64, device=DEV)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        _m_grouped_gemm_launch(a, b, c, sizes, True)          # warm-up outside capture
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        _m_grouped_gemm_launch(a, b, c, sizes, True)
+    # new routing and new activations in the same buffers, then replay
+    sizes.copy_(torch.tensor([1, 500, 0, 123, 300, 100], dtype=torch.int64))
+    a.copy_((torch.randn(m, k, generator=gen) * 0.5).bfloat16())
+    c.zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    ref = O.m_grouped_ref(a.cpu(), b.cpu(), sizes.cpu(), True)
+    assert O.rdiff(c.cpu().float(), ref.float()) < 2e-4

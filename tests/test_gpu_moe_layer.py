@@ -94,3 +94,58 @@ def test_decode_masked_variant():
             ref = O.moe_layer_ref(x[rows], idx, torch.ones(m, 1), w13, w2)
             assert O.rdiff(out[rows].float(), ref.float()) < 5e-3
         assert torch.all(out[g * m_max + m:(g + 1) * m_max] == 0)
+
+
+def test_multi_buffer_row_movers_on_one_gpu():
+    """The peer-memory dispatch / combine kernels with three ordinary buffers standing in for the
+    ranks' buffers: exact against torch indexing; an out-of-range index is reported, not followed."""
+    import ctypes
+
+    lib = _lib.load()
+    stream = torch.cuda.current_stream().cuda_stream
+    gen = torch.Generator().manual_seed(21)
+    t, k, h, world, cap = 257, 4, 512, 3, 600
+    x = torch.randn(t, h, generator=gen).to(torch.float8_e4m3fn).view(torch.uint8).to(DEV)
+    n = t * k
+    src_idx = torch.randint(0, t, (n,), generator=gen).to(DEV)
+    dst_rank = torch.randint(0, world, (n,), generator=gen, dtype=torch.int32)
+    # distinct rows per rank
+    dst_row = torch.empty(n, dtype=torch.int64)
+    for r in range(world):
+        sel = (dst_rank == r).nonzero().flatten()
+        dst_row[sel] = torch.randperm(cap, generator=gen)[: sel.numel()]
+    bufs = [torch.zeros(cap, h, dtype=torch.uint8, device=DEV) for _ in range(world)]
+    bases = (ctypes.c_void_p * world)(*[b.data_ptr() for b in bufs])
+    rank_d, row_d = dst_rank.to(DEV), dst_row.to(DEV)   # named: the kernels read them after the call returns
+    rc = lib.b200moe_scatter_rows_multi(x.data_ptr(), src_idx.data_ptr(), bases, rank_d.data_ptr(),
+                                        row_d.data_ptr(), n, h, world, cap, stream)
+    _lib.check(rc, "scatter")
+    torch.cuda.synchronize()
+    for r in range(world):
+        ref = torch.zeros(cap, h, dtype=torch.uint8)
+        sel = dst_rank == r
+        ref[dst_row[sel]] = x.cpu()[src_idx.cpu()[sel]]
+        assert torch.equal(bufs[r].cpu(), ref)
+    # combine: weighted sum of bf16 rows read from the three buffers
+    ybufs = [torch.randn(cap, h, generator=gen).bfloat16().to(DEV) for _ in range(world)]
+    ybases = (ctypes.c_void_p * world)(*[b.data_ptr() for b in ybufs])
+    w = torch.rand(t, k, generator=gen)
+    w_d = w.to(DEV)
+    out = torch.empty(t, h, dtype=torch.bfloat16, device=DEV)
+    rc = lib.b200moe_combine_topk_multi(ybases, rank_d.data_ptr(), row_d.data_ptr(), w_d.data_ptr(), out.data_ptr(),
+                                        t, k, h, world, cap, stream)
+    _lib.check(rc, "combine")
+    rows = torch.stack([ybufs[int(r)].cpu()[int(i)] for r, i in zip(dst_rank.tolist(), dst_row.tolist())]).float()
+    ref = (rows.view(t, k, h) * w[:, :, None]).sum(1)
+    assert (out.cpu().float() - ref).abs().max() <= 2e-2 * ref.abs().max()
+    assert O.rdiff(out.cpu().float(), ref) < 3e-3
+    # a row beyond the capacity is skipped and flagged
+    bad_row = dst_row.clone()
+    bad_row[5] = cap + 7
+    bad_row_d = bad_row.to(DEV)
+    before = bufs[int(dst_rank[5])].clone()
+    rc = lib.b200moe_scatter_rows_multi(x.data_ptr(), src_idx.data_ptr(), bases, rank_d.data_ptr(),
+                                        bad_row_d.data_ptr(), n, h, world, cap, stream)
+    _lib.check(rc, "scatter")
+    assert _lib.device_status() == 1 << 5
+    assert torch.equal(bufs[int(dst_rank[5])], before)   # same data everywhere else, nothing new written

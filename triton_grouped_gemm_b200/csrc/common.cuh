@@ -29,6 +29,7 @@ enum : unsigned {
   kDevTimeoutEpilogue = 1u << 2,
   kDevTimeoutPromote = 1u << 3,
   kDevBadGroupSize = 1u << 4,
+  kDevBadRowIndex = 1u << 5,  // a row mover was given a rank or row outside its buffers (access skipped)
 };
 
 // implemented in api.cu

@@ -67,9 +67,154 @@ combine_topk_kernel(const uint4* __restrict__ y, const long long* __restrict__ p
   }
 }
 
+// ---- the same two movers over several buffers: one per rank of an expert-parallel group, the
+// other ranks' buffers being peer memory mapped into this process.  The dispatch kernel stores
+// each row straight into the owning rank's receive buffer at its final position and the combine
+// kernel loads each (token, k) result from the rank that computed it, so a step needs no
+// all-to-all, no send-side gather and no staging copy of the returned rows; the bytes cross
+// NVLink once, as plain stores / loads issued by these kernels.  Every access is bounds-checked
+// (rank < world, row < capacity): a bad index sets a status bit and is skipped, it cannot fault
+// a peer.
+constexpr int kMaxPeers = 16;
+struct PeerBases {
+  void* base[kMaxPeers];
+};
+
+// bases[rank[i]][row[i], :] = src[src_idx[i], :]
+__global__ void __launch_bounds__(kMoeThreads)
+scatter_rows_multi_kernel(const uint4* __restrict__ src, const long long* __restrict__ src_idx, PeerBases bases,
+                          const int* __restrict__ rank, const long long* __restrict__ row, long long rows,
+                          int row_vecs, int world, long long capacity_rows, unsigned* status) {
+  const int lane = threadIdx.x & 31;
+  const long long warp = (static_cast<long long>(blockIdx.x) * kMoeThreads + threadIdx.x) >> 5;
+  const long long warps = (static_cast<long long>(gridDim.x) * kMoeThreads) >> 5;
+  for (long long r = warp; r < rows; r += warps) {
+    const int dst_rank = rank[r];
+    const long long dst_row = row[r];
+    if (dst_rank < 0 || dst_rank >= world || dst_row < 0 || dst_row >= capacity_rows) {
+      if (lane == 0 && status) atomicOr(status, kDevBadRowIndex);
+      continue;
+    }
+    const uint4* s = src + src_idx[r] * row_vecs;
+    uint4* d = static_cast<uint4*>(bases.base[dst_rank]) + dst_row * row_vecs;
+    int v = lane;
+    for (; v + 96 < row_vecs; v += 128) {
+      const uint4 a = __ldg(s + v), b = __ldg(s + v + 32), c = __ldg(s + v + 64), e = __ldg(s + v + 96);
+      d[v] = a;
+      d[v + 32] = b;
+      d[v + 64] = c;
+      d[v + 96] = e;
+    }
+    for (; v < row_vecs; v += 32) d[v] = __ldg(s + v);
+  }
+}
+
+// out[t, :] = bf16( sum_k w[t,k] * bases[rank[t,k]][row[t,k], :] ), fp32 accumulation in k order
+__global__ void __launch_bounds__(kMoeThreads)
+combine_topk_multi_kernel(PeerBases bases, const int* __restrict__ rank, const long long* __restrict__ row,
+                          const float* __restrict__ w, uint4* __restrict__ out, long long tokens, int top_k,
+                          int row_vecs, int world, long long capacity_rows, unsigned* status) {
+  const int lane = threadIdx.x & 31;
+  const long long warp = (static_cast<long long>(blockIdx.x) * kMoeThreads + threadIdx.x) >> 5;
+  const long long warps = (static_cast<long long>(gridDim.x) * kMoeThreads) >> 5;
+  for (long long t = warp; t < tokens; t += warps) {
+    for (int v = lane; v < row_vecs; v += 32) {
+      float acc[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+      for (int k = 0; k < top_k; ++k) {
+        const int src_rank = rank[t * top_k + k];
+        const long long src_row = row[t * top_k + k];
+        if (src_rank < 0 || src_rank >= world || src_row < 0 || src_row >= capacity_rows) {
+          if (v == lane && lane == 0 && status) atomicOr(status, kDevBadRowIndex);
+          continue;
+        }
+        // peer memory is not read-only for the whole grid's lifetime in general: plain loads
+        const uint4 q = *(static_cast<const uint4*>(bases.base[src_rank]) + src_row * row_vecs + v);
+        const float wk = w[t * top_k + k];
+        const uint32_t p[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          acc[2 * e] = fmaf(wk, __uint_as_float(p[e] << 16), acc[2 * e]);
+          acc[2 * e + 1] = fmaf(wk, __uint_as_float(p[e] & 0xFFFF0000u), acc[2 * e + 1]);
+        }
+      }
+      uint32_t o[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * e], acc[2 * e + 1]);
+        o[e] = *reinterpret_cast<uint32_t*>(&h);
+      }
+      out[t * row_vecs + v] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+  }
+}
+
+static int fill_bases(PeerBases* out, const void* const* bases, int world, const char* who) {
+  B200_REQUIRE(world >= 1 && world <= kMaxPeers, "%s: world (%d) must be in [1, %d]", who, world, kMaxPeers);
+  B200_REQUIRE(bases, "%s: null pointer table", who);
+  for (int i = 0; i < kMaxPeers; ++i) out->base[i] = nullptr;
+  for (int i = 0; i < world; ++i) {
+    B200_REQUIRE(bases[i] && (reinterpret_cast<uintptr_t>(bases[i]) & 15) == 0,
+                 "%s: buffer of rank %d is null or not 16-byte aligned", who, i);
+    out->base[i] = const_cast<void*>(bases[i]);
+  }
+  return 0;
+}
+
 }  // namespace b200
 
 extern "C" {
+
+int b200moe_scatter_rows_multi(const void* src, const int64_t* src_idx, void* const* dst_bases, const int* dst_rank,
+                               const int64_t* dst_row, int64_t rows, int64_t row_bytes, int world,
+                               int64_t capacity_rows, void* stream) {
+  using namespace b200;
+  const char* who = "b200moe_scatter_rows_multi";
+  B200_REQUIRE(rows >= 0 && row_bytes >= 0 && capacity_rows >= 0, "%s: negative size", who);
+  if (rows == 0 || row_bytes == 0) return 0;
+  B200_REQUIRE(src && src_idx && dst_rank && dst_row, "%s: null pointer", who);
+  B200_REQUIRE(row_bytes % 16 == 0 && row_bytes / 16 < (1ll << 30), "%s: row_bytes (%lld) must be a multiple of 16", who,
+               (long long)row_bytes);
+  B200_REQUIRE((reinterpret_cast<uintptr_t>(src) & 15) == 0, "%s: src must be 16-byte aligned", who);
+  PeerBases pb;
+  int rc = fill_bases(&pb, const_cast<const void* const*>(dst_bases), world, who);
+  if (rc) return rc;
+  const int sms = sm_count();
+  B200_REQUIRE(sms > 0, "%s: no CUDA device", who);
+  long long blocks = (rows + kMoeThreads / 32 - 1) / (kMoeThreads / 32);
+  if (blocks > 16ll * sms) blocks = 16ll * sms;
+  scatter_rows_multi_kernel<<<static_cast<int>(blocks), kMoeThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(src), reinterpret_cast<const long long*>(src_idx), pb, dst_rank,
+      reinterpret_cast<const long long*>(dst_row), rows, static_cast<int>(row_bytes / 16), world, capacity_rows,
+      device_status_ptr());
+  B200_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int b200moe_combine_topk_multi(const void* const* src_bases, const int* pair_rank, const int64_t* pair_row,
+                               const float* weights, void* out, int64_t tokens, int top_k, int hidden, int world,
+                               int64_t capacity_rows, void* stream) {
+  using namespace b200;
+  const char* who = "b200moe_combine_topk_multi";
+  B200_REQUIRE(tokens >= 0 && top_k > 0 && hidden >= 0 && capacity_rows >= 0, "%s: bad size", who);
+  if (tokens == 0 || hidden == 0) return 0;
+  B200_REQUIRE(pair_rank && pair_row && weights && out, "%s: null pointer", who);
+  B200_REQUIRE(hidden % 8 == 0, "%s: hidden (%d) must be a multiple of 8", who, hidden);
+  B200_REQUIRE((reinterpret_cast<uintptr_t>(out) & 15) == 0, "%s: out must be 16-byte aligned", who);
+  PeerBases pb;
+  int rc = fill_bases(&pb, src_bases, world, who);
+  if (rc) return rc;
+  const int sms = sm_count();
+  B200_REQUIRE(sms > 0, "%s: no CUDA device", who);
+  long long blocks = (tokens + kMoeThreads / 32 - 1) / (kMoeThreads / 32);
+  if (blocks > 16ll * sms) blocks = 16ll * sms;
+  combine_topk_multi_kernel<<<static_cast<int>(blocks), kMoeThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      pb, pair_rank, reinterpret_cast<const long long*>(pair_row), weights, static_cast<uint4*>(out), tokens, top_k,
+      hidden / 8, world, capacity_rows, device_status_ptr());
+  B200_CUDA(cudaGetLastError());
+  return 0;
+}
 
 int b200moe_gather_rows(const void* src, const int64_t* idx, void* dst, int64_t rows, int64_t row_bytes,
                         void* stream) {

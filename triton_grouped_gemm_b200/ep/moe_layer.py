@@ -21,13 +21,17 @@ from .dispatch import combine, dispatch, dispatch_chunk_async, make_chunked_plan
 
 class Fp8MoELayer:
     def __init__(self, w13: torch.Tensor, w2: torch.Tensor, num_experts: int,
-                 group: Optional[dist.ProcessGroup] = None, chunks: int = 4, comm_sms: int = 16):
+                 group: Optional[dist.ProcessGroup] = None, chunks: int = 4, comm_sms: int = 16,
+                 transport: str = "nccl", capacity_factor: float = 1.5, tokens_per_rank: int = 0, top_k: int = 0):
         """w13 [E_local, 2*I, H] (gate rows then up rows), w2 [E_local, H, I], bf16, this rank's experts.
         With more than one rank the expert GEMMs consume rows in the order the all-to-all delivers
         them (every [source rank][expert] block is a row group of its own, mapped to its expert's
         weights), so nothing is permuted on the expert side.  ``chunks`` > 1 pipelines the step
         over groups of local experts: the all-to-alls of neighbouring chunks run beside the expert
-        GEMMs, which then leave ``comm_sms`` SMs to the collective's kernels."""
+        GEMMs, which then leave ``comm_sms`` SMs to the collective's kernels.
+        ``transport="p2p"`` replaces the all-to-alls by kernels that store / load rows in the
+        other ranks' memory directly (``ep/p2p.py``); it needs ``tokens_per_rank`` and ``top_k`` to
+        size its buffers: ``capacity_factor`` x the mean number of rows a rank receives."""
         assert w13.dim() == 3 and w2.dim() == 3 and w13.shape[0] == w2.shape[0]
         self.group = group
         self.num_experts = num_experts
@@ -42,9 +46,22 @@ class Fp8MoELayer:
         self.world = world
         self.chunks = chunks if world > 1 else 1
         self.comm_sms = comm_sms
+        assert transport in ("nccl", "p2p")
+        self.transport = transport if world > 1 else "nccl"
+        if self.transport == "p2p":
+            from .p2p import PeerBuffer
+
+            assert tokens_per_rank > 0 and top_k > 0, "the p2p transport sizes its buffers from tokens_per_rank and top_k"
+            cap = (int(tokens_per_rank * top_k * capacity_factor) + 255) // 256 * 256
+            dev = w13.device
+            self.recv8 = PeerBuffer(cap, self.hidden, torch.uint8, dev, group)
+            self.recvs = PeerBuffer(cap, (self.hidden + 127) // 128, torch.float32, dev, group)
+            self.ybuf = PeerBuffer(cap, self.hidden, torch.bfloat16, dev, group)
+            self._flag = torch.zeros(1, dtype=torch.int32, device=dev)
 
     def experts(self, x8: torch.Tensor, xs: torch.Tensor, size_per_group: torch.Tensor,
-                group_to_expert: Optional[torch.Tensor] = None, num_sms: int = -1) -> torch.Tensor:
+                group_to_expert: Optional[torch.Tensor] = None, num_sms: int = -1,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Rows grouped by local expert: [R, H] fp8 + scales -> [R, H] bf16.  With
         ``group_to_expert`` (int32) the row groups are arbitrary blocks, block i using the
         weights of local expert ``group_to_expert[i]``."""
@@ -52,11 +69,28 @@ class Fp8MoELayer:
                                        group_to_b=group_to_expert)
         a8, a_s = swiglu_per_token_cast_to_fp8(h)
         return m_grouped_fp8_block_scaled((a8, a_s), self.w2, size_per_group, num_sms=num_sms,
-                                          group_to_b=group_to_expert)
+                                          group_to_b=group_to_expert, out=out)
+
+    def _forward_p2p(self, x8, xs, topk_idx, topk_weight) -> torch.Tensor:
+        """All ranks: scatter rows into their owners' buffers | barrier | GEMMs on the local
+        buffers | barrier | weighted sum reading the owners' results."""
+        from .p2p import combine_rows, make_peer_plan, scatter_rows
+
+        plan = make_peer_plan(topk_idx, self.num_experts, self.group, self.recv8.capacity)
+        scatter_rows(plan, x8, self.recv8)
+        scatter_rows(plan, xs, self.recvs)
+        dist.all_reduce(self._flag, group=self.group)       # every rank's rows have landed everywhere
+        r = plan.rows_here
+        self.experts(self.recv8.local[:r].view(torch.float8_e4m3fn), self.recvs.local[:r], plan.block_sizes,
+                     group_to_expert=plan.block_expert, out=self.ybuf.local[:r])
+        dist.all_reduce(self._flag, group=self.group)       # every rank's results are written
+        return combine_rows(plan, self.ybuf, topk_weight)
 
     def forward(self, x: torch.Tensor, topk_idx: torch.Tensor, topk_weight: torch.Tensor) -> torch.Tensor:
         """x [T, H] bf16, topk_idx/topk_weight [T, k] -> [T, H] bf16."""
         x8, xs = per_token_cast_to_fp8(x.contiguous())
+        if self.transport == "p2p":
+            return self._forward_p2p(x8, xs, topk_idx, topk_weight)
         if self.world > 1:
             return self._forward_pipelined(x8, xs, topk_idx, topk_weight)
         plan = make_plan(topk_idx, self.num_experts, self.group)
