@@ -141,3 +141,71 @@ def test_two_gloo_ranks_chunked_pipeline_plan():
             p.join(120)
             assert p.exitcode == 0
         assert results.get(0) is True and results.get(1) is True
+
+
+def _peer_plan_worker(rank, world, port, results):
+    """Index arithmetic of the peer-memory transport: every rank's plan is gathered on every rank
+    and the stores / loads the kernels would do are replayed with plain indexing."""
+    from triton_grouped_gemm_b200.ep.p2p import make_peer_plan
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        t, e, k, h, cap = 23 + 9 * rank, 8, 3, 4, 200
+        e_loc = e // world
+        idx, w = synthetic_routing(t, e, k, seed=30 + rank)
+        gen = torch.Generator().manual_seed(300 + rank)
+        x = torch.randn(t, h, generator=gen)
+        plan = make_peer_plan(idx, e, dist.group.WORLD, cap)
+        mine = dict(x=x, idx=idx, w=w, token_of_pair=plan.token_of_pair, dst_rank=plan.dst_rank, dst_row=plan.dst_row,
+                    pair_rank=plan.pair_rank, pair_row=plan.pair_row, rows_here=plan.rows_here,
+                    block_sizes=plan.block_sizes, block_expert=plan.block_expert)
+        everyone = [None] * world
+        dist.all_gather_object(everyone, mine)
+        # replay the scatter of all ranks into all ranks' buffers
+        bufs = [torch.full((cap, h), float("nan")) for _ in range(world)]
+        written = [torch.zeros(cap, dtype=torch.int32) for _ in range(world)]
+        owner_expert = [torch.full((cap,), -1, dtype=torch.int64) for _ in range(world)]
+        for src, p in enumerate(everyone):
+            flat = p["idx"].reshape(-1)
+            order = torch.argsort(flat, stable=True)
+            for i in range(p["token_of_pair"].numel()):
+                d, r = int(p["dst_rank"][i]), int(p["dst_row"][i])
+                bufs[d][r] = p["x"][int(p["token_of_pair"][i])]
+                written[d][r] += 1
+                owner_expert[d][r] = int(flat[order[i]])
+        ok = True
+        for d, p in enumerate(everyone):
+            r = p["rows_here"]
+            ok &= bool((written[d][:r] == 1).all()) and bool((written[d][r:] == 0).all())   # dense, no collisions
+            ok &= int(p["block_sizes"].sum()) == r and p["block_sizes"].numel() == world * e_loc
+            # rows of block b (source-major, expert-minor) all belong to expert d*e_loc + block_expert[b]
+            start = 0
+            for b, n in enumerate(p["block_sizes"].tolist()):
+                ok &= bool((owner_expert[d][start:start + n] == d * e_loc + int(p["block_expert"][b])).all())
+                start += n
+        # experts: row * (global expert id + 1); combine reads (pair_rank, pair_row)
+        ybufs = [bufs[d] * (owner_expert[d].clamp(min=0).float()[:, None] + 1.0) for d in range(world)]
+        me = everyone[rank]
+        rows = torch.stack([ybufs[int(r)][int(i)] for r, i in zip(me["pair_rank"].tolist(), me["pair_row"].tolist())])
+        out = (rows.view(t, k, h) * w[:, :, None]).sum(1)
+        ok &= torch.allclose(out, _reference(x, idx, w), atol=1e-5)
+        results[rank] = bool(ok)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_gloo_ranks_peer_memory_plan():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    with ctx.Manager() as mgr:
+        results = mgr.dict()
+        procs = [ctx.Process(target=_peer_plan_worker, args=(r, 2, port, results)) for r in range(2)]
+        for p in procs:
+            p.start()
+        for p in procs:
+            p.join(120)
+            assert p.exitcode == 0
+        assert results.get(0) is True and results.get(1) is True

@@ -105,8 +105,9 @@ def make_peer_plan(topk_idx: torch.Tensor, num_experts: int, group, capacity_row
     flat = topk_idx.reshape(-1).to(torch.int64)
     send_order = torch.argsort(flat, stable=True)
     counts = torch.bincount(flat, minlength=num_experts)
-    counts_all = torch.empty((world, num_experts), dtype=counts.dtype, device=dev)
-    dist.all_gather_into_tensor(counts_all, counts, group=group)
+    counts_flat = torch.empty(world * num_experts, dtype=counts.dtype, device=dev)
+    dist.all_gather_into_tensor(counts_flat, counts, group=group)
+    counts_all = counts_flat.view(world, num_experts)
     # arrival layout at destination d: blocks (source s, local expert j) in that order
     by_dest = counts_all.view(world, world, e_loc).permute(1, 0, 2).contiguous()      # [d, s, j]
     flat_blocks = by_dest.view(world, world * e_loc)
