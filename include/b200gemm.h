@@ -227,6 +227,15 @@ int b200moe_gather_rows(const void* src, const int64_t* idx, void* dst, int64_t 
 int b200moe_combine_topk(const void* y, const int64_t* pos, const float* weights, void* out, int64_t tokens, int top_k,
                          int hidden, void* stream);
 
+/* Routing plan of an MoE step: counting sort of the (token, k) pairs by expert.
+ * expert int64 [n] with values in [0, num_experts), num_experts <= 1024.  counts int32 [E]: pairs
+ * per expert; cursor int32 [E]: scratch (ends as the END of each expert's range); order int64 [n]:
+ * pair indices grouped by expert (expert e's pairs at [sum(counts[:e]), +counts[e]), order inside
+ * a range unspecified); pos int64 [n] = order^-1.  The role of the sort in the vendored baseline's
+ * permute (grouped_gemm/csrc/permute.cu:504-690), without a comparison sort. */
+int b200moe_route_plan(const int64_t* expert, int64_t n, int num_experts, int* counts, int* cursor, int64_t* order,
+                       int64_t* pos, void* stream);
+
 /* The same row movers over the buffers of several ranks (peer memory mapped into this process):
  * dst_bases[dst_rank[i]][dst_row[i], :] = src[src_idx[i], :], and
  * out[t, :] = bf16(sum_k weights[t,k] * src_bases[pair_rank[t,k]][pair_row[t,k], :]).

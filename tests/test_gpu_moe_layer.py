@@ -51,13 +51,23 @@ def test_gather_and_combine_kernels_are_exact():
     xs = torch.rand(t, h // 128, generator=gen)
     plan_c = make_plan(idx, e)
     plan_g = make_plan(idx.to(DEV), e)
-    # gather of byte rows and of fp32 scale rows: identical to torch indexing on the host
-    assert torch.equal(dispatch(plan_g, x8.to(DEV)).cpu().view(torch.uint8), dispatch(plan_c, x8).view(torch.uint8))
-    assert torch.equal(dispatch(plan_g, xs.to(DEV)).cpu(), dispatch(plan_c, xs))
-    # weighted top-k sum: fp32 accumulation, one rounding -> agrees with the host formula to 1 bf16 ulp
-    y = torch.randn(t * k, h, generator=gen).bfloat16()
-    out_g = combine(plan_g, y.to(DEV), w.to(DEV)).cpu()
-    out_c = combine(plan_c, y, w)
+    # the device plan (counting-sort kernels) groups the pairs by expert like the host's stable sort,
+    # in an unspecified order inside each expert: same counts, a permutation, expert ids ascending
+    order_g = plan_g.send_order.cpu()
+    assert plan_g.size_per_group.cpu().tolist() == plan_c.size_per_group.tolist()
+    assert torch.equal(torch.sort(order_g).values, torch.arange(t * k))
+    experts_in_order = idx.reshape(-1)[order_g]
+    assert bool((experts_in_order[1:] >= experts_in_order[:-1]).all())
+    assert torch.equal(plan_g.pos.cpu()[order_g], torch.arange(t * k))
+    # gather of byte rows and of fp32 scale rows: identical to torch indexing with the plan's order
+    token_of_row = order_g // k
+    assert torch.equal(dispatch(plan_g, x8.to(DEV)).cpu().view(torch.uint8), x8.view(torch.uint8)[token_of_row])
+    assert torch.equal(dispatch(plan_g, xs.to(DEV)).cpu(), xs[token_of_row])
+    # weighted top-k sum: fp32 accumulation, one rounding -> agrees with the host formula to 1 bf16 ulp.
+    # y is given in each plan's own row order: row i belongs to pair send_order[i]
+    y_pairs = torch.randn(t * k, h, generator=gen).bfloat16()        # indexed by pair (t*k + kk)
+    out_g = combine(plan_g, y_pairs[order_g].to(DEV), w.to(DEV)).cpu()
+    out_c = combine(plan_c, y_pairs[plan_c.send_order], w)
     assert O.rdiff(out_g.float(), out_c.float()) < 1e-3
     assert (out_g.float() - out_c.float()).abs().max() <= 2 ** -7 * out_c.float().abs().max()
 

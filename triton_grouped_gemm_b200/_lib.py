@@ -50,6 +50,7 @@ _SIGNATURES = {
                                             c_void_p, c_int, c_int64, c_int, c_int, c_int, c_void_p],
     "b200gemm_fp8_m_grouped_masked_block": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                             c_int, c_int, c_int, c_int, c_void_p],
+    "b200moe_route_plan": [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     "b200moe_scatter_rows_multi": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int64,
                                    c_void_p],
     "b200moe_combine_topk_multi": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int,

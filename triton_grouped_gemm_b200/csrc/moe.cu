@@ -67,6 +67,90 @@ combine_topk_kernel(const uint4* __restrict__ y, const long long* __restrict__ p
   }
 }
 
+// ---- routing plan: counting sort of the (token, k) pairs by expert --------------------------
+// expert[i] in [0, num_experts) for i < n.  Produces counts[e], order (pair indices grouped by
+// expert: expert e's pairs occupy [start_e, start_e + counts[e])) and pos = order^-1.  The order
+// inside an expert's range is not specified (rows of a group are independent in the GEMM), which
+// allows atomics: a block histograms its slice in shared memory, reserves one range per expert
+// with a single global atomic each, and hands out positions from shared-memory counters.
+constexpr int kPlanThreads = 256;
+constexpr int kPlanItems = 8;        // pairs per thread
+constexpr int kPlanMaxExperts = 1024;
+
+__global__ void __launch_bounds__(kPlanThreads)
+route_count_kernel(const long long* __restrict__ expert, long long n, int num_experts, int* __restrict__ counts) {
+  __shared__ int hist[kPlanMaxExperts];
+  for (int e = threadIdx.x; e < num_experts; e += kPlanThreads) hist[e] = 0;
+  __syncthreads();
+  const long long base = static_cast<long long>(blockIdx.x) * kPlanThreads * kPlanItems;
+#pragma unroll
+  for (int j = 0; j < kPlanItems; ++j) {
+    const long long i = base + j * kPlanThreads + threadIdx.x;
+    if (i < n) {
+      const long long e = expert[i];
+      if (e >= 0 && e < num_experts) atomicAdd(&hist[e], 1);
+    }
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < num_experts; e += kPlanThreads)
+    if (hist[e]) atomicAdd(&counts[e], hist[e]);
+}
+
+// one block: cursor[e] = exclusive prefix of counts (the start of expert e's range)
+__global__ void __launch_bounds__(kPlanMaxExperts)
+route_scan_kernel(const int* __restrict__ counts, int num_experts, int* __restrict__ cursor) {
+  __shared__ int tmp[kPlanMaxExperts];
+  const int e = threadIdx.x;
+  tmp[e] = e < num_experts ? counts[e] : 0;
+  __syncthreads();
+  for (int off = 1; off < kPlanMaxExperts; off <<= 1) {
+    const int v = e >= off ? tmp[e - off] : 0;
+    __syncthreads();
+    tmp[e] += v;
+    __syncthreads();
+  }
+  if (e < num_experts) cursor[e] = tmp[e] - counts[e];
+}
+
+__global__ void __launch_bounds__(kPlanThreads)
+route_scatter_kernel(const long long* __restrict__ expert, long long n, int num_experts, int* __restrict__ cursor,
+                     long long* __restrict__ order, long long* __restrict__ pos, unsigned* status) {
+  __shared__ int hist[kPlanMaxExperts];   // first: this block's count per expert; then: next free position
+  for (int e = threadIdx.x; e < num_experts; e += kPlanThreads) hist[e] = 0;
+  __syncthreads();
+  const long long base = static_cast<long long>(blockIdx.x) * kPlanThreads * kPlanItems;
+  long long ex[kPlanItems];
+#pragma unroll
+  for (int j = 0; j < kPlanItems; ++j) {
+    const long long i = base + j * kPlanThreads + threadIdx.x;
+    ex[j] = -1;
+    if (i < n) {
+      const long long e = expert[i];
+      if (e >= 0 && e < num_experts) {
+        ex[j] = e;
+        atomicAdd(&hist[e], 1);
+      } else if (status) {
+        atomicOr(status, kDevBadRowIndex);
+      }
+    }
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < num_experts; e += kPlanThreads) {
+    const int c = hist[e];
+    hist[e] = c ? atomicAdd(&cursor[e], c) : 0;  // start of this block's range inside expert e's range
+  }
+  __syncthreads();
+#pragma unroll
+  for (int j = 0; j < kPlanItems; ++j) {
+    if (ex[j] >= 0) {
+      const long long i = base + j * kPlanThreads + threadIdx.x;
+      const long long p = atomicAdd(&hist[ex[j]], 1);
+      order[p] = i;
+      pos[i] = p;
+    }
+  }
+}
+
 // ---- the same two movers over several buffers: one per rank of an expert-parallel group, the
 // other ranks' buffers being peer memory mapped into this process.  The dispatch kernel stores
 // each row straight into the owning rank's receive buffer at its final position and the combine
@@ -165,6 +249,33 @@ static int fill_bases(PeerBases* out, const void* const* bases, int world, const
 }  // namespace b200
 
 extern "C" {
+
+int b200moe_route_plan(const int64_t* expert, int64_t n, int num_experts, int* counts, int* cursor, int64_t* order,
+                       int64_t* pos, void* stream_v) {
+  using namespace b200;
+  const char* who = "b200moe_route_plan";
+  B200_REQUIRE(n >= 0 && num_experts > 0 && num_experts <= kPlanMaxExperts, "%s: num_experts (%d) must be in [1, %d]",
+               who, num_experts, kPlanMaxExperts);
+  B200_REQUIRE(counts && cursor, "%s: null pointer", who);
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  B200_CUDA(cudaMemsetAsync(counts, 0, sizeof(int) * num_experts, stream));
+  if (n > 0) {
+    B200_REQUIRE(expert && order && pos, "%s: null pointer", who);
+    const long long per_block = static_cast<long long>(kPlanThreads) * kPlanItems;
+    const long long blocks = (n + per_block - 1) / per_block;
+    B200_REQUIRE(blocks < (1ll << 31), "%s: too many pairs", who);
+    route_count_kernel<<<static_cast<int>(blocks), kPlanThreads, 0, stream>>>(
+        reinterpret_cast<const long long*>(expert), n, num_experts, counts);
+    route_scan_kernel<<<1, kPlanMaxExperts, 0, stream>>>(counts, num_experts, cursor);
+    route_scatter_kernel<<<static_cast<int>(blocks), kPlanThreads, 0, stream>>>(
+        reinterpret_cast<const long long*>(expert), n, num_experts, cursor, reinterpret_cast<long long*>(order),
+        reinterpret_cast<long long*>(pos), device_status_ptr());
+  } else {
+    route_scan_kernel<<<1, kPlanMaxExperts, 0, stream>>>(counts, num_experts, cursor);
+  }
+  B200_CUDA(cudaGetLastError());
+  return 0;
+}
 
 int b200moe_scatter_rows_multi(const void* src, const int64_t* src_idx, void* const* dst_bases, const int* dst_rank,
                                const int64_t* dst_row, int64_t rows, int64_t row_bytes, int world,

@@ -30,6 +30,7 @@ class DispatchPlan:
     recv_splits: List[int]          # rows received from each rank
     recv_to_expert_major: torch.Tensor  # [R] permutation: expert-major row i = received row perm[i]
     size_per_group: torch.Tensor    # [experts_per_rank] rows per local expert (int64, on the data device)
+    pos: Optional[torch.Tensor] = None  # [T*k] position of pair (t, k) in send order (send_order^-1)
 
     @property
     def rows_received(self) -> int:
@@ -52,6 +53,30 @@ def _gather_rows(rows: torch.Tensor, idx: torch.Tensor) -> torch.Tensor:
     return rows[idx]
 
 
+def route_plan(keys: torch.Tensor, num_keys: int):
+    """Counting sort of ``keys`` (int64, values in [0, num_keys)): returns (counts int64 [num_keys],
+    order int64 [n] - indices grouped by key, pos = order^-1).  On CUDA one pass of the library's
+    routing-plan kernels (order inside a key's range unspecified); on the host a stable argsort."""
+    n = keys.numel()
+    if keys.is_cuda and num_keys <= 1024:
+        from .. import _lib
+
+        keys = keys.contiguous()
+        counts = torch.empty(num_keys, dtype=torch.int32, device=keys.device)
+        cursor = torch.empty(num_keys, dtype=torch.int32, device=keys.device)
+        order = torch.empty(n, dtype=torch.int64, device=keys.device)
+        pos = torch.empty(n, dtype=torch.int64, device=keys.device)
+        with torch.cuda.device(keys.device):
+            rc = _lib.load().b200moe_route_plan(keys.data_ptr(), n, num_keys, counts.data_ptr(), cursor.data_ptr(),
+                                                order.data_ptr(), pos.data_ptr(), _lib.stream_ptr(keys.device))
+        _lib.check(rc, "b200moe_route_plan")
+        return counts.to(torch.int64), order, pos
+    order = torch.argsort(keys, stable=True)
+    pos = torch.empty_like(order)
+    pos[order] = torch.arange(n, device=keys.device)
+    return torch.bincount(keys, minlength=num_keys), order, pos
+
+
 def _all_to_all(out: torch.Tensor, inp: torch.Tensor, out_splits, in_splits, group) -> None:
     if group is None or dist.get_world_size(group) == 1:
         out.copy_(inp)
@@ -67,8 +92,12 @@ def make_plan(topk_idx: torch.Tensor, num_experts: int, group: Optional[dist.Pro
     t, k = topk_idx.shape
     dev = topk_idx.device
     flat = topk_idx.reshape(-1).to(torch.int64)
-    send_order = torch.argsort(flat, stable=True)
-    counts = torch.bincount(flat, minlength=num_experts)            # rows per destination expert
+    counts, send_order, pos = route_plan(flat, num_experts)          # rows per destination expert
+    if world == 1:
+        # one rank: the send order already is expert-major; nothing to exchange, no host synchronisation
+        return DispatchPlan(world=1, experts_per_rank=e_loc, num_tokens=t, top_k=k, send_order=send_order,
+                            send_splits=[t * k], recv_splits=[t * k],
+                            recv_to_expert_major=torch.arange(t * k, device=dev), size_per_group=counts, pos=pos)
     recv_counts = torch.empty_like(counts)                           # [world * e_loc]: from rank r, expert e
     _all_to_all(recv_counts, counts, None, None, group)
     send_splits = counts.view(world, e_loc).sum(1).tolist()
@@ -86,7 +115,7 @@ def make_plan(topk_idx: torch.Tensor, num_experts: int, group: Optional[dist.Pro
     perm = blk_starts[row_block] + (torch.arange(total, device=dev) - out_starts[row_block])
     return DispatchPlan(world=world, experts_per_rank=e_loc, num_tokens=t, top_k=k, send_order=send_order,
                         send_splits=send_splits, recv_splits=recv_splits, recv_to_expert_major=perm,
-                        size_per_group=recv_matrix.sum(0).to(torch.int64))
+                        size_per_group=recv_matrix.sum(0).to(torch.int64), pos=pos)
 
 
 @dataclass
@@ -107,6 +136,7 @@ class ChunkedPlan:
     size_per_group: List[torch.Tensor]  # per chunk: [ec] rows per local expert of the chunk (int64)
     block_sizes: List[torch.Tensor]     # per chunk: [world*ec] rows of each (source rank, expert) block, arrival order
     block_expert: List[torch.Tensor]    # per chunk: [world*ec] local expert (0..e_loc) of each block, int32
+    pos: Optional[torch.Tensor] = None  # [T*k] position of pair (t, k) in send order
 
 
 def make_chunked_plan(topk_idx: torch.Tensor, num_experts: int, group: Optional[dist.ProcessGroup],
@@ -126,8 +156,11 @@ def make_chunked_plan(topk_idx: torch.Tensor, num_experts: int, group: Optional[
     local = flat - rank_of * e_loc
     chunk_of = local // ec
     key = chunk_of * (world * ec) + rank_of * ec + (local - chunk_of * ec)
-    send_order = torch.argsort(key, stable=True)
-    counts = torch.bincount(flat, minlength=num_experts)                      # [world * e_loc]
+    counts_by_key, send_order, pos = route_plan(key, num_experts)
+    # key of expert e = (rank r, chunk c, j): c * (world * ec) + r * ec + j
+    e_ids = torch.arange(num_experts, device=dev)
+    e_rank, e_local = e_ids // e_loc, e_ids % e_loc
+    counts = counts_by_key[(e_local // ec) * (world * ec) + e_rank * ec + e_local % ec]   # [world * e_loc]
     recv_counts = torch.empty_like(counts)                                     # from rank r, local expert e
     _all_to_all(recv_counts, counts, None, None, group)
     send_m = counts.view(world, chunks, ec).sum(-1).t().contiguous()           # [chunks, world]
@@ -159,7 +192,7 @@ def make_chunked_plan(topk_idx: torch.Tensor, num_experts: int, group: Optional[
     return ChunkedPlan(world=world, experts_per_rank=e_loc, chunks=chunks, num_tokens=t, top_k=k,
                        send_order=send_order, send_offsets=send_offsets, send_splits=send_splits,
                        recv_splits=recv_splits, recv_to_expert_major=perms, size_per_group=sizes,
-                       block_sizes=block_sizes, block_expert=block_expert)
+                       block_sizes=block_sizes, block_expert=block_expert, pos=pos)
 
 
 def dispatch_chunk_async(plan: ChunkedPlan, c: int, payloads, group):
@@ -207,8 +240,10 @@ def combine(plan: DispatchPlan, expert_rows: torch.Tensor, topk_weight: torch.Te
                           device=expert_rows.device)
         _all_to_all(ret, back, plan.send_splits, plan.recv_splits, group)
     # position of pair (t, k) among the returned rows
-    pos = torch.empty_like(plan.send_order)
-    pos[plan.send_order] = torch.arange(pos.numel(), device=pos.device)
+    pos = plan.pos
+    if pos is None:
+        pos = torch.empty_like(plan.send_order)
+        pos[plan.send_order] = torch.arange(pos.numel(), device=pos.device)
     if ret.is_cuda and ret.dtype == torch.bfloat16 and ret.shape[1] % 8 == 0:
         from .. import _lib
 

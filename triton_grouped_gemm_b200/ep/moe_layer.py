@@ -125,9 +125,7 @@ class Fp8MoELayer:
                                                    async_op=True), y, keep, recvs))
         for w, *_ in pending:
             w.wait()
-        # position of pair (t, k) among the returned rows (send order is chunk-major)
-        pos = torch.empty_like(plan.send_order)
-        pos[plan.send_order] = torch.arange(total_pairs, device=pos.device)
+        pos = plan.pos  # position of pair (t, k) among the returned rows (send order is chunk-major)
         out = torch.empty((plan.num_tokens, self.hidden), dtype=torch.bfloat16, device=x8.device)
         w32 = topk_weight.reshape(-1).to(torch.float32).contiguous()
         with torch.cuda.device(x8.device):

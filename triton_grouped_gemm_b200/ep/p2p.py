@@ -102,9 +102,10 @@ def make_peer_plan(topk_idx: torch.Tensor, num_experts: int, group, capacity_row
     e_loc = num_experts // world
     t, k = topk_idx.shape
     dev = topk_idx.device
+    from .dispatch import route_plan
+
     flat = topk_idx.reshape(-1).to(torch.int64)
-    send_order = torch.argsort(flat, stable=True)
-    counts = torch.bincount(flat, minlength=num_experts)
+    counts, send_order, pos = route_plan(flat, num_experts)
     counts_flat = torch.empty(world * num_experts, dtype=counts.dtype, device=dev)
     dist.all_gather_into_tensor(counts_flat, counts, group=group)
     counts_all = counts_flat.view(world, num_experts)
@@ -121,8 +122,6 @@ def make_peer_plan(topk_idx: torch.Tensor, num_experts: int, group, capacity_row
     e_sorted = flat[send_order]
     dst_rank = (e_sorted // e_loc).to(torch.int32)
     dst_row = dst_block_start[e_sorted] + (torch.arange(t * k, device=dev) - my_send_start[e_sorted])
-    pos = torch.empty_like(send_order)
-    pos[send_order] = torch.arange(t * k, device=dev)
     return PeerPlan(num_tokens=t, top_k=k, token_of_pair=(send_order // k).contiguous(), dst_rank=dst_rank.contiguous(),
                     dst_row=dst_row.contiguous(), pair_rank=dst_rank[pos].contiguous(), pair_row=dst_row[pos].contiguous(),
                     rows_here=int(totals[me]), block_sizes=by_dest[me].reshape(-1).to(torch.int64).contiguous(),
