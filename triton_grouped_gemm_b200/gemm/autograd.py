@@ -50,3 +50,44 @@ def grouped_gemm(a: torch.Tensor, b: torch.Tensor, size_per_group: torch.Tensor,
     """``C[rows of g] = a[rows of g] @ (b[g].T if trans_b else b[g])`` with gradients for a and b.
     Rows of ``a`` beyond ``sum(size_per_group)`` get no output and no gradient (uninitialised)."""
     return _GroupedGemm.apply(a, b, size_per_group, trans_b)
+
+
+class _GroupedGemmFp8(torch.autograd.Function):
+    """FP8 training recipe over the block-scaled kernels: forward and input gradient in e4m3 with
+    1x128 activation / 128x128 weight scales (quantised on the fly), weight gradient in the
+    16-bit K-grouped kernel.  ``b`` is [G, N, K] (the ``trans_b=True`` layout)."""
+
+    @staticmethod
+    def forward(ctx, a, b, size_per_group):
+        from ..quant.per_block_cast import per_block_cast_to_fp8, per_token_cast_to_fp8
+        from .FP8.m_grouped_gemm_block_scaled import m_grouped_fp8_block_scaled
+
+        a = a.contiguous()
+        b = b.contiguous()
+        c = m_grouped_fp8_block_scaled(per_token_cast_to_fp8(a), per_block_cast_to_fp8(b), size_per_group)
+        ctx.save_for_backward(a, b, size_per_group)
+        return c.to(a.dtype)
+
+    @staticmethod
+    def backward(ctx, grad):
+        from ..quant.per_block_cast import per_block_cast_to_fp8, per_token_cast_to_fp8
+        from .FP8.m_grouped_gemm_block_scaled import m_grouped_fp8_block_scaled
+
+        a, b, size_per_group = ctx.saved_tensors
+        grad = grad.contiguous()
+        da = db = None
+        if ctx.needs_input_grad[0]:
+            # dA = dC B_g: contraction over N, so the weights are quantised in their [G, K, N] view
+            bt8 = per_block_cast_to_fp8(b.transpose(1, 2).contiguous())
+            da = m_grouped_fp8_block_scaled(per_token_cast_to_fp8(grad.to(torch.bfloat16)), bt8, size_per_group).to(a.dtype)
+        if ctx.needs_input_grad[1]:
+            sizes = size_per_group if size_per_group.dtype in (torch.int32, torch.int64) else size_per_group.long()
+            db = k_grouped_gemm(grad, a, sizes)   # [G, N, K], 16-bit operands, fp32 accumulation
+        return da, db, None
+
+
+def grouped_gemm_fp8(a: torch.Tensor, b: torch.Tensor, size_per_group: torch.Tensor):
+    """``C[rows of g] = a[rows of g] @ b[g].T`` computed in block-scaled FP8 (K and N multiples of
+    128 recommended; K % 16 == 0, N % 8 == 0 required), with an FP8 input gradient and a 16-bit
+    weight gradient.  ``a`` [M, K] and ``b`` [G, N, K] are bf16."""
+    return _GroupedGemmFp8.apply(a, b, size_per_group)
