@@ -247,6 +247,10 @@ int b200moe_route_plan(const int64_t* expert, int64_t n, int num_experts, int* c
 int b200moe_scatter_rows_multi(const void* src, const int64_t* src_idx, void* const* dst_bases, const int* dst_rank,
                                const int64_t* dst_row, int64_t rows, int64_t row_bytes, int world,
                                int64_t capacity_rows, void* stream);
+/* blocks > 0: b200moe_scatter_rows_multi launches that many 1024-thread blocks (one per SM at most)
+ * instead of filling the GPU, for running beside a persistent GEMM that was given the other SMs
+ * (num_sms).  0 restores the default.  Process-wide. */
+int b200moe_set_background_blocks(int blocks);
 int b200moe_combine_topk_multi(const void* const* src_bases, const int* pair_rank, const int64_t* pair_row,
                                const float* weights, void* out, int64_t tokens, int top_k, int hidden, int world,
                                int64_t capacity_rows, void* stream);

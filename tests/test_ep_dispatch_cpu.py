@@ -209,3 +209,81 @@ def test_two_gloo_ranks_peer_memory_plan():
             p.join(120)
             assert p.exitcode == 0
         assert results.get(0) is True and results.get(1) is True
+
+
+def _peer_chunk_plan_worker(rank, world, port, results):
+    """Replay of the pipelined peer-memory exchange: chunk-major scatter of rows and return
+    addresses, per-chunk blocks, push of the results back through the return addresses."""
+    from triton_grouped_gemm_b200.ep.p2p import make_peer_chunk_plan
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        t, e, k, h, cap, chunks = 26 + 5 * rank, 8, 3, 4, 200, 2
+        e_loc = e // world
+        ec = e_loc // chunks
+        idx, w = synthetic_routing(t, e, k, seed=40 + rank)
+        gen = torch.Generator().manual_seed(400 + rank)
+        x = torch.randn(t, h, generator=gen)
+        plan = make_peer_chunk_plan(idx, e, dist.group.WORLD, cap, chunks)
+        mine = dict(x=x, idx=idx, token_of_pair=plan.token_of_pair, dst_rank=plan.dst_rank, dst_row=plan.dst_row,
+                    meta=plan.meta, recv_offsets=plan.recv_offsets, send_offsets=plan.send_offsets,
+                    block_sizes=plan.block_sizes, block_expert=plan.block_expert, n=t * k)
+        everyone = [None] * world
+        dist.all_gather_object(everyone, mine)
+        bufs = [torch.full((cap, h), float("nan")) for _ in range(world)]
+        metas = [torch.full((cap, 2), -1, dtype=torch.int64) for _ in range(world)]
+        written = [torch.zeros(cap, dtype=torch.int32) for _ in range(world)]
+        row_expert = [torch.full((cap,), -1, dtype=torch.int64) for _ in range(world)]
+        ok = True
+        for src, p in enumerate(everyone):
+            ok &= p["send_offsets"][-1] == p["n"]
+            for i in range(p["n"]):
+                d, r = int(p["dst_rank"][i]), int(p["dst_row"][i])
+                bufs[d][r] = p["x"][int(p["token_of_pair"][i])]
+                metas[d][r] = p["meta"][i]
+                written[d][r] += 1
+        # every rank's buffer: dense, chunk ranges consistent with the blocks, experts as declared
+        for d, p in enumerate(everyone):
+            r_tot = p["recv_offsets"][-1]
+            ok &= bool((written[d][:r_tot] == 1).all()) and bool((written[d][r_tot:] == 0).all())
+            for c in range(chunks):
+                lo, hi = p["recv_offsets"][c], p["recv_offsets"][c + 1]
+                ok &= int(p["block_sizes"][c].sum()) == hi - lo
+                start = lo
+                for b, nrows in enumerate(p["block_sizes"][c].tolist()):
+                    src = b // ec
+                    exp_global = d * e_loc + int(p["block_expert"][c][b])
+                    for r in range(start, start + nrows):
+                        back_pos, back_rank = int(metas[d][r][0]), int(metas[d][r][1])
+                        ok &= back_rank == src and 0 <= back_pos < everyone[back_rank]["n"]
+                        row_expert[d][r] = exp_global
+                    start += nrows
+        # results = row * (expert + 1), pushed back through the return addresses, combined locally
+        rets = [torch.full((p["n"], h), float("nan")) for p in everyone]
+        for d in range(world):
+            r_tot = everyone[d]["recv_offsets"][-1]
+            y = bufs[d][:r_tot] * (row_expert[d][:r_tot].float()[:, None] + 1.0)
+            for r in range(r_tot):
+                rets[int(metas[d][r][1])][int(metas[d][r][0])] = y[r]
+        out = (rets[rank][plan.pos].view(t, k, h) * w[:, :, None]).sum(1)
+        ok &= torch.allclose(out, _reference(x, idx, w), atol=1e-5)
+        results[rank] = bool(ok)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_gloo_ranks_pipelined_peer_memory_plan():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    with ctx.Manager() as mgr:
+        results = mgr.dict()
+        procs = [ctx.Process(target=_peer_chunk_plan_worker, args=(r, 2, port, results)) for r in range(2)]
+        for p in procs:
+            p.start()
+        for p in procs:
+            p.join(120)
+            assert p.exitcode == 0
+        assert results.get(0) is True and results.get(1) is True

@@ -1,6 +1,7 @@
 """Expert-parallel FP8 layer on two GPUs (skipped on a single-GPU box): both transports - NCCL
 all-to-all and the peer-memory row movers - must reproduce the single-rank layer exactly, over
-several steps that reuse the exchange buffers."""
+several steps that reuse the exchange buffers; each transport in its one-shot form (chunks = 1)
+and pipelined over four groups of local experts."""
 
 import os
 import socket
@@ -11,7 +12,7 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _worker(rank, world, port, transport, results):
+def _worker(rank, world, port, transport, chunks, results):
     import torch.distributed as dist
 
     from triton_grouped_gemm_b200 import _lib
@@ -28,7 +29,8 @@ def _worker(rank, world, port, transport, results):
         w2 = (torch.randn(e, h, inter, generator=g) * 0.05).bfloat16()
         e_loc = e // world
         layer = Fp8MoELayer(w13[rank * e_loc:(rank + 1) * e_loc].to(dev), w2[rank * e_loc:(rank + 1) * e_loc].to(dev), e,
-                            dist.group.WORLD, transport=transport, tokens_per_rank=t, top_k=k, capacity_factor=2.0)
+                            dist.group.WORLD, transport=transport, chunks=chunks, tokens_per_rank=t, top_k=k,
+                            capacity_factor=2.0)
         full = Fp8MoELayer(w13.to(dev), w2.to(dev), e, None)
         worst = 0.0
         for step in range(3):
@@ -43,8 +45,8 @@ def _worker(rank, world, port, transport, results):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("transport", ["p2p", "nccl"])
-def test_two_gpu_layer_matches_single_rank(transport):
+@pytest.mark.parametrize("transport,chunks", [("p2p", 1), ("p2p", 4), ("nccl", 1), ("nccl", 4)])
+def test_two_gpu_layer_matches_single_rank(transport, chunks):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
@@ -55,7 +57,7 @@ def test_two_gpu_layer_matches_single_rank(transport):
     ctx = mp.get_context("spawn")
     with ctx.Manager() as mgr:
         results = mgr.dict()
-        procs = [ctx.Process(target=_worker, args=(r, 2, port, transport, results)) for r in range(2)]
+        procs = [ctx.Process(target=_worker, args=(r, 2, port, transport, chunks, results)) for r in range(2)]
         for p in procs:
             p.start()
         for p in procs:

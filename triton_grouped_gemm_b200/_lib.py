@@ -53,6 +53,7 @@ _SIGNATURES = {
     "b200moe_route_plan": [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     "b200moe_scatter_rows_multi": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int64,
                                    c_void_p],
+    "b200moe_set_background_blocks": [c_int],
     "b200moe_combine_topk_multi": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int,
                                    c_int64, c_void_p],
     "b200ipc_alloc": [c_int64, c_void_p],

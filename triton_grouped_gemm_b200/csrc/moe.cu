@@ -160,18 +160,22 @@ route_scatter_kernel(const long long* __restrict__ expert, long long n, int num_
 // (rank < world, row < capacity): a bad index sets a status bit and is skipped, it cannot fault
 // a peer.
 constexpr int kMaxPeers = 16;
+// > 0: the multi-buffer movers run as that many 1024-thread blocks (at most one per SM), so that a
+// persistent GEMM launched beside them on the remaining SMs is never kept off an SM by a mover
+// block that happened to start there first
+static int g_mover_background_blocks = 0;
 struct PeerBases {
   void* base[kMaxPeers];
 };
 
 // bases[rank[i]][row[i], :] = src[src_idx[i], :]
-__global__ void __launch_bounds__(kMoeThreads)
+__global__ void __launch_bounds__(1024)
 scatter_rows_multi_kernel(const uint4* __restrict__ src, const long long* __restrict__ src_idx, PeerBases bases,
                           const int* __restrict__ rank, const long long* __restrict__ row, long long rows,
                           int row_vecs, int world, long long capacity_rows, unsigned* status) {
   const int lane = threadIdx.x & 31;
-  const long long warp = (static_cast<long long>(blockIdx.x) * kMoeThreads + threadIdx.x) >> 5;
-  const long long warps = (static_cast<long long>(gridDim.x) * kMoeThreads) >> 5;
+  const long long warp = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
   for (long long r = warp; r < rows; r += warps) {
     const int dst_rank = rank[r];
     const long long dst_row = row[r];
@@ -277,6 +281,11 @@ int b200moe_route_plan(const int64_t* expert, int64_t n, int num_experts, int* c
   return 0;
 }
 
+int b200moe_set_background_blocks(int blocks) {
+  b200::g_mover_background_blocks = blocks > 0 ? blocks : 0;
+  return 0;
+}
+
 int b200moe_scatter_rows_multi(const void* src, const int64_t* src_idx, void* const* dst_bases, const int* dst_rank,
                                const int64_t* dst_row, int64_t rows, int64_t row_bytes, int world,
                                int64_t capacity_rows, void* stream) {
@@ -295,7 +304,12 @@ int b200moe_scatter_rows_multi(const void* src, const int64_t* src_idx, void* co
   B200_REQUIRE(sms > 0, "%s: no CUDA device", who);
   long long blocks = (rows + kMoeThreads / 32 - 1) / (kMoeThreads / 32);
   if (blocks > 16ll * sms) blocks = 16ll * sms;
-  scatter_rows_multi_kernel<<<static_cast<int>(blocks), kMoeThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+  int threads = kMoeThreads;
+  if (g_mover_background_blocks > 0) {
+    threads = 1024;
+    blocks = g_mover_background_blocks < sms ? g_mover_background_blocks : sms;
+  }
+  scatter_rows_multi_kernel<<<static_cast<int>(blocks), threads, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(src), reinterpret_cast<const long long*>(src_idx), pb, dst_rank,
       reinterpret_cast<const long long*>(dst_row), rows, static_cast<int>(row_bytes / 16), world, capacity_rows,
       device_status_ptr());

@@ -58,6 +58,11 @@ class Fp8MoELayer:
             self.recvs = PeerBuffer(cap, (self.hidden + 127) // 128, torch.float32, dev, group)
             self.ybuf = PeerBuffer(cap, self.hidden, torch.bfloat16, dev, group)
             self._flag = torch.zeros(1, dtype=torch.int32, device=dev)
+            if self.chunks > 1:
+                # pipelined form: results are pushed back into the token owner's buffer chunk by chunk
+                self.meta = PeerBuffer(cap, 2, torch.int64, dev, group)
+                self.ret = PeerBuffer(tokens_per_rank * top_k, self.hidden, torch.bfloat16, dev, group)
+                self._side = (torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev))
 
     def experts(self, x8: torch.Tensor, xs: torch.Tensor, size_per_group: torch.Tensor,
                 group_to_expert: Optional[torch.Tensor] = None, num_sms: int = -1,
@@ -90,6 +95,8 @@ class Fp8MoELayer:
         """x [T, H] bf16, topk_idx/topk_weight [T, k] -> [T, H] bf16."""
         x8, xs = per_token_cast_to_fp8(x.contiguous())
         if self.transport == "p2p":
+            if self.chunks > 1:
+                return self._forward_p2p_pipelined(x8, xs, topk_idx, topk_weight)
             return self._forward_p2p(x8, xs, topk_idx, topk_weight)
         if self.world > 1:
             return self._forward_pipelined(x8, xs, topk_idx, topk_weight)
@@ -131,6 +138,70 @@ class Fp8MoELayer:
         with torch.cuda.device(x8.device):
             rc = _lib.load().b200moe_combine_topk(ret.data_ptr(), pos.data_ptr(), w32.data_ptr(), out.data_ptr(),
                                                   plan.num_tokens, plan.top_k, self.hidden, _lib.stream_ptr(x8.device))
+        _lib.check(rc, "b200moe_combine_topk")
+        return out
+
+    def _forward_p2p_pipelined(self, x8, xs, topk_idx, topk_weight) -> torch.Tensor:
+        """Peer memory in both directions, beside the GEMMs: a dispatch stream scatters chunk after
+        chunk into the owners' buffers (rows, scales and each row's return address), the main
+        stream runs chunk c's GEMMs as soon as its rows have landed everywhere, a return stream
+        pushes chunk c's results into the token owners' buffers; the movers run as a few large
+        blocks on the SMs the GEMMs leave free.  A local weighted sum finishes the step."""
+        from .. import _lib
+        from .p2p import make_peer_chunk_plan, scatter_range
+
+        lib = _lib.load()
+        dev = x8.device
+        plan = make_peer_chunk_plan(topk_idx, self.num_experts, self.group, self.recv8.capacity, self.chunks)
+        assert plan.pos.numel() <= self.ret.capacity, "more (token, k) pairs than the return buffer holds"
+        sms = lib.b200gemm_sm_count()
+        gemm_sms = sms - self.comm_sms if 0 < self.comm_sms < sms - 2 else -1
+        main = torch.cuda.current_stream(dev)
+        s_disp, s_ret = self._side
+        ready = torch.cuda.Event()
+        ready.record(main)
+        landed = [torch.cuda.Event() for _ in range(self.chunks)]
+        computed = [torch.cuda.Event() for _ in range(self.chunks)]
+        # movers that run beside a GEMM use `comm_sms` large blocks (one per SM the GEMM leaves free);
+        # the first dispatch and the last return have the GPU to themselves and use the full grid
+        background = max(self.comm_sms, 1)
+        try:
+            with torch.cuda.stream(s_disp):
+                s_disp.wait_event(ready)
+                for c in range(self.chunks):
+                    lo, hi = plan.send_offsets[c], plan.send_offsets[c + 1]
+                    tok, dr, dw = plan.token_of_pair[lo:hi], plan.dst_rank[lo:hi], plan.dst_row[lo:hi]
+                    lib.b200moe_set_background_blocks(0 if c == 0 else background)
+                    scatter_range(x8, tok, dr, dw, self.recv8)
+                    scatter_range(xs, tok, dr, dw, self.recvs)
+                    scatter_range(plan.meta, torch.arange(lo, hi, device=dev), dr, dw, self.meta)
+                    dist.all_reduce(self._flag, group=self.group)      # chunk c has landed on every rank
+                    landed[c].record(s_disp)
+            for c in range(self.chunks):
+                lo, hi = plan.recv_offsets[c], plan.recv_offsets[c + 1]
+                main.wait_event(landed[c])
+                self.experts(self.recv8.local[lo:hi].view(torch.float8_e4m3fn), self.recvs.local[lo:hi],
+                             plan.block_sizes[c], group_to_expert=plan.block_expert[c], num_sms=gemm_sms,
+                             out=self.ybuf.local[lo:hi])
+                computed[c].record(main)
+                with torch.cuda.stream(s_ret):
+                    s_ret.wait_event(computed[c])
+                    back_row = self.meta.local[lo:hi, 0].contiguous()
+                    back_rank = self.meta.local[lo:hi, 1].to(torch.int32).contiguous()
+                    lib.b200moe_set_background_blocks(0 if c == self.chunks - 1 else background)
+                    scatter_range(self.ybuf.local, torch.arange(lo, hi, device=dev), back_rank, back_row, self.ret)
+            with torch.cuda.stream(s_ret):
+                dist.all_reduce(self._flag, group=self.group)          # every rank's results have been pushed
+                done = torch.cuda.Event()
+                done.record(s_ret)
+            main.wait_event(done)
+        finally:
+            lib.b200moe_set_background_blocks(0)
+        out = torch.empty((plan.num_tokens, self.hidden), dtype=torch.bfloat16, device=dev)
+        w32 = topk_weight.reshape(-1).to(torch.float32).contiguous()
+        with torch.cuda.device(dev):
+            rc = lib.b200moe_combine_topk(self.ret.local.data_ptr(), plan.pos.data_ptr(), w32.data_ptr(), out.data_ptr(),
+                                          plan.num_tokens, plan.top_k, self.hidden, _lib.stream_ptr(dev))
         _lib.check(rc, "b200moe_combine_topk")
         return out
 

@@ -153,3 +153,90 @@ def combine_rows(plan: PeerPlan, buf: PeerBuffer, topk_weight: torch.Tensor) -> 
                                                     buf.world, buf.capacity, _lib.stream_ptr(out.device))
     _lib.check(rc, "b200moe_combine_topk_multi")
     return out
+
+
+@dataclass
+class PeerChunkPlan:
+    """Peer-memory plan split into ``chunks`` groups of local experts (chunk c = local experts
+    [c*ec, (c+1)*ec) on every rank).  Send order and every rank's receive buffers are chunk-major:
+    [chunk][source rank][expert of the chunk], so a chunk is one contiguous row range everywhere."""
+    num_tokens: int
+    top_k: int
+    chunks: int
+    token_of_pair: torch.Tensor      # [T*k] send order
+    dst_rank: torch.Tensor           # [T*k] int32
+    dst_row: torch.Tensor            # [T*k] int64
+    pos: torch.Tensor                # [T*k] position of pair (t, k) in send order = its row in this rank's return buffer
+    send_offsets: List[int]          # [chunks + 1] send-order ranges of the chunks
+    recv_offsets: List[int]          # [chunks + 1] row ranges of the chunks in this rank's receive buffers
+    block_sizes: List[torch.Tensor]  # per chunk [world * ec] int64
+    block_expert: List[torch.Tensor] # per chunk [world * ec] int32 (local expert index)
+    meta: torch.Tensor               # [T*k, 2] int64: (send-order position, this rank) of each pair
+
+
+def make_peer_chunk_plan(topk_idx: torch.Tensor, num_experts: int, group, capacity_rows: int,
+                         chunks: int) -> PeerChunkPlan:
+    from .dispatch import route_plan
+
+    world, me = dist.get_world_size(group), dist.get_rank(group)
+    assert num_experts % world == 0
+    e_loc = num_experts // world
+    assert e_loc % chunks == 0
+    ec = e_loc // chunks
+    t, k = topk_idx.shape
+    n = t * k
+    dev = topk_idx.device
+    flat = topk_idx.reshape(-1).to(torch.int64)
+    rank_of = flat // e_loc
+    local = flat - rank_of * e_loc
+    chunk_of = local // ec
+    key = chunk_of * (world * ec) + rank_of * ec + (local - chunk_of * ec)
+    counts_by_key, send_order, pos = route_plan(key, num_experts)
+    e_ids = torch.arange(num_experts, device=dev)
+    key_of_expert = ((e_ids % e_loc) // ec) * (world * ec) + (e_ids // e_loc) * ec + (e_ids % e_loc) % ec
+    counts = counts_by_key[key_of_expert]                                             # by global expert
+    counts_flat = torch.empty(world * num_experts, dtype=counts.dtype, device=dev)
+    dist.all_gather_into_tensor(counts_flat, counts, group=group)
+    # arrival layout at destination d: blocks (chunk c, source s, expert j of the chunk) in that order
+    by_dest = counts_flat.view(world, world, chunks, ec).permute(1, 2, 0, 3).contiguous()   # [d, c, s, j]
+    flat_blocks = by_dest.view(world, chunks * world * ec)
+    starts = (flat_blocks.cumsum(1) - flat_blocks).view(world, chunks, world, ec)            # [d, c, s, j]
+    dst_block_start = starts[:, :, me, :].reshape(num_experts)                               # (d, c, j) = global expert
+    totals = flat_blocks.sum(1)
+    host = torch.cat([totals, by_dest[me].sum((1, 2)), counts_by_key.view(chunks, world * ec).sum(1)]).cpu()  # one sync
+    if int(host[:world].max()) > capacity_rows:
+        raise RuntimeError(f"a rank would receive {int(host[:world].max())} rows, more than the exchange buffers hold "
+                           f"({capacity_rows}); raise capacity_factor")
+    recv_offsets, send_offsets = [0], [0]
+    for c in range(chunks):
+        recv_offsets.append(recv_offsets[-1] + int(host[world + c]))
+        send_offsets.append(send_offsets[-1] + int(host[world + chunks + c]))
+    send_start_by_key = counts_by_key.cumsum(0) - counts_by_key
+    key_sorted = key[send_order]
+    e_sorted = flat[send_order]
+    idx = torch.arange(n, device=dev)
+    dst_rank = (e_sorted // e_loc).to(torch.int32)
+    dst_row = dst_block_start[e_sorted] + (idx - send_start_by_key[key_sorted])
+    meta = torch.stack([idx, torch.full_like(idx, me)], dim=1).contiguous()
+    return PeerChunkPlan(num_tokens=t, top_k=k, chunks=chunks, token_of_pair=(send_order // k).contiguous(),
+                         dst_rank=dst_rank.contiguous(), dst_row=dst_row.contiguous(), pos=pos,
+                         send_offsets=send_offsets, recv_offsets=recv_offsets,
+                         block_sizes=[by_dest[me, c].reshape(-1).to(torch.int64).contiguous() for c in range(chunks)],
+                         block_expert=[(torch.arange(ec, device=dev, dtype=torch.int32) + c * ec).repeat(world).contiguous()
+                                       for c in range(chunks)],
+                         meta=meta)
+
+
+def scatter_range(src: torch.Tensor, src_idx: torch.Tensor, dst_rank: torch.Tensor, dst_row: torch.Tensor,
+                  buf: PeerBuffer) -> None:
+    """buf[dst_rank[i]][dst_row[i]] = src[src_idx[i]] for the given index vectors (contiguous tensors
+    that the caller keeps alive until the stream has run the kernel)."""
+    src2 = src.view(torch.uint8) if src.dtype in (torch.float8_e4m3fn, torch.float8_e5m2) else src
+    assert src2.is_contiguous() and src_idx.is_contiguous() and dst_rank.is_contiguous() and dst_row.is_contiguous()
+    row_bytes = src2.shape[1] * src2.element_size()
+    assert row_bytes == buf.local.shape[1] * buf.local.element_size()
+    with torch.cuda.device(src2.device):
+        rc = _lib.load().b200moe_scatter_rows_multi(src2.data_ptr(), src_idx.data_ptr(), buf.bases, dst_rank.data_ptr(),
+                                                    dst_row.data_ptr(), src_idx.numel(), row_bytes, buf.world,
+                                                    buf.capacity, _lib.stream_ptr(src2.device))
+    _lib.check(rc, "b200moe_scatter_rows_multi")
