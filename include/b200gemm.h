@@ -174,6 +174,20 @@ int b200gemm_fp8_m_grouped_block_mapped(const void* a, const float* a_scale, con
                                         const int* group_to_b, int num_b, int64_t m_rows, int n, int k, int num_sms,
                                         void* stream);
 
+/* Gate+up projection of a SwiGLU feed-forward with the activation and its 1x128 quantisation in
+ * the epilogue.  b [num_b or G, n, k] holds gate and up weight rows interleaved in 128-row blocks
+ * (rows [256 t, 256 t + 128) = gate rows [128 t, +128), rows [256 t + 128, +128) = up rows
+ * [128 t, +128)), b_scale likewise; n = 2 x intermediate size, a multiple of 256.  Writes
+ * act [m_rows, n/2] e4m3 = quantised bf16(silu(bf16(gate)) * bf16(up)) and act_scale [m_rows, n/256]
+ * fp32: bit for bit what b200gemm_fp8_m_grouped_block followed by b200quant_swiglu_act_1x128
+ * produce from the un-interleaved weights, without storing the bf16 product.  group_to_b may be
+ * NULL (group g uses b[g]); masked_stride > 0 selects the masked row layout (rows g*stride ...),
+ * 0 the compact one.  No counterpart in the reference. */
+int b200gemm_fp8_m_grouped_block_swiglu(const void* a, const float* a_scale, const void* b, const float* b_scale,
+                                        void* act, float* act_scale, const void* sizes, int sizes_is_i64,
+                                        int num_groups, const int* group_to_b, int num_b, int64_t m_rows,
+                                        int masked_stride, int n, int k, int num_sms, void* stream);
+
 /* Masked-layout twin (decode): rows [g*expected_m, g*expected_m + masked_m[g]) of out.  No
  * reference counterpart as a kernel; it combines the masked layout of
  * gemm/BF16/m_grouped_gemm_masked_TMA.py:164-250 with the block-scaled contract above. */

@@ -208,3 +208,41 @@ def test_group_to_weight_map(pair):
     out2 = m_grouped_fp8_block_scaled((a8.to(DEV), a_s.to(DEV)), (b8_blocks.to(DEV), b_s_blocks.to(DEV)),
                                       torch.tensor(block_sizes, device=DEV)).cpu()
     assert torch.equal(out, out2)
+
+
+@pytest.mark.parametrize("pair", [0, 1])
+@pytest.mark.parametrize("sizes,inter,k", [([300, 0, 1, 127, 129], 256, 512), ([128], 128, 128), ([64, 700, 5], 384, 1024)])
+def test_swiglu_epilogue_is_bit_identical_to_product_plus_quantiser(sizes, inter, k, pair):
+    """Gate+up GEMM with SwiGLU + 1x128 quantiser in its epilogue (weights interleaved in 128-row
+    blocks) against the bf16 product followed by the SwiGLU quantiser kernel: same bytes, same
+    scales; also with row blocks mapped to weights."""
+    from triton_grouped_gemm_b200.gemm.FP8.m_grouped_gemm_block_scaled import (interleave_gate_up,
+                                                                              m_grouped_fp8_block_scaled_swiglu)
+    from triton_grouped_gemm_b200.quant.per_block_cast import (per_block_cast_to_fp8, per_token_cast_to_fp8,
+                                                             swiglu_per_token_cast_to_fp8)
+
+    _lib.load().b200gemm_set_cta_pair(pair)
+    g, m = len(sizes), sum(sizes)
+    gen = torch.Generator().manual_seed(inter + k + g)
+    x = torch.randn(m, k, generator=gen).bfloat16().to(DEV)
+    w13 = (torch.randn(g, 2 * inter, k, generator=gen) * 0.05).bfloat16().to(DEV)
+    st = torch.tensor(sizes, device=DEV)
+    a = per_token_cast_to_fp8(x)
+    h = m_grouped_fp8_block_scaled(a, per_block_cast_to_fp8(w13), st)
+    q_ref, s_ref = swiglu_per_token_cast_to_fp8(h)
+    q, s = m_grouped_fp8_block_scaled_swiglu(a, per_block_cast_to_fp8(interleave_gate_up(w13)), st)
+    assert torch.equal(q.view(torch.uint8), q_ref.view(torch.uint8)) and torch.equal(s, s_ref)
+    # masked layout: 2 slots per group... every group gets a slot of `stride` rows, first sizes[g] valid
+    stride = 768
+    xm = torch.zeros(g * stride, k, dtype=torch.bfloat16, device=DEV)
+    row = 0
+    for i, n_i in enumerate(sizes):
+        xm[i * stride:i * stride + n_i] = x[row:row + n_i]
+        row += n_i
+    am = per_token_cast_to_fp8(xm)
+    qm, sm = m_grouped_fp8_block_scaled_swiglu(am, per_block_cast_to_fp8(interleave_gate_up(w13)), st, masked_stride=stride)
+    row = 0
+    for i, n_i in enumerate(sizes):
+        assert torch.equal(qm[i * stride:i * stride + n_i].view(torch.uint8), q_ref[row:row + n_i].view(torch.uint8))
+        assert torch.equal(sm[i * stride:i * stride + n_i], s_ref[row:row + n_i])
+        row += n_i

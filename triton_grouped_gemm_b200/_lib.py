@@ -48,6 +48,8 @@ _SIGNATURES = {
                                      c_int, c_int, c_int, c_int, c_void_p],
     "b200gemm_fp8_m_grouped_block_mapped": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                             c_void_p, c_int, c_int64, c_int, c_int, c_int, c_void_p],
+    "b200gemm_fp8_m_grouped_block_swiglu": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                            c_int, c_void_p, c_int, c_int64, c_int, c_int, c_int, c_int, c_void_p],
     "b200gemm_fp8_m_grouped_masked_block": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                             c_int, c_int, c_int, c_int, c_void_p],
     "b200moe_route_plan": [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],

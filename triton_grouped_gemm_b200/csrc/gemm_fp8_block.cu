@@ -17,11 +17,20 @@
 //                       owns TMEM lanes [32*quarter, +32) and columns [128*half, +128), i.e.
 //                       exactly one 128-wide scale block of B per thread; these warpgroups
 //                       raise their register budget (setmaxnreg) to hold 128 fp32 accumulators
+//
+// kSwiglu (256-column tiles only): the GEMM is the gate+up projection of a SwiGLU feed-forward
+// whose weight rows the caller interleaved in 128-row blocks (tile t = gate block t, then up
+// block t), and the epilogue writes act = bf16(silu(bf16(gate)) * bf16(up)) quantised 1x128 -
+// e4m3 bytes plus one fp32 scale per row and tile - instead of the bf16 product: the same bytes
+// and scales as storing the product and running the SwiGLU quantiser on it, without the round
+// trip through HBM.  The warp holding a row's up half passes its values to the warp holding the
+// gate half through the two warps' store-staging buffers (mbarrier handshake per tile).
 #include <cuda_bf16.h>
 
 #include "../../include/b200gemm.h"
 #include "common.cuh"
 #include "gemm_tile.cuh"
+#include "quant_math.cuh"
 
 namespace b200 {
 
@@ -50,18 +59,20 @@ struct Fp8BlockCfg {
   static constexpr int kScaleTileBytes = kBlockM * 128;
   static constexpr int kScaleOffset = kEpiOffset + 8 * 32 * 128;
   static constexpr int kBarOffset = kScaleOffset + 2 * kScaleTileBytes;
-  static constexpr int kNumBars = 2 * kStages + 8;  // + scale_full[2], scale_empty[2]
+  // + tmem_full[2], tmem_empty[2], scale_full[2], scale_empty[2], exchange_full[4], exchange_empty[4]
+  static constexpr int kNumBars = 2 * kStages + 16;
   static constexpr int kDynamicBytes = kBarOffset + kNumBars * 8 + 16 + 1024;
 };
 
-template <int kBlockN, bool kPair>
+template <int kBlockN, bool kPair, bool kSwiglu>
 __global__ void __launch_bounds__(Fp8BlockCfg<kBlockN, kPair>::kThreads, 1)
 fp8_block_m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                            const __grid_constant__ CUtensorMap tm_c, const __grid_constant__ CUtensorMap tm_as,
                            int scales_by_tma, __nv_bfloat16* __restrict__ c_ptr, const float* __restrict__ a_scale,
                            const float* __restrict__ b_scale, const void* __restrict__ sizes, int sizes_i64,
                            int num_groups, int masked_stride, int n, int k, const int* __restrict__ b_map,
-                           int num_b, unsigned* status) {
+                           int num_b, float* __restrict__ act_scale_out, unsigned* status) {
+  static_assert(!kSwiglu || kBlockN == 256, "the SwiGLU epilogue pairs the two 128-column halves of a 256-column tile");
   using L = Fp8BlockCfg<kBlockN, kPair>;
   // weight matrix of row group g: b[b_map[g]] (clamped into range), or b[g] without a map
   auto weight_of = [&](int g) -> int {
@@ -82,6 +93,8 @@ fp8_block_m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
   auto tmem_empty_bar = [&](int a) { return bar_base + 8u * (2 * kStages + 2 + a); };
   auto scale_full_bar = [&](int a) { return bar_base + 8u * (2 * kStages + 4 + a); };
   auto scale_empty_bar = [&](int a) { return bar_base + 8u * (2 * kStages + 6 + a); };
+  auto xchg_full_bar = [&](int q) { return bar_base + 8u * (2 * kStages + 8 + q); };
+  auto xchg_empty_bar = [&](int q) { return bar_base + 8u * (2 * kStages + 12 + q); };
   volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(smem + L::kBarOffset + L::kNumBars * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kBarOffset + L::kNumBars * 8 + 4);
 
@@ -105,6 +118,10 @@ fp8_block_m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
       mbar_init(tmem_empty_bar(a), L::kPromoWarps * kCtas);
       mbar_init(scale_full_bar(a), 1);
       mbar_init(scale_empty_bar(a), L::kPromoWarps);
+    }
+    for (int q = 0; q < 4; ++q) {
+      mbar_init(xchg_full_bar(q), 1);
+      mbar_init(xchg_empty_bar(q), 1);
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -239,6 +256,7 @@ fp8_block_m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
     const int half = (warp - 4) >> 2;
     uint32_t it = 0;
     uint32_t scale_it = 0;
+    uint32_t xchg_it = 0;  // tiles passed through the gate/up exchange (kSwiglu)
     // this thread's row inside a staged scale tile: 128 bytes per row, 16-byte chunks XOR-ed
     // with (row % 8) by the 128-byte swizzle
     const int srow = quarter * 32 + lane;
@@ -360,6 +378,86 @@ fp8_block_m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
 #pragma unroll
       for (int j = 0; j < 64; ++j) unpack_f32x2(acc2[j], acc[2 * j], acc[2 * j + 1]);
       if (!ok) break;
+      if constexpr (kSwiglu) {
+        // tile columns [0, 128) hold gate block nt, [128, 256) up block nt of the same 128 outputs
+        uint8_t* buf_lo = smem + L::kEpiOffset + quarter * (32 * 128);        // the gate warp's staging buffer
+        uint8_t* buf_hi = smem + L::kEpiOffset + (4 + quarter) * (32 * 128);  // the up warp's
+        if (half == 1) {
+          // up half: round to bf16 (what storing the product would do) and hand over
+          if (!wait_bounded(xchg_empty_bar(quarter), (xchg_it & 1u) ^ 1u, abort_flag, status, kDevTimeoutPromote)) break;
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            uint8_t* buf = c == 0 ? buf_lo : buf_hi;
+#pragma unroll
+            for (int v = 0; v < 8; ++v) {
+              uint32_t p[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e)
+                p[e] = pack2_16bit(acc[c * 64 + v * 8 + 2 * e], acc[c * 64 + v * 8 + 2 * e + 1], 0);
+              *reinterpret_cast<uint4*>(buf + lane * 128 + ((v ^ (lane & 7)) << 4)) = make_uint4(p[0], p[1], p[2], p[3]);
+            }
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(xchg_full_bar(quarter));
+        } else {
+          if (!wait_bounded(xchg_full_bar(quarter), xchg_it & 1u, abort_flag, status, kDevTimeoutPromote)) break;
+          float amax = 0.f;
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            const uint8_t* buf = c == 0 ? buf_lo : buf_hi;
+#pragma unroll
+            for (int v = 0; v < 8; ++v) {
+              const uint4 u4 = *reinterpret_cast<const uint4*>(buf + lane * 128 + ((v ^ (lane & 7)) << 4));
+              const uint32_t uw[4] = {u4.x, u4.y, u4.z, u4.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const int j = c * 64 + v * 8 + 2 * e;
+                const float g0 = __bfloat162float(__float2bfloat16_rn(acc[j]));
+                const float g1 = __bfloat162float(__float2bfloat16_rn(acc[j + 1]));
+                acc[j] = silu_mul_round_bf16(g0, __uint_as_float(uw[e] << 16));
+                acc[j + 1] = silu_mul_round_bf16(g1, __uint_as_float(uw[e] & 0xFFFF0000u));
+                amax = fmaxf(amax, fmaxf(fabsf(acc[j]), fabsf(acc[j + 1])));
+              }
+            }
+          }
+          __syncwarp();  // every lane has read its row: buf_lo may be reused for the fp8 staging
+          amax = fmaxf(amax, 1e-4f);
+          const float inv = inv_scale_448(amax);
+          const int inter = n >> 1;
+          if (row_ok) act_scale_out[row * static_cast<long long>(inter >> 7) + nt] = __fdiv_rn(amax, 448.0f);
+          // 16 e4m3 bytes (columns 16 v .. 16 v + 15 of the 128) as one 16-byte vector
+          auto quantised16 = [&](int v) -> uint4 {
+            uint32_t w4[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const int b = 16 * v + 4 * j;
+              w4[j] = cvt_e4m3x2(__fmul_rn(acc[b], inv), __fmul_rn(acc[b + 1], inv)) |
+                      (cvt_e4m3x2(__fmul_rn(acc[b + 2], inv), __fmul_rn(acc[b + 3], inv)) << 16);
+            }
+            return make_uint4(w4[0], w4[1], w4[2], w4[3]);
+          };
+          if (row_w0 + 32 <= w.group_row_end()) {
+#pragma unroll
+            for (int v = 0; v < 8; ++v)
+              *reinterpret_cast<uint4*>(buf_lo + lane * 128 + ((v ^ (lane & 7)) << 4)) = quantised16(v);
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_2d(&tm_c, smem_u32(buf_lo), nt * 128, static_cast<int>(row_w0));
+              tma_store_commit();
+              tma_store_wait_read<0>();  // the buffer goes back to the up warp below
+            }
+          } else if (row_ok) {
+            uint8_t* out_row = reinterpret_cast<uint8_t*>(c_ptr) + row * static_cast<long long>(inter) + nt * 128;
+#pragma unroll
+            for (int v = 0; v < 8; ++v) *reinterpret_cast<uint4*>(out_row + v * 16) = quantised16(v);
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(xchg_empty_bar(quarter));
+        }
+        ++xchg_it;
+        continue;
+      }
       if (row_w0 + 32 <= w.group_row_end()) {
         // all 32 rows of this warp are valid: round, stage in the 128-byte-swizzle layout and
         // let TMA write 64-column chunks (the tensor map clips columns >= n)
@@ -416,13 +514,13 @@ fp8_block_m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
   }
 }
 
-template <int kBlockN, bool kPair>
+template <int kBlockN, bool kPair, bool kSwiglu = false>
 static int launch_fp8_block(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const CUtensorMap& tm_c,
                             const CUtensorMap& tm_as, int scales_by_tma, void* c, const float* a_scale, const float* b_scale, const void* sizes, int sizes_is_i64,
                             int num_groups, int masked_stride, int n, int k, const int* b_map, int num_b, int grid,
-                            cudaStream_t stream) {
+                            cudaStream_t stream, float* act_scale_out = nullptr) {
   using L = Fp8BlockCfg<kBlockN, kPair>;
-  auto kern = fp8_block_m_grouped_kernel<kBlockN, kPair>;
+  auto kern = fp8_block_m_grouped_kernel<kBlockN, kPair, kSwiglu>;
   B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes));
   if constexpr (kPair) {
     // a cluster of two CTAs per tile; keep only as many CTAs as are co-resident
@@ -464,12 +562,13 @@ static int launch_fp8_block(const CUtensorMap& tm_a, const CUtensorMap& tm_b, co
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     B200_CUDA(cudaLaunchKernelEx(&cfg, kern, tm_a, tm_b, tm_c, tm_as, scales_by_tma, static_cast<__nv_bfloat16*>(c), a_scale, b_scale, sizes,
-                                 sizes_is_i64, num_groups, masked_stride, n, k, b_map, num_b, device_status_ptr()));
+                                 sizes_is_i64, num_groups, masked_stride, n, k, b_map, num_b, act_scale_out,
+                                 device_status_ptr()));
   } else {
     kern<<<grid, L::kThreads, L::kDynamicBytes, stream>>>(tm_a, tm_b, tm_c, tm_as, scales_by_tma,
                                                           static_cast<__nv_bfloat16*>(c), a_scale,
                                                           b_scale, sizes, sizes_is_i64, num_groups, masked_stride, n,
-                                                          k, b_map, num_b, device_status_ptr());
+                                                          k, b_map, num_b, act_scale_out, device_status_ptr());
   }
   B200_CUDA(cudaGetLastError());
   return 0;
@@ -478,7 +577,13 @@ static int launch_fp8_block(const CUtensorMap& tm_a, const CUtensorMap& tm_b, co
 static int fp8_block_common(const void* a, const float* a_scale, const void* b, const float* b_scale, void* c,
                             const void* sizes, int sizes_is_i64, int num_groups, int64_t m_rows, int masked_stride,
                             int n, int k, int num_sms, void* stream_v, const char* who, const int* b_map = nullptr,
-                            int num_b = 0) {
+                            int num_b = 0, float* act_scale_out = nullptr) {
+  // act_scale_out != nullptr: SwiGLU epilogue - c receives e4m3 bytes [m_rows, n/2], act_scale_out fp32
+  // [m_rows, n/256]; b must hold gate and up rows interleaved in 128-row blocks
+  const bool swiglu = act_scale_out != nullptr;
+  if (swiglu)
+    B200_REQUIRE(n > 0 && n % 256 == 0, "%s: the SwiGLU epilogue needs n (= 2 x intermediate size, %d) to be a multiple of 256",
+                 who, n);
   if (!b_map) num_b = num_groups;
   B200_REQUIRE(num_b > 0 || num_groups == 0, "%s: num_b must be positive when a group-to-weight map is given", who);
   B200_REQUIRE(num_groups >= 0 && m_rows >= 0 && n >= 0 && k >= 0, "%s: negative dimension", who);
@@ -496,7 +601,7 @@ static int fp8_block_common(const void* a, const float* a_scale, const void* b, 
   B200_REQUIRE(sms > 0, "%s: no CUDA device", who);
   const int grid = (num_sms > 0 && num_sms < sms) ? num_sms : sms;
   const long long m_tiles_est = (m_rows + kBlockM - 1) / kBlockM;
-  const int block_n = (n <= 128 || m_tiles_est * ((n + 255) / 256) < grid) ? 128 : 256;
+  const int block_n = swiglu ? 256 : ((n <= 128 || m_tiles_est * ((n + 255) / 256) < grid) ? 128 : 256);
   // CTA pairs when every pair of SMs gets 256 x 256 tiles (or when forced by the tuning knob)
   bool pair = false;
   if (g_cta_pair_mode == 1) pair = grid >= 2;
@@ -521,7 +626,14 @@ static int fp8_block_common(const void* a, const float* a_scale, const void* b, 
     if (rc) return rc;
   }
   CUtensorMap tm_c;
-  {
+  if (swiglu) {
+    const uint64_t dims[2] = {static_cast<uint64_t>(n / 2), static_cast<uint64_t>(m_rows)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(n / 2)};
+    const uint32_t box[2] = {128, 32};
+    int rc = encode_tmap(&tm_c, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, c, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B,
+                         "act[M, n/2] (e4m3)");
+    if (rc) return rc;
+  } else {
     const uint64_t dims[2] = {static_cast<uint64_t>(n), static_cast<uint64_t>(m_rows)};
     const uint64_t strides[1] = {static_cast<uint64_t>(n) * 2};
     const uint32_t box[2] = {64, 32};
@@ -540,6 +652,15 @@ static int fp8_block_common(const void* a, const float* a_scale, const void* b, 
     int rc = encode_tmap(&tm_as, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, a_scale, dims, strides, box,
                          CU_TENSOR_MAP_SWIZZLE_128B, "a_scale");
     if (rc) return rc;
+  }
+  if (swiglu) {
+    if (pair)
+      return launch_fp8_block<256, true, true>(tm_a, tm_b, tm_c, tm_as, scales_by_tma, c, a_scale, b_scale, sizes,
+                                               sizes_is_i64, num_groups, masked_stride, n, k, b_map, num_b, grid, stream,
+                                               act_scale_out);
+    return launch_fp8_block<256, false, true>(tm_a, tm_b, tm_c, tm_as, scales_by_tma, c, a_scale, b_scale, sizes,
+                                              sizes_is_i64, num_groups, masked_stride, n, k, b_map, num_b, grid, stream,
+                                              act_scale_out);
   }
   if (pair)
     return launch_fp8_block<256, true>(tm_a, tm_b, tm_c, tm_as, scales_by_tma, c, a_scale, b_scale, sizes, sizes_is_i64, num_groups,
@@ -570,6 +691,19 @@ int b200gemm_fp8_m_grouped_block_mapped(const void* a, const float* a_scale, con
     return b200::set_error(b200::kErrInvalidArgument, "b200gemm_fp8_m_grouped_block_mapped: group_to_b is null");
   return b200::fp8_block_common(a, a_scale, b, b_scale, c, sizes, sizes_is_i64, num_groups, m_rows, 0, n, k, num_sms,
                                 stream, "b200gemm_fp8_m_grouped_block_mapped", group_to_b, num_b);
+}
+
+int b200gemm_fp8_m_grouped_block_swiglu(const void* a, const float* a_scale, const void* b, const float* b_scale,
+                                        void* act, float* act_scale, const void* sizes, int sizes_is_i64,
+                                        int num_groups, const int* group_to_b, int num_b, int64_t m_rows,
+                                        int masked_stride, int n, int k, int num_sms, void* stream) {
+  const char* who = "b200gemm_fp8_m_grouped_block_swiglu";
+  if (!act_scale) return b200::set_error(b200::kErrInvalidArgument, "%s: act_scale is null", who);
+  if (masked_stride < 0) return b200::set_error(b200::kErrInvalidArgument, "%s: masked_stride must be >= 0", who);
+  if (reinterpret_cast<uintptr_t>(act) & 15)
+    return b200::set_error(b200::kErrInvalidArgument, "%s: act must be 16-byte aligned", who);
+  return b200::fp8_block_common(a, a_scale, b, b_scale, act, sizes, sizes_is_i64, num_groups, m_rows, masked_stride, n,
+                                k, num_sms, stream, who, group_to_b, group_to_b ? num_b : 0, act_scale);
 }
 
 int b200gemm_fp8_m_grouped_masked_block(const void* a, const float* a_scale, const void* b, const float* b_scale,

@@ -10,6 +10,7 @@
 
 #include "../../include/b200gemm.h"
 #include "common.cuh"
+#include "quant_math.cuh"
 
 namespace b200 {
 
@@ -17,17 +18,6 @@ __device__ __forceinline__ float to_f32(uint16_t raw, int is_fp16) {
   if (is_fp16) return __half2float(__ushort_as_half(raw));
   return __uint_as_float(static_cast<uint32_t>(raw) << 16);
 }
-
-// two fp32 -> two e4m3 bytes (round to nearest even, finite values saturate at +-448,
-// NaN -> 0x7f); low byte = first value
-__device__ __forceinline__ uint32_t cvt_e4m3x2(float a, float b) {
-  return static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3));
-}
-
-// The reference writes `448.0 / amax` with a Python scalar on the left; torch evaluates that
-// as reciprocal(amax) * 448 (two roundings), which differs from a single IEEE division in
-// the last bit often enough to flip e4m3 bytes.  Reproduce the two roundings.
-__device__ __forceinline__ float inv_scale_448(float amax) { return __fmul_rn(__frcp_rn(amax), 448.0f); }
 
 __device__ __forceinline__ float abs_max8(const uint4& v, int is_fp16) {
   const uint32_t w[4] = {v.x, v.y, v.z, v.w};
@@ -95,15 +85,6 @@ quant_act_1x128_kernel(const uint4* __restrict__ x, uint2* __restrict__ q, float
 // with silu(x) = x / (1 + exp(-x)) evaluated in fp32 (fast exponential and quotient) from the
 // 16-bit inputs; act is then quantised exactly like act_1x128 above (same bytes and scales as
 // running per_token_cast_to_fp8 on the rounded activation).  Saves writing and re-reading act.
-__device__ __forceinline__ float silu_mul_round_bf16(float g, float u) {
-  // silu has no reference bit pattern to reproduce (the torch oracle rounds the activation to
-  // bf16, which absorbs a 2^-21 relative error in all but ~1e-4 of the elements), so the
-  // exponential and the quotient use the special-function unit: ex2.approx and rcp.approx
-  // instead of ~25 instructions of IEEE expf and division per element, which kept this kernel
-  // at half of the memory roofline.  g << 0: exp(-g) = inf, g / inf = -0.
-  const float act = __fmul_rn(__fdividef(g, 1.0f + __expf(-g)), u);
-  return __bfloat162float(__float2bfloat16_rn(act));
-}
 
 __global__ void __launch_bounds__(kActThreads)
 quant_swiglu_1x128_kernel(const uint16_t* __restrict__ h, uint2* __restrict__ q, float* __restrict__ s,

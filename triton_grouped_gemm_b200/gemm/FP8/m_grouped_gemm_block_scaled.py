@@ -93,3 +93,44 @@ def m_grouped_fp8_block_scaled_masked(a: Pair, b: Pair, out: Tensor, masked_m: T
             int(expected_m), n, k, -1, _lib.stream_ptr(a8.device))
     _lib.check(rc, "b200gemm_fp8_m_grouped_masked_block")
     return None
+
+
+def interleave_gate_up(w13: Tensor) -> Tensor:
+    """[..., 2*I, H] with gate rows then up rows -> the same rows interleaved in 128-row blocks
+    (gate block 0, up block 0, gate block 1, ...), the weight layout of the SwiGLU-epilogue GEMM.
+    128x128 quantisation commutes with this permutation (it moves whole scale blocks)."""
+    two_i, h = w13.shape[-2:]
+    assert two_i % 256 == 0, "the intermediate size must be a multiple of 128"
+    lead = w13.shape[:-2]
+    return w13.reshape(*lead, 2, two_i // 256, 128, h).transpose(-4, -3).reshape(*lead, two_i, h).contiguous()
+
+
+def m_grouped_fp8_block_scaled_swiglu(a: Pair, b_interleaved: Pair, size_per_group: Tensor, *, masked_stride: int = 0,
+                                      group_to_b: Optional[Tensor] = None, num_sms: int = -1) -> Pair:
+    """Gate+up GEMM with SwiGLU and the 1x128 quantiser in its epilogue.  ``b_interleaved`` is the
+    quantised ``interleave_gate_up(w13)``.  Returns (act e4m3 [M, I], scales fp32 [M, I/128]) - the
+    same bytes and scales as ``swiglu_per_token_cast_to_fp8(m_grouped_fp8_block_scaled(a, w13))``.
+    ``masked_stride`` > 0: masked row layout (``masked_stride`` rows per group, the first
+    ``size_per_group[g]`` valid; other rows of the results are left unwritten)."""
+    a8, a_s, b8, b_s, m, n, k, g = _check_pairs(a, b_interleaved)
+    assert n % 256 == 0, "n = 2 x intermediate size must be a multiple of 256"
+    _lib.require_cuda(size_per_group)
+    sizes, is64 = _lib.sizes_arg(size_per_group)
+    num_groups = size_per_group.numel()
+    if group_to_b is not None:
+        assert group_to_b.dtype == torch.int32 and group_to_b.is_contiguous() and group_to_b.numel() == num_groups
+        _lib.require_cuda(group_to_b)
+    else:
+        assert num_groups == g
+    if masked_stride:
+        assert m == num_groups * masked_stride, "a must hold masked_stride rows per group"
+    inter = n // 2
+    act = torch.empty((m, inter), device=a8.device, dtype=torch.float8_e4m3fn)
+    act_scale = torch.empty((m, inter // 128), device=a8.device, dtype=torch.float32)
+    with torch.cuda.device(a8.device):
+        rc = _lib.load().b200gemm_fp8_m_grouped_block_swiglu(
+            _lib.ptr(a8), _lib.ptr(a_s), _lib.ptr(b8), _lib.ptr(b_s), _lib.ptr(act), _lib.ptr(act_scale), _lib.ptr(sizes),
+            is64, num_groups, _lib.ptr(group_to_b) if group_to_b is not None else None, g, m, int(masked_stride), n, k,
+            int(num_sms), _lib.stream_ptr(a8.device))
+    _lib.check(rc, "b200gemm_fp8_m_grouped_block_swiglu")
+    return act, act_scale
