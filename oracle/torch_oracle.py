@@ -220,10 +220,13 @@ def _to_fp8_saturated(x: torch.Tensor, dtype) -> torch.Tensor:
     return x.clamp(min=-mx, max=mx).to(dtype)
 
 
-def _trans_quant_one_expert(x: torch.Tensor, block: int = 128, dtype=torch.float8_e4m3fn):
+def _trans_quant_one_expert(x: torch.Tensor, block: int = 128, dtype=torch.float8_e4m3fn, clamp_scale: bool = True):
     """quant/trans_per_block_quant_expand_128x.py:222-250 -- one expert:
     transpose [seq, dim] -> [dim, seq], zero-pad seq to a multiple of 128, one
-    scale = amax/448 per 128x128 block (no lower clamp), q = clamp(fp32(x)/scale)."""
+    scale = amax/448 per 128x128 block, q = clamp(fp32(x)/scale).  ``clamp_scale`` adds the
+    clamp of the scale to [1e-12, 3e38] that the reference's shipped operator applies (its
+    Triton kernel, same file :124-126); without it this is the torch helper alone, whose
+    all-zero block gives scale 0 and NaN bytes."""
     x = x.T
     dim, seq = x.shape
     seq_e = ceil_div(seq, block) * block
@@ -231,26 +234,31 @@ def _trans_quant_one_expert(x: torch.Tensor, block: int = 128, dtype=torch.float
     xe = xe.reshape(dim // block, block, seq_e // block, block).transpose(1, 2).reshape(-1, block * block)
     amax = xe.abs().amax(-1, True)
     scale = amax.float() / torch.finfo(dtype).max
+    if clamp_scale:
+        scale = scale.clamp(min=1e-12, max=3e38)
     q = _to_fp8_saturated(xe / scale, dtype)
     q = q.reshape(dim // block, seq_e // block, block, block).transpose(1, 2).reshape(dim, seq_e)
     return q, scale.reshape(dim // block, seq_e // block)
 
 
-def trans_quant_expand_ref(x: torch.Tensor, tokens_per_expert) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+def trans_quant_expand_ref(x: torch.Tensor, tokens_per_expert,
+                           clamp_scale: bool = True) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """Transposing 128x128 quantiser with per-expert expansion
     (quant/trans_per_block_quant_expand_128x.py:253-273).
 
     ``x`` [M, N] -> fp8 [N, M_EXPAND], scales [N/128, M_EXPAND/128], padded sizes.
     ``M_EXPAND = M + 128*G - M % 128`` (same file :172); columns / scales beyond the
-    sum of padded sizes are zero.  An all-zero 128x128 block inside an expert gives
-    scale 0 and NaN bytes (0/0) -- reference behaviour, kept.
+    sum of padded sizes are zero.  With ``clamp_scale`` (the operator's behaviour, see
+    ``_trans_quant_one_expert``) an all-zero 128x128 block inside an expert gives zero bytes and
+    scale 1e-12; with ``clamp_scale=False`` (the torch helper, which the CPU fixtures were made
+    with) it gives scale 0 and NaN bytes (0/0).
     """
     sz = _sizes_list(tokens_per_expert)
     m = x.shape[0]
     ne = len(sz)
     qs, ss = [], []
     for part in torch.split(x, sz, dim=0):
-        q, s = _trans_quant_one_expert(part)
+        q, s = _trans_quant_one_expert(part, clamp_scale=clamp_scale)
         qs.append(q)
         ss.append(s)
     q = torch.cat(qs, dim=-1)

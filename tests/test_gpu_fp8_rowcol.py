@@ -1,6 +1,7 @@
 """FP8 grouped GEMMs with per-row x per-channel scales against the CPU oracle (dequantised
-fp32 reference of the same fp8 bytes).  Tolerance rdiff <= 2e-3; only accumulation order and
-the final rounding differ, so 5e-4 is asserted."""
+fp32 reference of the same fp8 bytes) and against outputs of the reference's own Triton kernels
+(tests/golden/fp8_rowcol.pt, made on a B200 by tests/golden/make_golden_gpu.py).  Tolerance
+rdiff <= 2e-3; only accumulation order and the final rounding differ, so 5e-4 is asserted."""
 
 import pytest
 import torch
@@ -109,3 +110,49 @@ def test_k_grouped_rowcol(tokens, m, n, dt_a, dt_b, pair):
     for i, t in enumerate(tokens):
         if t == 0:
             assert torch.all(out[i] == 0)
+
+
+# ---------------------------------------------------------------- against the reference's kernels
+
+def _rowcol_cases():
+    import sys
+
+    from conftest import GOLDEN
+
+    if str(GOLDEN) not in sys.path:
+        sys.path.insert(0, str(GOLDEN))
+    import fp8_rowcol_cases as C
+
+    return C, {"per_channel_cast_to_fp8": O.per_channel_cast_to_fp8, "per_expert_cast_to_fp8": O.per_expert_cast_to_fp8}
+
+
+@pytest.mark.parametrize("pair", [-1, 0], ids=["auto", "single"])
+@pytest.mark.parametrize("name", ["one_tile_e4e4", "ragged_e5e4_fp16", "ragged_e4e4_ktail", "test_family_e5e4"])
+def test_m_grouped_rowcol_vs_reference_kernel_output(golden_dir, name, pair):
+    C, casts = _rowcol_cases()
+    e = torch.load(golden_dir / "fp8_rowcol.pt", weights_only=False)["m_grouped"][name]
+    inp = C.m_case_inputs(name, casts)
+    assert C.input_hashes(inp) == e["inputs_sha256"]
+    _lib.load().b200gemm_set_cta_pair(pair)
+    out = gmm_fp8_act_per_channel_w_per_expert(inp["a8"].to(DEV), inp["a_scale"].to(DEV), inp["b8"].to(DEV),
+                                               inp["b_scale"].reshape(-1).to(DEV), inp["sizes"].to(DEV),
+                                               inp["dtype_out"]).cpu()
+    assert out.dtype == e["out"].dtype and out.shape == e["out"].shape
+    assert O.rdiff(out.float(), e["out"].float()) < 5e-4
+
+
+@pytest.mark.parametrize("pair", [-1, 0], ids=["auto", "single"])
+@pytest.mark.parametrize("name", ["one_tile_e4e4", "ragged_e4e4", "ragged_e5e4"])
+def test_k_grouped_rowcol_vs_reference_kernel_output(golden_dir, name, pair):
+    C, casts = _rowcol_cases()
+    e = torch.load(golden_dir / "fp8_rowcol.pt", weights_only=False)["k_grouped"][name]
+    inp = C.k_case_inputs(name, casts)
+    assert C.input_hashes(inp) == e["inputs_sha256"]
+    _lib.load().b200gemm_set_cta_pair(pair)
+    g, k_tot = inp["tokens"].numel(), int(inp["tokens"].sum())
+    xs = inp["x_scale"].t().contiguous().to(DEV).t()   # group-major memory, logical [M, G]
+    ys = inp["y_scale"].t().contiguous().to(DEV).t()
+    out = matmul(inp["x8"].to(DEV), xs, inp["y8"].to(DEV), ys, inp["tokens"].to(DEV), inp["m"], inp["n"], k_tot, g,
+                 inp["dtype_a"], inp["dtype_b"]).cpu()
+    assert out.shape == e["out"].shape and out.dtype == e["out"].dtype
+    assert O.rdiff(out.float(), e["out"].float()) < 5e-4

@@ -127,13 +127,21 @@ def test_trans_quant_extreme_blocks_and_signed_zeros(dtype):
     _assert_same(q, s, q_ref, s_ref)
 
 
-def test_trans_quant_all_zero_block_gives_reference_nan_bytes():
-    x = torch.randn(256, 128).to(torch.bfloat16)
-    x[128:256] = 0  # second 128x128 block of the only expert is all zero -> scale 0, 0/0
-    t = torch.tensor([256])
+def test_trans_quant_all_zero_and_tiny_blocks_follow_the_operators_scale_clamp():
+    """The reference's shipped operator clamps the block scale to [1e-12, 3e38]
+    (quant/trans_per_block_quant_expand_128x.py:124-126): an all-zero block gives zero bytes
+    and scale 1e-12 (not the torch helper's scale 0 and NaN bytes), and nothing downstream sees
+    a NaN."""
+    x = torch.randn(384, 128).to(torch.bfloat16)
+    x[128:256] = 0  # second 128x128 block of the only expert is all zero
+    x[130, 5] = -0.0
+    x[256:384] = (torch.randn(128, 128) * 1e-11).to(torch.bfloat16)  # amax / 448 below the clamp
+    t = torch.tensor([384])
     q_ref, s_ref, _ = O.trans_quant_expand_ref(x, t)
     q, s, _ = trans_per_block_quant_expand_128x(x.to(DEV), t.to(DEV))
     _assert_same(q, s, q_ref, s_ref)
+    assert float(s[0, 1]) == float(torch.tensor(1e-12, dtype=torch.float32))
+    assert not torch.isnan(q.float()).any()
 
 
 def test_full_size_linearity_property():

@@ -99,10 +99,35 @@ def test_casts_bit_exact(golden_dir, name):
 @pytest.mark.parametrize("name", ["equal", "ragged"])
 def test_trans_quant_bit_exact(golden_dir, name):
     c = _load(golden_dir, "trans_quant.pt")[name]
-    q, s, pad = O.trans_quant_expand_ref(c["x"], c["sizes"])
-    assert torch.equal(_u8(q), c["q"])
-    assert torch.equal(s.view(torch.int32), c["s"].view(torch.int32))
-    assert pad.tolist() == c["padded"].tolist()
+    # the fixture comes from the reference's torch helper; the operator's clamp of the scale to
+    # [1e-12, 3e38] touches no block of it, so both forms of the oracle must reproduce it
+    for clamp_scale in (False, True):
+        q, s, pad = O.trans_quant_expand_ref(c["x"], c["sizes"], clamp_scale=clamp_scale)
+        assert torch.equal(_u8(q), c["q"])
+        assert torch.equal(s.view(torch.int32), c["s"].view(torch.int32))
+        assert pad.tolist() == c["padded"].tolist()
+
+
+def test_trans_quant_scale_clamp_of_the_shipped_operator():
+    """quant/trans_per_block_quant_expand_128x.py:124-126: scale = clamp(amax / fmax, 1e-12, 3e38).
+    An all-zero block: zero bytes (sign kept) and scale float32(1e-12); a block whose amax / 448 is
+    below 1e-12 is divided by 1e-12; the torch helper alone gives scale 0 and NaN bytes."""
+    x = torch.randn(384, 128).to(torch.bfloat16)
+    x[128:256] = 0
+    x[130, 5] = -0.0
+    x[256:384] = (torch.randn(128, 128) * 1e-11).to(torch.bfloat16)
+    sizes = torch.tensor([384])
+    q, s, _ = O.trans_quant_expand_ref(x, sizes)
+    tiny = torch.tensor(1e-12, dtype=torch.float32)
+    assert s[0, 1] == tiny and s[0, 2] == tiny and s[0, 0] > 1e-3
+    qb = _u8(q)
+    assert set(qb[:, 128:256].unique().tolist()) <= {0x00, 0x80}
+    assert qb[5, 130] == 0x80
+    expect = (x[256:384].float() / tiny).clamp(-448, 448).to(torch.float8_e4m3fn).t()
+    assert torch.equal(qb[:, 256:384], _u8(expect))
+    q0, s0, _ = O.trans_quant_expand_ref(x, sizes, clamp_scale=False)
+    assert s0[0, 1] == 0 and bool((_u8(q0)[:, 128:256] == 0xFF).all())
+    assert torch.equal(_u8(q0)[:, :128], qb[:, :128]) and s0[0, 0] == s[0, 0]
 
 
 def test_dequant_roundtrip_is_close():
@@ -120,3 +145,55 @@ def test_routing_sizes_deterministic():
     assert s.numel() == 128 and int((s % 128).abs().sum()) == 0
     assert 655360 <= int(s.sum()) <= 655360 + 128 * 128
     assert torch.equal(s, O.routing_sizes(128, 655360, seed=2026))
+
+
+# ---------------------------------------------------------------- FP8 row x channel GEMMs
+# fp8_rowcol.pt holds what the reference's own Triton kernels computed on a B200
+# (tests/golden/make_golden_gpu.py); the inputs are rebuilt here from the seed and must hash to
+# what the kernels were given.
+
+def _rowcol_casts():
+    return {"per_channel_cast_to_fp8": O.per_channel_cast_to_fp8, "per_expert_cast_to_fp8": O.per_expert_cast_to_fp8}
+
+
+def _rowcol_cases():
+    import sys
+
+    from conftest import GOLDEN
+
+    if str(GOLDEN) not in sys.path:
+        sys.path.insert(0, str(GOLDEN))
+    import fp8_rowcol_cases as C
+
+    return C
+
+
+@pytest.mark.parametrize("name", ["one_tile_e4e4", "ragged_e5e4_fp16", "ragged_e4e4_ktail", "test_family_e5e4"])
+def test_fp8_rowcol_m_grouped_oracle_vs_reference_kernel(golden_dir, name):
+    C = _rowcol_cases()
+    e = _load(golden_dir, "fp8_rowcol.pt")["m_grouped"][name]
+    assert "out" in e, e.get("error")
+    inp = C.m_case_inputs(name, _rowcol_casts())
+    assert C.input_hashes(inp) == e["inputs_sha256"]
+    ref = O.fp8_rowcol_m_grouped_ref(inp["a8"], inp["a_scale"], inp["b8"], inp["b_scale"], inp["sizes"], inp["dtype_out"])
+    assert ref.dtype == e["out"].dtype and ref.shape == e["out"].shape
+    # same products, fp32 accumulation in a different order, one rounding: measured 0 .. 7e-10
+    assert O.rdiff(ref.float(), e["out"].float()) < 5e-4
+
+
+@pytest.mark.parametrize("name", ["one_tile_e4e4", "ragged_e4e4", "ragged_e5e4"])
+def test_fp8_rowcol_k_grouped_oracle_vs_reference_kernel(golden_dir, name):
+    C = _rowcol_cases()
+    e = _load(golden_dir, "fp8_rowcol.pt")["k_grouped"][name]
+    assert "out" in e, e.get("error")
+    inp = C.k_case_inputs(name, _rowcol_casts())
+    assert C.input_hashes(inp) == e["inputs_sha256"]
+    g = inp["tokens"].numel()
+    assert inp["x_scale"].shape == (inp["m"], g) and (g == 1 or inp["x_scale"].stride() == (1, inp["m"]))  # group-major
+    ref = O.fp8_rowcol_k_grouped_ref(inp["x8"], inp["x_scale"], inp["y8"], inp["y_scale"], inp["tokens"], inp["m"],
+                                     inp["n"], g)
+    assert ref.shape == e["out"].shape
+    assert O.rdiff(ref.float(), e["out"].float()) < 5e-4  # measured 0 .. 6e-8
+    for i, t in enumerate(inp["tokens"].tolist()):
+        if t == 0:
+            assert bool((e["out"][i] == 0).all())

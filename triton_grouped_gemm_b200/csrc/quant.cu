@@ -227,10 +227,15 @@ quant_w_128x128_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ q, 
 // ------------------------------------------------------------------ transposing 128x128 with expansion
 // Follows per_block_trans_quant_expand_torch (quant/trans_per_block_quant_expand_128x.py:216-273):
 // per expert, rows are padded with zeros to a multiple of 128; per 128x128 block
-//   scale = amax / 448 (no lower clamp),  q = e4m3( clamp(fp32(x) / scale, +-448) )
+//   scale = clamp(amax / 448, 1e-12, 3e38),  q = e4m3( clamp(fp32(x) / scale, +-448) )
 // and the block is written transposed: out[n, pad_start_g + local_row].  Columns and scales
-// past the last padded expert (up to m_expand) are zero.  An all-zero block gives scale 0 and
-// 0/0 = NaN bytes exactly like the torch code on the host (0xff).
+// past the last padded expert (up to m_expand) are zero.  The clamp of the scale is the one the
+// reference's shipped operator applies (its Triton kernel, same file :124-126); the torch helper
+// has none and turns an all-zero block (zero gradients, a dead column) into scale 0 and NaN
+// bytes, which would poison every product that consumes them.  With the clamp such a block
+// gives zero bytes and scale 1e-12; blocks whose amax / 448 is at least 1e-12 are bit for bit
+// what the torch helper produces.  (The block maximum ignores NaN elements, as a reduction
+// with max.f32 does; a NaN element itself becomes the byte 0xff.)
 constexpr int kTqPitch = 132;  // bytes per staged row: 33 words -> conflict-free column reads
 
 // Largest |x| of eight 16-bit floats as raw bits (sign cleared).  For bf16 and fp16 alike the
@@ -371,7 +376,7 @@ quant_trans_expand_kernel(const uint16_t* __restrict__ x, const void* __restrict
     uint32_t* dst0 = reinterpret_cast<uint32_t*>(stage + tr * kTqPitch + tc);
     const float amax_fast = to_f32(static_cast<uint16_t>(mx), kFp16);
     // fast block: no NaN/Inf anywhere, scale and its reciprocal far from the ends of the range
-    if (mx < kInfBits && amax_fast >= 0x1p-60f && amax_fast <= 0x1p100f) {
+    if (mx < kInfBits && amax_fast >= 0x1p-30f && amax_fast <= 0x1p100f) {
       const float scale = __fdiv_rn(amax_fast, 448.0f);
       if (threadIdx.x == 0) s[static_cast<long long>(nt) * scale_cols + mt] = scale;
       const float r = __frcp_rn(scale);
@@ -383,7 +388,8 @@ quant_trans_expand_kernel(const uint16_t* __restrict__ x, const void* __restrict
         dst[1] = o.y;
       }
     } else {
-      // NaN/Inf in the block, an all-zero block or an extreme scale: per-element IEEE division
+      // NaN/Inf in the block, an all-zero block or an extreme scale (any block whose scale the
+      // clamp could touch lands here): per-element IEEE division
       // with the fp32 maximum taken by fmaxf
       float amax = 0.f;
 #pragma unroll
@@ -396,7 +402,8 @@ quant_trans_expand_kernel(const uint16_t* __restrict__ x, const void* __restrict
       amax = redf[0];
 #pragma unroll
       for (int i = 1; i < kBlkThreads / 32; ++i) amax = fmaxf(amax, redf[i]);
-      const float scale = __fdiv_rn(amax, 448.0f);
+      float scale = __fdiv_rn(amax, 448.0f);
+      scale = fminf(fmaxf(scale, 1e-12f), 3e38f);  // the shipped operator's clamp
       if (threadIdx.x == 0) s[static_cast<long long>(nt) * scale_cols + mt] = scale;
 #pragma unroll
       for (int p = 0; p < 8; ++p) {

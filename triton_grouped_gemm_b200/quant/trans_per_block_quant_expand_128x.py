@@ -2,8 +2,11 @@
 quant/trans_per_block_quant_expand_128x.py:135-213).
 
 Output bytes and scales equal the reference's torch implementation
-``per_block_trans_quant_expand_torch`` (:253-273); the reference's own Triton kernel differs
-from that torch code only in clamping the scale to [1e-12, 3e38] (:125)."""
+``per_block_trans_quant_expand_torch`` (:253-273) with the one addition its shipped Triton
+operator makes: the block scale is clamped to [1e-12, 3e38] (:125).  An all-zero 128x128 block
+(zero gradients, a dead column) therefore gives zero bytes and scale 1e-12 instead of the torch
+helper's scale 0 and NaN bytes; every block with amax / 448 >= 1e-12 is bit for bit the torch
+result."""
 
 from __future__ import annotations
 
