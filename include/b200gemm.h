@@ -37,14 +37,20 @@ extern "C" {
 #define B200GEMM_DEV_TIMEOUT_MMA 0x2u
 #define B200GEMM_DEV_TIMEOUT_EPILOGUE 0x4u
 #define B200GEMM_DEV_TIMEOUT_PROMOTE 0x8u
+/* the group sizes of an M-grouped call added up to more rows than m_rows: the excess rows were
+ * neither read nor written (the call computed the groups that fit) */
 #define B200GEMM_DEV_BAD_GROUP_SIZE 0x10u
+/* a row mover was given a rank, a destination row or a source row outside its buffers: that row
+ * was skipped */
+#define B200GEMM_DEV_BAD_ROW_INDEX 0x20u
 
 /* ---- library services (no reference counterpart: the reference reports errors with Python
  *      assert / ValueError and lets a wedged kernel hang) -------------------------------- */
 int b200gemm_version(void);
 const char* b200gemm_last_error(void);
-/* Copies the current device's status word to *out_status (host pointer); synchronises the
- * device.  clear != 0 resets it afterwards. */
+/* Waits for all work on the current device (cudaDeviceSynchronize, so kernels on non-blocking
+ * streams are covered), then copies its status word to *out_status (host pointer).
+ * clear != 0 resets it afterwards. */
 int b200gemm_device_status(unsigned* out_status, int clear);
 int b200gemm_sm_count(void);
 /* Tuning override for the 16-bit M-grouped kernels: 0 = pick the tile width (64 / 128 / 256
@@ -67,8 +73,12 @@ int b200gemm_cta_pair_grid(void);
  * gemm/BF16/m_grouped_gemm.py:43-292).
  *   A [m_rows, k] row-major, compact (no padding rows); C [m_rows, n] row-major.
  *   trans_b != 0: B [G, n, k];  trans_b == 0: B [G, k, n].
- *   sizes [G]: rows per group (sum <= m_rows).  Requires k % 8 == 0, n % 8 == 0,
- *   16-byte aligned base pointers.  num_sms <= 0 = all SMs. */
+ *   sizes [G]: rows per group, sum <= m_rows.  The kernels enforce that bound themselves (the
+ *   sizes live on the device, the host cannot check them without a synchronisation): a group
+ *   that would run past row m_rows is cut off there, later groups get no rows, nothing at or
+ *   beyond row m_rows of A, C or the row scales is touched, and B200GEMM_DEV_BAD_GROUP_SIZE is
+ *   raised in the status word.  The same holds for every M-grouped entry point below.
+ *   Requires k % 8 == 0, n % 8 == 0, 16-byte aligned base pointers.  num_sms <= 0 = all SMs. */
 int b200gemm_m_grouped(const void* a, const void* b, void* c, const void* sizes, int sizes_is_i64,
                        int num_groups, int64_t m_rows, int n, int k, int trans_b, int dtype, int num_sms,
                        void* stream);
@@ -231,22 +241,28 @@ int b200quant_trans_expand_128x(const void* x, const void* sizes, int sizes_is_i
 
 /* dst[i, :] = src[idx[i], :] for i < rows (rows of row_bytes bytes, a multiple of 16; idx int64).
  * The dispatch-side gather into expert-major order; the reference has this only in its vendored
- * baseline extension (grouped_gemm/csrc/permute.cu:40-297, moe_permute_topK_kernel). */
+ * baseline extension (grouped_gemm/csrc/permute.cu:40-297, moe_permute_topK_kernel).  src holds
+ * src_rows rows: an index outside [0, src_rows) (such as the -1 of a rejected routing pair) is
+ * skipped - dst[i] keeps its contents - and B200GEMM_DEV_BAD_ROW_INDEX is raised. */
 int b200moe_gather_rows(const void* src, const int64_t* idx, void* dst, int64_t rows, int64_t row_bytes,
-                        void* stream);
+                        int64_t src_rows, void* stream);
 
 /* out[t, :] = bf16(sum_k weights[t,k] * y[pos[t,k], :]), fp32 accumulation: the combine-side
  * weighted sum of a token's top-k expert outputs (baseline counterpart:
- * grouped_gemm/csrc/permute.cu, moe_recover_topK_kernel).  y, out bf16 with `hidden` columns. */
+ * grouped_gemm/csrc/permute.cu, moe_recover_topK_kernel).  y [y_rows, hidden], out bf16.  A pos
+ * outside [0, y_rows) contributes nothing and raises B200GEMM_DEV_BAD_ROW_INDEX. */
 int b200moe_combine_topk(const void* y, const int64_t* pos, const float* weights, void* out, int64_t tokens, int top_k,
-                         int hidden, void* stream);
+                         int hidden, int64_t y_rows, void* stream);
 
 /* Routing plan of an MoE step: counting sort of the (token, k) pairs by expert.
  * expert int64 [n] with values in [0, num_experts), num_experts <= 1024.  counts int32 [E]: pairs
  * per expert; cursor int32 [E]: scratch (ends as the END of each expert's range); order int64 [n]:
  * pair indices grouped by expert (expert e's pairs at [sum(counts[:e]), +counts[e]), order inside
- * a range unspecified); pos int64 [n] = order^-1.  The role of the sort in the vendored baseline's
- * permute (grouped_gemm/csrc/permute.cu:504-690), without a comparison sort. */
+ * a range unspecified); pos int64 [n] = order^-1.  A pair whose expert id lies outside the range
+ * (a dropped token's -1) is counted nowhere, raises B200GEMM_DEV_BAD_ROW_INDEX, gets pos = -1,
+ * and leaves one slot at the end of order at -1; the row movers skip such indices.  The role of
+ * the sort in the vendored baseline's permute (grouped_gemm/csrc/permute.cu:504-690), without a
+ * comparison sort. */
 int b200moe_route_plan(const int64_t* expert, int64_t n, int num_experts, int* counts, int* cursor, int64_t* order,
                        int64_t* pos, void* stream);
 
@@ -254,20 +270,38 @@ int b200moe_route_plan(const int64_t* expert, int64_t n, int num_experts, int* c
  * dst_bases[dst_rank[i]][dst_row[i], :] = src[src_idx[i], :], and
  * out[t, :] = bf16(sum_k weights[t,k] * src_bases[pair_rank[t,k]][pair_row[t,k], :]).
  * dst_bases / src_bases: HOST arrays of `world` (<= 16) device pointers, each buffer holding
- * capacity_rows rows; ranks and rows are bounds-checked on the device (a bad index sets bit 5 of
- * the status word and is skipped).  They replace the all-to-alls of an expert-parallel layer:
- * the caller synchronises the ranks between writing and reading (e.g. a barrier collective).
- * No counterpart in the reference. */
+ * capacity_rows rows; src holds src_rows rows.  Ranks, destination rows and source rows are
+ * bounds-checked on the device (a bad index raises B200GEMM_DEV_BAD_ROW_INDEX and is skipped).
+ * They replace the all-to-alls of an expert-parallel layer: the caller synchronises the ranks
+ * between writing and reading (e.g. a barrier collective).
+ * blocks > 0: the mover runs as that many 1024-thread blocks (one per SM at most) instead of
+ * filling the GPU, for running beside a persistent GEMM that was given the other SMs (num_sms);
+ * <= 0: fill the GPU.  No counterpart in the reference. */
 int b200moe_scatter_rows_multi(const void* src, const int64_t* src_idx, void* const* dst_bases, const int* dst_rank,
                                const int64_t* dst_row, int64_t rows, int64_t row_bytes, int world,
-                               int64_t capacity_rows, void* stream);
-/* blocks > 0: b200moe_scatter_rows_multi launches that many 1024-thread blocks (one per SM at most)
- * instead of filling the GPU, for running beside a persistent GEMM that was given the other SMs
- * (num_sms).  0 restores the default.  Process-wide. */
-int b200moe_set_background_blocks(int blocks);
+                               int64_t capacity_rows, int64_t src_rows, int blocks, void* stream);
 int b200moe_combine_topk_multi(const void* const* src_bases, const int* pair_rank, const int64_t* pair_row,
                                const float* weights, void* out, int64_t tokens, int top_k, int hidden, int world,
                                int64_t capacity_rows, void* stream);
+
+/* Quantise-on-dispatch.  For the pairs i in [first_pair, first_pair + num_pairs) of a step's send
+ * order: the 16-bit row x[token_of_pair[i], :] (x [tokens, hidden], hidden % 128 == 0, <= 8192) is
+ * quantised 1x128 - bytes and scales identical to b200quant_act_1x128 - and stored at row
+ * dst_row[i] of rank dst_rank[i]: the e4m3 row into row_bases (hidden bytes per row), its
+ * hidden/128 fp32 scales into scale_bases, and the pair's return address (int64 i, int64
+ * my_rank) into meta_bases (16 bytes per row).  One kernel instead of the activation quantiser
+ * plus one scatter per payload, and the fp8 copy of x never goes through HBM.  Bounds checks and
+ * `blocks` as above.  No counterpart in the reference. */
+int b200moe_dispatch_quant_rows_multi(const void* x, const int64_t* token_of_pair, void* const* row_bases,
+                                      void* const* scale_bases, void* const* meta_bases, const int* dst_rank,
+                                      const int64_t* dst_row, int64_t first_pair, int64_t num_pairs, int64_t tokens,
+                                      int hidden, int dtype, int world, int64_t capacity_rows, int my_rank, int blocks,
+                                      void* stream);
+/* The way back: dst_bases[meta[r][1]][meta[r][0], :] = src[r, :] for r < rows, meta [rows, 2] int64
+ * being the return addresses left by b200moe_dispatch_quant_rows_multi beside the rows
+ * (capacity_rows = rows of each return buffer).  No counterpart in the reference. */
+int b200moe_return_rows_multi(const void* src, const int64_t* meta, void* const* dst_bases, int64_t rows,
+                              int64_t row_bytes, int world, int64_t capacity_rows, int blocks, void* stream);
 
 /* Buffers other processes of the node can address, for the peer-memory row movers above.
  * alloc: cudaMalloc on the current device, zero-filled.  export: 64-byte CUDA IPC handle of a

@@ -159,13 +159,14 @@ def _peer_plan_worker(rank, world, port, results):
         plan = make_peer_plan(idx, e, dist.group.WORLD, cap)
         mine = dict(x=x, idx=idx, w=w, token_of_pair=plan.token_of_pair, dst_rank=plan.dst_rank, dst_row=plan.dst_row,
                     pair_rank=plan.pair_rank, pair_row=plan.pair_row, rows_here=plan.rows_here,
-                    block_sizes=plan.block_sizes, block_expert=plan.block_expert)
+                    size_per_group=plan.size_per_group)
         everyone = [None] * world
         dist.all_gather_object(everyone, mine)
         # replay the scatter of all ranks into all ranks' buffers
         bufs = [torch.full((cap, h), float("nan")) for _ in range(world)]
         written = [torch.zeros(cap, dtype=torch.int32) for _ in range(world)]
         owner_expert = [torch.full((cap,), -1, dtype=torch.int64) for _ in range(world)]
+        row_source = [torch.full((cap,), -1, dtype=torch.int64) for _ in range(world)]
         for src, p in enumerate(everyone):
             flat = p["idx"].reshape(-1)
             order = torch.argsort(flat, stable=True)
@@ -174,15 +175,18 @@ def _peer_plan_worker(rank, world, port, results):
                 bufs[d][r] = p["x"][int(p["token_of_pair"][i])]
                 written[d][r] += 1
                 owner_expert[d][r] = int(flat[order[i]])
+                row_source[d][r] = src
         ok = True
         for d, p in enumerate(everyone):
             r = p["rows_here"]
             ok &= bool((written[d][:r] == 1).all()) and bool((written[d][r:] == 0).all())   # dense, no collisions
-            ok &= int(p["block_sizes"].sum()) == r and p["block_sizes"].numel() == world * e_loc
-            # rows of block b (source-major, expert-minor) all belong to expert d*e_loc + block_expert[b]
+            ok &= int(p["size_per_group"].sum()) == r and p["size_per_group"].numel() == e_loc
+            # one contiguous row group per local expert, inside it the source ranks in order
             start = 0
-            for b, n in enumerate(p["block_sizes"].tolist()):
-                ok &= bool((owner_expert[d][start:start + n] == d * e_loc + int(p["block_expert"][b])).all())
+            for l, n in enumerate(p["size_per_group"].tolist()):
+                ok &= bool((owner_expert[d][start:start + n] == d * e_loc + l).all())
+                src_run = row_source[d][start:start + n]
+                ok &= bool((src_run[1:] >= src_run[:-1]).all())
                 start += n
         # experts: row * (global expert id + 1); combine reads (pair_rank, pair_row)
         ybufs = [bufs[d] * (owner_expert[d].clamp(min=0).float()[:, None] + 1.0) for d in range(world)]
@@ -212,62 +216,78 @@ def test_two_gloo_ranks_peer_memory_plan():
 
 
 def _peer_chunk_plan_worker(rank, world, port, results):
-    """Replay of the pipelined peer-memory exchange: chunk-major scatter of rows and return
-    addresses, per-chunk blocks, push of the results back through the return addresses."""
-    from triton_grouped_gemm_b200.ep.p2p import make_peer_chunk_plan
+    """Replay of the pipelined peer-memory exchange: chunk-major send order, every rank's buffer
+    laid out [local expert][source rank], return addresses (send-order position, source rank) as
+    the dispatch kernel writes them, push of the results back through them."""
+    from triton_grouped_gemm_b200.ep.p2p import chunk_bounds, make_peer_chunk_plan
 
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
-        t, e, k, h, cap, chunks = 26 + 5 * rank, 8, 3, 4, 200, 2
+        t, e, k, h, cap, chunks = 26 + 5 * rank, 12, 3, 4, 200, 4   # 6 local experts in 4 uneven chunks
         e_loc = e // world
-        ec = e_loc // chunks
+        bounds = chunk_bounds(e_loc, chunks)
         idx, w = synthetic_routing(t, e, k, seed=40 + rank)
+        if rank == 1:
+            idx[3, 2] = -1          # a dropped pair: sent nowhere, contributes nothing
         gen = torch.Generator().manual_seed(400 + rank)
         x = torch.randn(t, h, generator=gen)
-        plan = make_peer_chunk_plan(idx, e, dist.group.WORLD, cap, chunks)
+        plan = make_peer_chunk_plan(idx, e, dist.group.WORLD, cap, bounds)
         mine = dict(x=x, idx=idx, token_of_pair=plan.token_of_pair, dst_rank=plan.dst_rank, dst_row=plan.dst_row,
-                    meta=plan.meta, recv_offsets=plan.recv_offsets, send_offsets=plan.send_offsets,
-                    block_sizes=plan.block_sizes, block_expert=plan.block_expert, n=t * k)
+                    recv_offsets=plan.recv_offsets, send_offsets=plan.send_offsets,
+                    size_per_group=plan.size_per_group, n=int(plan.token_of_pair.numel()), pairs=t * k)
         everyone = [None] * world
         dist.all_gather_object(everyone, mine)
         bufs = [torch.full((cap, h), float("nan")) for _ in range(world)]
         metas = [torch.full((cap, 2), -1, dtype=torch.int64) for _ in range(world)]
         written = [torch.zeros(cap, dtype=torch.int32) for _ in range(world)]
-        row_expert = [torch.full((cap,), -1, dtype=torch.int64) for _ in range(world)]
-        ok = True
+        sent_chunk = [torch.full((cap,), -1, dtype=torch.int64) for _ in range(world)]
+        ok = bounds[0] == 0 and bounds[-1] == e_loc and len(bounds) == chunks + 1
         for src, p in enumerate(everyone):
-            ok &= p["send_offsets"][-1] == p["n"]
-            for i in range(p["n"]):
-                d, r = int(p["dst_rank"][i]), int(p["dst_row"][i])
-                bufs[d][r] = p["x"][int(p["token_of_pair"][i])]
-                metas[d][r] = p["meta"][i]
-                written[d][r] += 1
-        # every rank's buffer: dense, chunk ranges consistent with the blocks, experts as declared
+            ok &= p["send_offsets"][-1] == p["n"] and p["n"] == int(((p["idx"] >= 0) & (p["idx"] < e)).sum())
+            for c in range(chunks):
+                for i in range(p["send_offsets"][c], p["send_offsets"][c + 1]):
+                    d, r = int(p["dst_rank"][i]), int(p["dst_row"][i])
+                    bufs[d][r] = p["x"][int(p["token_of_pair"][i])]
+                    metas[d][r] = torch.tensor([i, src])
+                    written[d][r] += 1
+                    sent_chunk[d][r] = c
+        # every rank's buffer: dense; chunk c = rows [recv_offsets[c], recv_offsets[c+1]) = experts
+        # [bounds[c], bounds[c+1]), each expert one contiguous group with the sources in order
+        row_expert = [torch.full((cap,), -1, dtype=torch.int64) for _ in range(world)]
         for d, p in enumerate(everyone):
             r_tot = p["recv_offsets"][-1]
             ok &= bool((written[d][:r_tot] == 1).all()) and bool((written[d][r_tot:] == 0).all())
-            for c in range(chunks):
-                lo, hi = p["recv_offsets"][c], p["recv_offsets"][c + 1]
-                ok &= int(p["block_sizes"][c].sum()) == hi - lo
-                start = lo
-                for b, nrows in enumerate(p["block_sizes"][c].tolist()):
-                    src = b // ec
-                    exp_global = d * e_loc + int(p["block_expert"][c][b])
-                    for r in range(start, start + nrows):
-                        back_pos, back_rank = int(metas[d][r][0]), int(metas[d][r][1])
-                        ok &= back_rank == src and 0 <= back_pos < everyone[back_rank]["n"]
-                        row_expert[d][r] = exp_global
-                    start += nrows
+            ok &= int(p["size_per_group"].sum()) == r_tot
+            start = 0
+            for l, nrows in enumerate(p["size_per_group"].tolist()):
+                c = max(cc for cc in range(chunks) if bounds[cc] <= l)
+                ok &= p["recv_offsets"][c] <= start and start + nrows <= p["recv_offsets"][c + 1]
+                ok &= bool((sent_chunk[d][start:start + nrows] == c).all())
+                srcs = metas[d][start:start + nrows, 1]
+                ok &= bool((srcs[1:] >= srcs[:-1]).all())
+                for r in range(start, start + nrows):
+                    back_pos, back_rank = int(metas[d][r][0]), int(metas[d][r][1])
+                    ok &= 0 <= back_pos < everyone[back_rank]["n"]
+                    # the pair really was routed to this expert
+                    pr = everyone[back_rank]
+                    flat = pr["idx"].reshape(-1)
+                    ok &= bool(torch.equal(pr["x"][int(pr["token_of_pair"][back_pos])], bufs[d][r]))
+                    row_expert[d][r] = d * e_loc + l
+                start += nrows
         # results = row * (expert + 1), pushed back through the return addresses, combined locally
-        rets = [torch.full((p["n"], h), float("nan")) for p in everyone]
+        rets = [torch.zeros(p["pairs"], h) for p in everyone]
         for d in range(world):
             r_tot = everyone[d]["recv_offsets"][-1]
             y = bufs[d][:r_tot] * (row_expert[d][:r_tot].float()[:, None] + 1.0)
             for r in range(r_tot):
                 rets[int(metas[d][r][1])][int(metas[d][r][0])] = y[r]
-        out = (rets[rank][plan.pos].view(t, k, h) * w[:, :, None]).sum(1)
-        ok &= torch.allclose(out, _reference(x, idx, w), atol=1e-5)
+        pos = plan.pos
+        contrib = torch.where((pos >= 0)[:, None], rets[rank][pos.clamp(min=0)], torch.zeros(1, h))
+        out = (contrib.view(t, k, h) * w[:, :, None]).sum(1)
+        valid = ((idx >= 0) & (idx < e)).float()
+        ref = (x[:, None, :] * (idx.clamp(min=0)[:, :, None].float() + 1.0) * (w * valid)[:, :, None]).sum(1)
+        ok &= torch.allclose(out, ref, atol=1e-5)
         results[rank] = bool(ok)
     finally:
         dist.destroy_process_group()

@@ -1,7 +1,9 @@
 """Expert-parallel FP8 layer on two GPUs (skipped on a single-GPU box): both transports - NCCL
 all-to-all and the peer-memory row movers - must reproduce the single-rank layer exactly, over
 several steps that reuse the exchange buffers; each transport in its one-shot form (chunks = 1)
-and pipelined over four groups of local experts."""
+and pipelined over groups of local experts (4 even groups; for peer memory also 3 uneven ones,
+where quantise-on-dispatch replaces the activation quantiser).  The peer-memory layers are
+closed collectively before the process group goes away."""
 
 import os
 import socket
@@ -40,12 +42,15 @@ def _worker(rank, world, port, transport, chunks, results):
             out = layer.forward(x, idx.to(dev), w.to(dev))
             ref = full.forward(x, idx.to(dev), w.to(dev))
             worst = max(worst, ((out.float() - ref.float()).abs().sum() / ref.float().abs().sum()).item())
-        results[rank] = (worst, _lib.device_status())
+        status = _lib.device_status()
+        layer.close()          # collective: waits for the device, barriers, then unmaps and frees
+        layer.close()          # a second call is a no-op
+        results[rank] = (worst, status)
     finally:
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("transport,chunks", [("p2p", 1), ("p2p", 4), ("nccl", 1), ("nccl", 4)])
+@pytest.mark.parametrize("transport,chunks", [("p2p", 1), ("p2p", 4), ("p2p", 3), ("nccl", 1), ("nccl", 4)])
 def test_two_gpu_layer_matches_single_rank(transport, chunks):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")

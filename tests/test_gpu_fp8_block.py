@@ -177,6 +177,14 @@ def test_full_size_properties():
     c2 = m_grouped_fp8_block_scaled(a, (b[0], b[1] * 2), sz)
     assert torch.equal(c1 * 2, c2)
     starts = torch.cumsum(sizes, 0) - sizes
+    # every group against real arithmetic: its first, a middle and its last rows (8 each)
+    for g in range(128):
+        s0, sz_g = int(starts[g]), int(sizes[g])
+        rows = (torch.cat([torch.arange(0, 8), torch.arange(sz_g // 2, sz_g // 2 + 8), torch.arange(sz_g - 8, sz_g)])
+                + s0).to(DEV)
+        ref = O.fp8_block_m_grouped_ref(a[0][rows].cpu(), a[1][rows].cpu(), b[0][g:g + 1].cpu(), b[1][g:g + 1].cpu(),
+                                        [rows.numel()])
+        assert O.rdiff(c1[rows].float().cpu(), ref.float()) < TOL, f"group {g}"
     for g in (0, 64, 127):
         s = int(starts[g])
         rows = 64
@@ -246,3 +254,21 @@ def test_swiglu_epilogue_is_bit_identical_to_product_plus_quantiser(sizes, inter
         assert torch.equal(qm[i * stride:i * stride + n_i].view(torch.uint8), q_ref[row:row + n_i].view(torch.uint8))
         assert torch.equal(sm[i * stride:i * stride + n_i], s_ref[row:row + n_i])
         row += n_i
+
+
+@pytest.mark.parametrize("pair", [0, 1])
+def test_sizes_summing_past_m_rows_are_cut_off_and_flagged(pair):
+    """sum(sizes) > m_rows: the overrunning group is cut at m_rows, nothing past the end of c is
+    written (c is a prefix of a larger buffer of this test, so an overrun would show instead of
+    faulting), the activation scales are not indexed there, and status bit 0x10 is raised."""
+    _lib.load().b200gemm_set_cta_pair(pair)
+    sizes_bad, m_rows, n, k = [100, 300, 200], 350, 512, 384
+    a8, a_s, b8, b_s = _quantised(m_rows, 3, n, k, seed=31)
+    c_big = torch.full((m_rows + 512, n), 5.0, device=DEV, dtype=torch.bfloat16)
+    m_grouped_fp8_block_scaled((a8.to(DEV), a_s.to(DEV)), (b8.to(DEV), b_s.to(DEV)),
+                               torch.tensor(sizes_bad, device=DEV), out=c_big[:m_rows])
+    assert _lib.device_status() == 0x10
+    out = c_big.cpu()
+    assert torch.all(out[m_rows:] == 5.0)
+    ref = O.fp8_block_m_grouped_ref(a8, a_s, b8, b_s, [100, 250, 0])
+    assert O.rdiff(out[:m_rows].float(), ref.float()) < TOL

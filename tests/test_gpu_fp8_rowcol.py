@@ -156,3 +156,26 @@ def test_k_grouped_rowcol_vs_reference_kernel_output(golden_dir, name, pair):
                  inp["dtype_a"], inp["dtype_b"]).cpu()
     assert out.shape == e["out"].shape and out.dtype == e["out"].dtype
     assert O.rdiff(out.float(), e["out"].float()) < 5e-4
+
+
+def test_m_grouped_rowcol_sizes_past_m_rows_are_cut_off_and_flagged():
+    """sum(sizes) > m_rows: nothing at or past row m_rows of C is written (C is a prefix of a larger
+    buffer of this test), a_scale is not indexed there, status bit 0x10 is raised."""
+    sizes_bad, m_rows, n, k = [200, 300, 128], 400, 256, 256
+    gen = torch.Generator().manual_seed(9)
+    a8, a_s = O.per_channel_cast_to_fp8(torch.randn(m_rows, k, generator=gen).bfloat16(), E4)
+    b8 = (torch.randn(3, n, k, generator=gen) * 100).clamp(-400, 400).to(E4)
+    b_s = torch.rand(3, n, generator=gen) * 0.01 + 0.001
+    lib = _lib.load()
+    c_big = torch.full((m_rows + 256, n), 5.0, device=DEV, dtype=torch.bfloat16)
+    a_d, as_d, b_d, bs_d = a8.to(DEV), a_s.reshape(-1).to(DEV), b8.to(DEV), b_s.reshape(-1).to(DEV)
+    sz = torch.tensor(sizes_bad, dtype=torch.int32, device=DEV)
+    rc = lib.b200gemm_fp8_m_grouped_rowcol(a_d.data_ptr(), as_d.data_ptr(), b_d.data_ptr(), bs_d.data_ptr(),
+                                           c_big.data_ptr(), sz.data_ptr(), 0, 3, m_rows, n, k, 0, 0, 0, -1,
+                                           torch.cuda.current_stream().cuda_stream)
+    assert rc == 0, _lib.last_error()
+    assert _lib.device_status() == 0x10
+    out = c_big.cpu()
+    assert torch.all(out[m_rows:] == 5.0)
+    ref = O.fp8_rowcol_m_grouped_ref(a8, a_s, b8, b_s, [200, 200, 0], torch.bfloat16)
+    assert O.rdiff(out[:m_rows].float(), ref.float()) < 5e-4

@@ -163,6 +163,13 @@ def test_full_size_properties():
     c2 = k_grouped_gemm(a, b * 2, sz)
     assert torch.equal(c1 * 2, c2)
     starts = torch.cumsum(sizes, 0) - sizes
+    # every group against real arithmetic on the host: a 16 x 16 patch of its output (all of the
+    # group's tokens enter every element), at a position that moves with the group
+    for g in range(128):
+        s, e = int(starts[g]), int(starts[g] + sizes[g])
+        r0, c0 = (g * 16) % 2048, (g * 48) % 768
+        ref = (a[s:e, r0:r0 + 16].cpu().float().t() @ b[s:e, c0:c0 + 16].cpu().float()).bfloat16()
+        assert O.rdiff(c1[g, r0:r0 + 16, c0:c0 + 16].float().cpu(), ref.float()) < 2e-3, f"group {g}"
     for g in (0, 77, 127):
         s, e = int(starts[g]), int(starts[g] + sizes[g])
         ref = (a[s:e].float().t() @ b[s:e].float()).bfloat16()  # fp32 on the GPU as a cross-check only

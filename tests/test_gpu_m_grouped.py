@@ -223,6 +223,13 @@ def test_full_size_properties():
     c2 = m_grouped_gemm(a, b * 2, sz, True)
     assert torch.equal(c1 * 2, c2)  # exact: scaling by 2 commutes with every rounding
     starts = torch.cumsum(sizes, 0) - sizes
+    # every group against real arithmetic: its first, a middle and its last rows (8 each), so a
+    # group that read another expert's weights or the wrong row block cannot hide behind linearity
+    for g in range(128):
+        s0, sz_g = int(starts[g]), int(sizes[g])
+        rows = torch.cat([torch.arange(0, 8), torch.arange(sz_g // 2, sz_g // 2 + 8), torch.arange(sz_g - 8, sz_g)]) + s0
+        ref = (a[rows.to(DEV)].cpu().float() @ b[g].cpu().float().t()).bfloat16()
+        assert O.rdiff(c1[rows.to(DEV)].cpu().float(), ref.float()) < 2e-4, f"group {g}"
     for g in (0, 63, 127):
         s, n_rows = int(starts[g]), min(int(sizes[g]), 256)
         ref = (a[s:s + n_rows].cpu().float() @ b[g].cpu().float().t()).bfloat16()
@@ -295,3 +302,27 @@ def test_launch_is_cuda_graph_capturable():
     torch.cuda.synchronize()
     ref = O.m_grouped_ref(a.cpu(), b.cpu(), sizes.cpu(), True)
     assert O.rdiff(c.cpu().float(), ref.float()) < 2e-4
+
+
+@pytest.mark.parametrize("pair", [0, 1], ids=["single", "pair"])
+@pytest.mark.parametrize("trans_b", [True, False])
+def test_sizes_summing_past_m_rows_are_cut_off_and_flagged(pair, trans_b):
+    """A routing vector whose sum exceeds the rows A and C really have (sizes live on the device, the
+    host cannot check them): the group that runs over is cut at m_rows, later groups get nothing,
+    memory past the end of C stays untouched and the status word says so.  C sits inside a larger
+    allocation of this test, so an overrun would be seen, not faulted on."""
+    sizes_bad = [100, 200, 300, 64]
+    m_rows, n, k = 450, 512, 192
+    gen = torch.Generator().manual_seed(3)
+    a = (torch.randn(m_rows, k, generator=gen) * 0.5).bfloat16()
+    b_nk = (torch.randn(4, n, k, generator=gen) * 0.5).bfloat16()
+    b = b_nk if trans_b else b_nk.transpose(1, 2).contiguous()
+    c_big = torch.full((m_rows + 512, n), 7.0, device=DEV, dtype=torch.bfloat16)
+    _lib.load().b200gemm_set_cta_pair(pair)
+    _m_grouped_gemm_launch(a.to(DEV), b.to(DEV), c_big[:m_rows], torch.tensor(sizes_bad, device=DEV), trans_b)
+    status = _lib.device_status()
+    assert status == 0x10, f"status {status:#x}"
+    out = c_big.cpu()
+    assert torch.all(out[m_rows:] == 7.0), "rows past m_rows were written"
+    ref = O.m_grouped_ref(a, b, torch.tensor([100, 200, 150, 0]), trans_b)
+    assert O.rdiff(out[:m_rows].float(), ref.float()) < 2e-4

@@ -128,7 +128,7 @@ def test_multi_buffer_row_movers_on_one_gpu():
     bases = (ctypes.c_void_p * world)(*[b.data_ptr() for b in bufs])
     rank_d, row_d = dst_rank.to(DEV), dst_row.to(DEV)   # named: the kernels read them after the call returns
     rc = lib.b200moe_scatter_rows_multi(x.data_ptr(), src_idx.data_ptr(), bases, rank_d.data_ptr(),
-                                        row_d.data_ptr(), n, h, world, cap, stream)
+                                        row_d.data_ptr(), n, h, world, cap, t, 0, stream)
     _lib.check(rc, "scatter")
     torch.cuda.synchronize()
     for r in range(world):
@@ -155,7 +155,120 @@ def test_multi_buffer_row_movers_on_one_gpu():
     bad_row_d = bad_row.to(DEV)
     before = bufs[int(dst_rank[5])].clone()
     rc = lib.b200moe_scatter_rows_multi(x.data_ptr(), src_idx.data_ptr(), bases, rank_d.data_ptr(),
-                                        bad_row_d.data_ptr(), n, h, world, cap, stream)
+                                        bad_row_d.data_ptr(), n, h, world, cap, t, 0, stream)
     _lib.check(rc, "scatter")
     assert _lib.device_status() == 1 << 5
     assert torch.equal(bufs[int(dst_rank[5])], before)   # same data everywhere else, nothing new written
+    # a source row outside src is skipped and flagged too (16 large blocks: the form used beside a GEMM)
+    bad_src = src_idx.clone()
+    bad_src[9] = t + 3
+    bad_src[11] = -1
+    for b in bufs:
+        b.zero_()
+    rc = lib.b200moe_scatter_rows_multi(x.data_ptr(), bad_src.data_ptr(), bases, rank_d.data_ptr(),
+                                        row_d.data_ptr(), n, h, world, cap, t, 16, stream)
+    _lib.check(rc, "scatter")
+    assert _lib.device_status() == 1 << 5
+    for r in range(world):
+        ref = torch.zeros(cap, h, dtype=torch.uint8)
+        sel = (dst_rank == r) & (torch.arange(n) != 9) & (torch.arange(n) != 11)
+        ref[dst_row[sel]] = x.cpu()[src_idx.cpu()[sel]]
+        assert torch.equal(bufs[r].cpu(), ref)
+
+
+def test_quantise_on_dispatch_and_return_movers_on_one_gpu():
+    """b200moe_dispatch_quant_rows_multi with three ordinary buffers per payload standing in for the
+    ranks': the rows, scales and return addresses it stores are bit for bit what the activation
+    quantiser followed by one scatter per payload stores.  b200moe_return_rows_multi then sends
+    rows back through those addresses.  Both in their GPU-filling and their few-large-blocks form."""
+    import ctypes
+
+    lib = _lib.load()
+    stream = torch.cuda.current_stream().cuda_stream
+    gen = torch.Generator().manual_seed(33)
+    t, k, h, world, cap, me = 193, 4, 1024, 3, 400, 1
+    x = torch.randn(t, h, generator=gen).bfloat16()
+    x[7, 128:256] = 0                      # a block at the 1e-4 clamp
+    x[9, :] *= 300.0
+    n = t * k
+    tok = torch.randint(0, t, (n,), generator=gen)
+    dst_rank = torch.randint(0, world, (n,), generator=gen, dtype=torch.int32)
+    dst_row = torch.empty(n, dtype=torch.int64)
+    for r in range(world):
+        sel = (dst_rank == r).nonzero().flatten()
+        dst_row[sel] = torch.randperm(cap, generator=gen)[: sel.numel()]
+    q_ref, s_ref = O.per_token_cast_to_fp8(x)
+    x_d, tok_d, rank_d, row_d = x.to(DEV), tok.to(DEV), dst_rank.to(DEV), dst_row.to(DEV)
+    first, count = 5, n - 9                # a sub-range of the send order, as a chunk is
+    for blocks in (0, 8):
+        b8 = [torch.zeros(cap, h, dtype=torch.uint8, device=DEV) for _ in range(world)]
+        bs = [torch.zeros(cap, h // 128, dtype=torch.float32, device=DEV) for _ in range(world)]
+        bm = [torch.full((cap, 2), -7, dtype=torch.int64, device=DEV) for _ in range(world)]
+        mk = lambda bufs: (ctypes.c_void_p * world)(*[b.data_ptr() for b in bufs])  # noqa: E731
+        rc = lib.b200moe_dispatch_quant_rows_multi(x_d.data_ptr(), tok_d.data_ptr(), mk(b8), mk(bs), mk(bm),
+                                                   rank_d.data_ptr(), row_d.data_ptr(), first, count, t, h, 0, world, cap,
+                                                   me, blocks, stream)
+        _lib.check(rc, "dispatch_quant")
+        torch.cuda.synchronize()
+        for r in range(world):
+            e8 = torch.zeros(cap, h, dtype=torch.uint8)
+            es = torch.zeros(cap, h // 128)
+            em = torch.full((cap, 2), -7, dtype=torch.int64)
+            for i in range(first, first + count):
+                if int(dst_rank[i]) == r:
+                    e8[dst_row[i]] = q_ref.view(torch.uint8)[tok[i]]
+                    es[dst_row[i]] = s_ref[tok[i]]
+                    em[dst_row[i]] = torch.tensor([i, me])
+            assert torch.equal(b8[r].cpu(), e8)
+            assert torch.equal(bs[r].cpu().view(torch.int32), es.view(torch.int32))
+            assert torch.equal(bm[r].cpu(), em)
+        assert _lib.device_status() == 0
+    # the way back: rows [0, m) of a result buffer go to (meta[r, 1], meta[r, 0])
+    m = 300
+    y = torch.randn(m, h, generator=gen).bfloat16().to(DEV)
+    back_rank = torch.randint(0, world, (m,), generator=gen)
+    back_row = torch.empty(m, dtype=torch.int64)
+    for r in range(world):
+        sel = (back_rank == r).nonzero().flatten()
+        back_row[sel] = torch.randperm(cap, generator=gen)[: sel.numel()]
+    meta = torch.stack([back_row, back_rank], dim=1).contiguous().to(DEV)
+    for blocks in (0, 8):
+        rets = [torch.zeros(cap, h, dtype=torch.bfloat16, device=DEV) for _ in range(world)]
+        rbases = (ctypes.c_void_p * world)(*[b.data_ptr() for b in rets])
+        rc = lib.b200moe_return_rows_multi(y.data_ptr(), meta.data_ptr(), rbases, m, h * 2, world, cap, blocks, stream)
+        _lib.check(rc, "return_rows")
+        torch.cuda.synchronize()
+        for r in range(world):
+            ref = torch.zeros(cap, h, dtype=torch.bfloat16)
+            sel = back_rank == r
+            ref[back_row[sel]] = y.cpu()[sel]
+            assert torch.equal(rets[r].cpu(), ref)
+    # a return address outside the buffers is skipped and flagged
+    meta_bad = meta.clone()
+    meta_bad[3, 1] = world
+    meta_bad[4, 0] = cap
+    rc = lib.b200moe_return_rows_multi(y.data_ptr(), meta_bad.data_ptr(), rbases, m, h * 2, world, cap, 0, stream)
+    _lib.check(rc, "return_rows")
+    assert _lib.device_status() == 1 << 5
+
+
+def test_dropped_routing_pair_is_skipped_not_followed():
+    """One (token, k) pair with expert id -1 (a dropped token): the routing plan gives it no slot,
+    the movers skip it (status bit 5), and the layer's output for that token is the weighted sum of
+    its other experts."""
+    e, h, inter, k, t = 4, 256, 128, 2, 96
+    gen = torch.Generator().manual_seed(8)
+    w13 = (torch.randn(e, 2 * inter, h, generator=gen) * 0.05).bfloat16()
+    w2 = (torch.randn(e, h, inter, generator=gen) * 0.05).bfloat16()
+    x = torch.randn(t, h, generator=gen).bfloat16()
+    idx, w = synthetic_routing(t, e, k, seed=3)
+    idx[17, 1] = -1
+    layer = Fp8MoELayer(w13.to(DEV), w2.to(DEV), e, None)
+    out = layer.forward(x.to(DEV), idx.to(DEV), w.to(DEV)).cpu()
+    assert _lib.device_status() == 1 << 5
+    idx_ok, w_ok = idx.clone(), w.clone()
+    idx_ok[17, 1] = idx[17, 0]
+    w_ok[17, 1] = 0.0
+    ref = layer.forward(x.to(DEV), idx_ok.to(DEV), w_ok.to(DEV)).cpu()
+    assert _lib.device_status() == 0
+    assert torch.equal(out, ref)

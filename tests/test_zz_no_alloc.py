@@ -11,6 +11,7 @@ through every other test; it also passes when run on its own in a fresh process.
 import pytest
 import torch
 
+import oracle as O
 from triton_grouped_gemm_b200 import _lib
 
 pytestmark = pytest.mark.gpu
@@ -64,6 +65,10 @@ def test_static_scratch_matches_workspace_entry_on_two_calls_in_a_row():
     # fact the results are identical
     assert _rdiff(out1, ref1) < 2e-4 and _rdiff(out2, ref2) < 2e-4
     assert torch.equal(out1, ref1) and torch.equal(out2, ref2)
+    # and against the CPU oracle directly, so this file does not lean on the other K-grouped tests
+    for (a, b, sizes), out in ((p1, out1), (p2, out2)):
+        ref = O.k_grouped_ref(a.cpu(), b.cpu(), sizes.cpu())
+        assert _rdiff(out.cpu(), ref) < 2e-4
     # and once more with the first problem, now after the second one used the array
     _static_scratch(*p1, out1)
     torch.cuda.synchronize()

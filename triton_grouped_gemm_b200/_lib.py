@@ -54,8 +54,10 @@ _SIGNATURES = {
                                             c_int, c_int, c_int, c_int, c_void_p],
     "b200moe_route_plan": [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     "b200moe_scatter_rows_multi": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int64,
-                                   c_void_p],
-    "b200moe_set_background_blocks": [c_int],
+                                   c_int64, c_int, c_void_p],
+    "b200moe_dispatch_quant_rows_multi": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
+                                          c_int64, c_int64, c_int, c_int, c_int, c_int64, c_int, c_int, c_void_p],
+    "b200moe_return_rows_multi": [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int64, c_int, c_void_p],
     "b200moe_combine_topk_multi": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int,
                                    c_int64, c_void_p],
     "b200ipc_alloc": [c_int64, c_void_p],
@@ -66,8 +68,8 @@ _SIGNATURES = {
     "b200layout_group_starts": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "b200layout_psum": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
     "b200layout_grouped_rows": [c_void_p, c_int, c_int, c_int, c_void_p, c_int64, c_void_p],
-    "b200moe_gather_rows": [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p],
-    "b200moe_combine_topk": [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p],
+    "b200moe_gather_rows": [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p],
+    "b200moe_combine_topk": [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int64, c_void_p],
     "b200quant_act_1x128": [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_void_p],
     "b200quant_swiglu_act_1x128": [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p],
     "b200quant_w_128x128": [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p],

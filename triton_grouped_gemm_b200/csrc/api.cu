@@ -119,6 +119,9 @@ int b200gemm_device_status(unsigned* out_status, int clear) {
   if (!out_status) return b200::set_error(b200::kErrInvalidArgument, "out_status is null");
   unsigned* p = b200::device_status_ptr();
   if (!p) return b200::set_error(b200::kErrCuda, "no CUDA device / status word unavailable");
+  // kernels on non-blocking streams (torch's side streams are) do not order with the legacy
+  // stream's copy below, so wait for the whole device first
+  B200_CUDA(cudaDeviceSynchronize());
   B200_CUDA(cudaMemcpy(out_status, p, sizeof(unsigned), cudaMemcpyDeviceToHost));
   if (clear && *out_status) B200_CUDA(cudaMemset(p, 0, sizeof(unsigned)));
   return 0;

@@ -125,7 +125,7 @@ __device__ __forceinline__ bool wait_bounded_cluster(uint32_t bar, uint32_t pari
 // stride == 0 : compact rows (group g starts at the sum of the earlier sizes)
 // stride  > 0 : masked layout (group g starts at g * stride, only sizes[g] rows are valid)
 // stride == -1: padded rows (group g starts at the sum of the earlier sizes, each rounded up
-//               to a multiple of tile_rows; rows between size and the padded size are skipped)
+//               to a multiple of 128; rows between size and the padded size are skipped)
 struct GroupWalker {
   const void* sizes;
   int sizes_i64;
@@ -135,41 +135,60 @@ struct GroupWalker {
   int g;             // current group
   int tile_begin;    // first padded tile of group g
   int ntiles;        // tiles of group g
-  int size;          // rows of group g
+  int size;          // rows of group g (after clamping, see enter())
+  bool overflow;     // some group's rows ran past row_limit and were cut off
   long long row_begin;  // first row of group g (contiguous kind)
+  long long row_limit;  // rows the A / C tensors really have: no row >= row_limit is ever touched
 
-  __device__ __forceinline__ int load_size(int i) const {
+  // Loads the size of group i, whose first row is already in row_begin.  Negative sizes count as
+  // zero, masked sizes are clamped to the slot, and in the contiguous layouts a group is cut off
+  // at row_limit: a size vector whose sum exceeds the tensors' row count (a bad routing vector)
+  // must neither write past the end of C nor read scales past their end, and it must not
+  // stretch the persistent loop either.  The cut is remembered in `overflow`.
+  __device__ __forceinline__ void enter(int i) {
     long long v = sizes_i64 ? static_cast<const long long*>(sizes)[i]
                             : static_cast<long long>(static_cast<const int*>(sizes)[i]);
     if (v < 0) v = 0;
-    if (stride > 0 && v > stride) v = stride;
-    return static_cast<int>(v);
+    if (stride > 0) {
+      if (v > stride) v = stride;
+    } else {
+      long long room = row_limit - row_begin;
+      if (room < 0) room = 0;
+      if (v > room) {
+        v = room;
+        overflow = true;
+      }
+    }
+    size = static_cast<int>(v);
+    ntiles = (size + tile_rows - 1) / tile_rows;
   }
 
+  // row_limit_: number of rows of the row-grouped tensors (m_rows; G * stride in the masked layout)
   __device__ __forceinline__ void init(const void* sizes_, int sizes_i64_, int num_groups_, int stride_,
-                                       int tile_rows_) {
+                                       int tile_rows_, long long row_limit_) {
     sizes = sizes_;
     sizes_i64 = sizes_i64_;
     num_groups = num_groups_;
     stride = stride_;
     tile_rows = tile_rows_;
+    row_limit = row_limit_;
+    overflow = false;
     g = 0;
     tile_begin = 0;
     row_begin = 0;
-    size = num_groups > 0 ? load_size(0) : 0;
-    ntiles = (size + tile_rows - 1) / tile_rows;
+    size = 0;
+    ntiles = 0;
+    if (num_groups > 0) enter(0);
   }
 
   // Move to padded row tile `t` (t must not decrease between calls).  false = past the end.
   __device__ __forceinline__ bool seek(int t) {
     while (g < num_groups && t >= tile_begin + ntiles) {
       tile_begin += ntiles;
-      row_begin += stride < 0 ? static_cast<long long>(ntiles) * tile_rows : static_cast<long long>(size);
+      // padded layout: every group occupies its size rounded up to 128 rows, whatever the tile height
+      row_begin += stride < 0 ? (static_cast<long long>(size) + 127) / 128 * 128 : static_cast<long long>(size);
       ++g;
-      if (g < num_groups) {
-        size = load_size(g);
-        ntiles = (size + tile_rows - 1) / tile_rows;
-      }
+      if (g < num_groups) enter(g);
     }
     return g < num_groups;
   }

@@ -42,8 +42,8 @@ template <int kBlockN, int kStages, bool kBMnMajor, bool kFp8>
 __global__ void __launch_bounds__(kNumThreads, 1)
 m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                  const __grid_constant__ CUtensorMap tm_c, void* __restrict__ c_ptr, const void* __restrict__ sizes, int sizes_i64, int num_groups,
-                 int masked_stride, int n, int k, int in_fmt, int out_fp16, const float* __restrict__ a_scale,
-                 const float* __restrict__ b_scale, unsigned* status) {
+                 int masked_stride, long long m_rows, int n, int k, int in_fmt, int out_fp16,
+                 const float* __restrict__ a_scale, const float* __restrict__ b_scale, unsigned* status) {
   static_assert(!(kFp8 && kBMnMajor), "fp8 operands are K-major only");
   constexpr int kElemsPerKb = kFp8 ? 128 : 64;
   using L = MGroupedSmem<kBlockN, kStages>;
@@ -93,7 +93,7 @@ m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     GroupWalker w;
-    w.init(sizes, sizes_i64, num_groups, masked_stride, kBlockM);
+    w.init(sizes, sizes_i64, num_groups, masked_stride, kBlockM, m_rows);
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
@@ -131,7 +131,7 @@ m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     GroupWalker w;
-    w.init(sizes, sizes_i64, num_groups, masked_stride, kBlockM);
+    w.init(sizes, sizes_i64, num_groups, masked_stride, kBlockM, m_rows);
     const uint32_t a_fmt = kFp8 ? static_cast<uint32_t>(in_fmt & 0xF) : static_cast<uint32_t>(in_fmt);
     const uint32_t b_fmt = kFp8 ? static_cast<uint32_t>((in_fmt >> 4) & 0xF) : static_cast<uint32_t>(in_fmt);
     const uint32_t idesc = make_instr_desc(a_fmt, b_fmt, 0u, kBMnMajor ? 1u : 0u, kBlockM, kBlockN);
@@ -178,7 +178,7 @@ m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   } else {
     // ------------------------------------------------------------ epilogue (warps 2..5)
     GroupWalker w;
-    w.init(sizes, sizes_i64, num_groups, masked_stride, kBlockM);
+    w.init(sizes, sizes_i64, num_groups, masked_stride, kBlockM, m_rows);
     const int quarter = warp & 3;  // TMEM lane quarter this warp may read
     uint8_t* epi_stage = smem + L::kEpiOffset + quarter * kEpiStageBytesPerWarp;
     int epi_sel = 0;
@@ -215,6 +215,8 @@ m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       if (lane == 0) mbar_arrive(tmem_empty_bar(acc));
     }
     if (lane == 0) tma_store_wait_all<0>();  // staged stores have left shared memory and landed
+    // the sizes added up to more rows than A / C have: the excess was cut off, tell the host
+    if (w.overflow && quarter == 0 && lane == 0 && status) atomicOr(status, kDevBadGroupSize);
   }
 
   // ---------------------------------------------------------------- teardown
@@ -236,15 +238,15 @@ m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 template <int kBlockN, int kStages, bool kBMnMajor, bool kFp8>
 static int launch_m_grouped(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const CUtensorMap& tm_c, void* c,
                             const void* sizes,
-                            int sizes_is_i64, int num_groups, int masked_stride, int n, int k, int in_fmt,
-                            int out_fp16, const float* a_scale, const float* b_scale, int grid,
+                            int sizes_is_i64, int num_groups, int masked_stride, long long m_rows, int n, int k,
+                            int in_fmt, int out_fp16, const float* a_scale, const float* b_scale, int grid,
                             cudaStream_t stream) {
   using L = MGroupedSmem<kBlockN, kStages>;
   auto kern = m_grouped_kernel<kBlockN, kStages, kBMnMajor, kFp8>;
   B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes));
   unsigned* status = device_status_ptr();
   kern<<<grid, kNumThreads, L::kDynamicBytes, stream>>>(tm_a, tm_b, tm_c, c, sizes, sizes_is_i64, num_groups, masked_stride,
-                                                        n, k, in_fmt, out_fp16, a_scale, b_scale, status);
+                                                        m_rows, n, k, in_fmt, out_fp16, a_scale, b_scale, status);
   B200_CUDA(cudaGetLastError());
   return 0;
 }
@@ -325,16 +327,16 @@ static int m_grouped_common(const void* a, const void* b, void* c, const void* s
   if (pair) {
     const int want = (num_sms > 0 && num_sms < sms) ? num_sms : 0;
     return trans_b ? launch_m_grouped_pair<false, false>(tm_a, tm_b, tm_c, c, sizes, sizes_is_i64, num_groups,
-                                                         masked_stride, n, k, in_fmt, dtype, nullptr, nullptr, want,
+                                                         masked_stride, m_rows, n, k, in_fmt, dtype, nullptr, nullptr, want,
                                                          stream)
                    : launch_m_grouped_pair<true, false>(tm_a, tm_b, tm_c, c, sizes, sizes_is_i64, num_groups,
-                                                        masked_stride, n, k, in_fmt, dtype, nullptr, nullptr, want,
+                                                        masked_stride, m_rows, n, k, in_fmt, dtype, nullptr, nullptr, want,
                                                         stream);
   }
 #define B200_LAUNCH(BN, ST)                                                                                          \
-  (trans_b ? launch_m_grouped<BN, ST, false, false>(tm_a, tm_b, tm_c, c, sizes, sizes_is_i64, num_groups, masked_stride, n, \
+  (trans_b ? launch_m_grouped<BN, ST, false, false>(tm_a, tm_b, tm_c, c, sizes, sizes_is_i64, num_groups, masked_stride, m_rows, n, \
                                                     k, in_fmt, dtype, nullptr, nullptr, grid, stream)                \
-           : launch_m_grouped<BN, ST, true, false>(tm_a, tm_b, tm_c, c, sizes, sizes_is_i64, num_groups, masked_stride, n,  \
+           : launch_m_grouped<BN, ST, true, false>(tm_a, tm_b, tm_c, c, sizes, sizes_is_i64, num_groups, masked_stride, m_rows, n,  \
                                                    k, in_fmt, dtype, nullptr, nullptr, grid, stream))
   if (block_n == 256) return B200_LAUNCH(256, 4);
   if (block_n == 128) return B200_LAUNCH(128, 6);
@@ -397,11 +399,11 @@ static int fp8_rowcol_m_grouped(const void* a, const float* a_scale, const void*
   }
   const int in_fmt = fmt_a | (fmt_b << 4);
   if (pair)
-    return launch_m_grouped_pair<false, true>(tm_a, tm_b, tm_c, c, sizes, sizes_is_i64, num_groups, 0, n, k, in_fmt,
+    return launch_m_grouped_pair<false, true>(tm_a, tm_b, tm_c, c, sizes, sizes_is_i64, num_groups, 0, m_rows, n, k, in_fmt,
                                               out_dtype, a_scale, b_scale,
                                               (num_sms > 0 && num_sms < sms) ? num_sms : 0, stream);
 #define B200_LAUNCH8(BN, ST)                                                                                        \
-  launch_m_grouped<BN, ST, false, true>(tm_a, tm_b, tm_c, c, sizes, sizes_is_i64, num_groups, 0, n, k, in_fmt, out_dtype, \
+  launch_m_grouped<BN, ST, false, true>(tm_a, tm_b, tm_c, c, sizes, sizes_is_i64, num_groups, 0, m_rows, n, k, in_fmt, out_dtype, \
                                         a_scale, b_scale, grid, stream)
   if (block_n == 256) return B200_LAUNCH8(256, 4);
   if (block_n == 128) return B200_LAUNCH8(128, 6);

@@ -70,8 +70,9 @@ fp8_block_m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
                            const __grid_constant__ CUtensorMap tm_c, const __grid_constant__ CUtensorMap tm_as,
                            int scales_by_tma, __nv_bfloat16* __restrict__ c_ptr, const float* __restrict__ a_scale,
                            const float* __restrict__ b_scale, const void* __restrict__ sizes, int sizes_i64,
-                           int num_groups, int masked_stride, int n, int k, const int* __restrict__ b_map,
-                           int num_b, float* __restrict__ act_scale_out, unsigned* status) {
+                           int num_groups, int masked_stride, long long m_rows, int n, int k,
+                           const int* __restrict__ b_map, int num_b, float* __restrict__ act_scale_out,
+                           unsigned* status) {
   static_assert(!kSwiglu || kBlockN == 256, "the SwiGLU epilogue pairs the two 128-column halves of a 256-column tile");
   using L = Fp8BlockCfg<kBlockN, kPair>;
   // weight matrix of row group g: b[b_map[g]] (clamped into range), or b[g] without a map
@@ -147,7 +148,7 @@ fp8_block_m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     GroupWalker w;
-    w.init(sizes, sizes_i64, num_groups, masked_stride, kTileM);
+    w.init(sizes, sizes_i64, num_groups, masked_stride, kTileM, m_rows);
     int stage = 0;
     uint32_t phase = 0;
     uint32_t scale_it = 0;  // scale tiles requested so far: buffer = scale_it & 1
@@ -203,7 +204,7 @@ fp8_block_m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer (pair: leader only)
     GroupWalker w;
-    w.init(sizes, sizes_i64, num_groups, masked_stride, kTileM);
+    w.init(sizes, sizes_i64, num_groups, masked_stride, kTileM, m_rows);
     const uint32_t idesc = make_instr_desc(0u, 0u, 0u, 0u, kTileM, kBlockN);  // e4m3 x e4m3 -> f32
     int stage = 0;
     uint32_t phase = 0;
@@ -251,7 +252,7 @@ fp8_block_m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
     // ------------------------------------------------------------ promotion + epilogue
     if constexpr (L::kRebalance) warpgroup_reg_inc<224>();
     GroupWalker w;
-    w.init(sizes, sizes_i64, num_groups, masked_stride, kTileM);
+    w.init(sizes, sizes_i64, num_groups, masked_stride, kTileM, m_rows);
     const int quarter = warp & 3;
     const int half = (warp - 4) >> 2;
     uint32_t it = 0;
@@ -499,6 +500,8 @@ fp8_block_m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
       }
     }
     if (lane == 0) tma_store_wait_all<0>();
+    // the sizes added up to more rows than a / c have: the excess was cut off, tell the host
+    if (ok && w.overflow && rank == 0 && warp == 4 && lane == 0 && status) atomicOr(status, kDevBadGroupSize);
   }
 
   tc_fence_before_sync();
@@ -517,8 +520,8 @@ fp8_block_m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
 template <int kBlockN, bool kPair, bool kSwiglu = false>
 static int launch_fp8_block(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const CUtensorMap& tm_c,
                             const CUtensorMap& tm_as, int scales_by_tma, void* c, const float* a_scale, const float* b_scale, const void* sizes, int sizes_is_i64,
-                            int num_groups, int masked_stride, int n, int k, const int* b_map, int num_b, int grid,
-                            cudaStream_t stream, float* act_scale_out = nullptr) {
+                            int num_groups, int masked_stride, long long m_rows, int n, int k, const int* b_map, int num_b,
+                            int grid, cudaStream_t stream, float* act_scale_out = nullptr) {
   using L = Fp8BlockCfg<kBlockN, kPair>;
   auto kern = fp8_block_m_grouped_kernel<kBlockN, kPair, kSwiglu>;
   B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes));
@@ -562,13 +565,13 @@ static int launch_fp8_block(const CUtensorMap& tm_a, const CUtensorMap& tm_b, co
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     B200_CUDA(cudaLaunchKernelEx(&cfg, kern, tm_a, tm_b, tm_c, tm_as, scales_by_tma, static_cast<__nv_bfloat16*>(c), a_scale, b_scale, sizes,
-                                 sizes_is_i64, num_groups, masked_stride, n, k, b_map, num_b, act_scale_out,
+                                 sizes_is_i64, num_groups, masked_stride, m_rows, n, k, b_map, num_b, act_scale_out,
                                  device_status_ptr()));
   } else {
     kern<<<grid, L::kThreads, L::kDynamicBytes, stream>>>(tm_a, tm_b, tm_c, tm_as, scales_by_tma,
                                                           static_cast<__nv_bfloat16*>(c), a_scale,
-                                                          b_scale, sizes, sizes_is_i64, num_groups, masked_stride, n,
-                                                          k, b_map, num_b, act_scale_out, device_status_ptr());
+                                                          b_scale, sizes, sizes_is_i64, num_groups, masked_stride, m_rows,
+                                                          n, k, b_map, num_b, act_scale_out, device_status_ptr());
   }
   B200_CUDA(cudaGetLastError());
   return 0;
@@ -656,20 +659,20 @@ static int fp8_block_common(const void* a, const float* a_scale, const void* b, 
   if (swiglu) {
     if (pair)
       return launch_fp8_block<256, true, true>(tm_a, tm_b, tm_c, tm_as, scales_by_tma, c, a_scale, b_scale, sizes,
-                                               sizes_is_i64, num_groups, masked_stride, n, k, b_map, num_b, grid, stream,
-                                               act_scale_out);
+                                               sizes_is_i64, num_groups, masked_stride, m_rows, n, k, b_map, num_b, grid,
+                                               stream, act_scale_out);
     return launch_fp8_block<256, false, true>(tm_a, tm_b, tm_c, tm_as, scales_by_tma, c, a_scale, b_scale, sizes,
-                                              sizes_is_i64, num_groups, masked_stride, n, k, b_map, num_b, grid, stream,
-                                              act_scale_out);
+                                              sizes_is_i64, num_groups, masked_stride, m_rows, n, k, b_map, num_b, grid,
+                                              stream, act_scale_out);
   }
   if (pair)
     return launch_fp8_block<256, true>(tm_a, tm_b, tm_c, tm_as, scales_by_tma, c, a_scale, b_scale, sizes, sizes_is_i64, num_groups,
-                                       masked_stride, n, k, b_map, num_b, grid, stream);
+                                       masked_stride, m_rows, n, k, b_map, num_b, grid, stream);
   if (block_n == 256)
     return launch_fp8_block<256, false>(tm_a, tm_b, tm_c, tm_as, scales_by_tma, c, a_scale, b_scale, sizes, sizes_is_i64, num_groups,
-                                        masked_stride, n, k, b_map, num_b, grid, stream);
+                                        masked_stride, m_rows, n, k, b_map, num_b, grid, stream);
   return launch_fp8_block<128, false>(tm_a, tm_b, tm_c, tm_as, scales_by_tma, c, a_scale, b_scale, sizes, sizes_is_i64, num_groups,
-                                      masked_stride, n, k, b_map, num_b, grid, stream);
+                                      masked_stride, m_rows, n, k, b_map, num_b, grid, stream);
 }
 
 }  // namespace b200

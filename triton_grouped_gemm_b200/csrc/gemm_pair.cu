@@ -40,9 +40,9 @@ template <bool kBMnMajor, bool kFp8>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
 m_grouped_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                       const __grid_constant__ CUtensorMap tm_c, void* __restrict__ c_ptr,
-                      const void* __restrict__ sizes, int sizes_i64, int num_groups, int masked_stride, int n, int k,
-                      int in_fmt, int out_fp16, const float* __restrict__ a_scale, const float* __restrict__ b_scale,
-                      unsigned* status) {
+                      const void* __restrict__ sizes, int sizes_i64, int num_groups, int masked_stride,
+                      long long m_rows, int n, int k, int in_fmt, int out_fp16, const float* __restrict__ a_scale,
+                      const float* __restrict__ b_scale, unsigned* status) {
   static_assert(!(kFp8 && kBMnMajor), "fp8 operands are K-major only");
   using L = PairSmem;
   constexpr int kStages = kPairStages;
@@ -96,7 +96,7 @@ m_grouped_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer (both CTAs)
     GroupWalker w;
-    w.init(sizes, sizes_i64, num_groups, masked_stride, kPairTileM);
+    w.init(sizes, sizes_i64, num_groups, masked_stride, kPairTileM, m_rows);
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
@@ -141,7 +141,7 @@ m_grouped_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
     // ------------------------------------------------------------ MMA issuer (leader CTA only)
     if (rank == 0) {
       GroupWalker w;
-      w.init(sizes, sizes_i64, num_groups, masked_stride, kPairTileM);
+      w.init(sizes, sizes_i64, num_groups, masked_stride, kPairTileM, m_rows);
       const uint32_t a_fmt = kFp8 ? static_cast<uint32_t>(in_fmt & 0xF) : static_cast<uint32_t>(in_fmt);
       const uint32_t b_fmt = kFp8 ? static_cast<uint32_t>((in_fmt >> 4) & 0xF) : static_cast<uint32_t>(in_fmt);
       const uint32_t idesc = make_instr_desc(a_fmt, b_fmt, 0u, kBMnMajor ? 1u : 0u, kPairTileM, kPairTileN);
@@ -189,7 +189,7 @@ m_grouped_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
   } else {
     // ------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
     GroupWalker w;
-    w.init(sizes, sizes_i64, num_groups, masked_stride, kPairTileM);
+    w.init(sizes, sizes_i64, num_groups, masked_stride, kPairTileM, m_rows);
     const int quarter = warp & 3;
     uint8_t* epi_stage = smem + L::kEpiOffset + quarter * kEpiStageBytesPerWarp;
     int epi_sel = 0;
@@ -223,6 +223,7 @@ m_grouped_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
       if (lane == 0) mbar_arrive_cluster(tmem_empty_bar(acc), 0);
     }
     if (lane == 0) tma_store_wait_all<0>();
+    if (w.overflow && rank == 0 && quarter == 0 && lane == 0 && status) atomicOr(status, kDevBadGroupSize);
   }
 
   // ---------------------------------------------------------------- teardown
@@ -264,9 +265,9 @@ static int pair_grid_size(Kern kern, int smem_bytes, int want_ctas) {
 
 template <bool kBMnMajor, bool kFp8>
 int launch_m_grouped_pair(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const CUtensorMap& tm_c, void* c,
-                          const void* sizes, int sizes_is_i64, int num_groups, int masked_stride, int n, int k,
-                          int in_fmt, int out_fp16, const float* a_scale, const float* b_scale, int want_ctas,
-                          cudaStream_t stream) {
+                          const void* sizes, int sizes_is_i64, int num_groups, int masked_stride, long long m_rows,
+                          int n, int k, int in_fmt, int out_fp16, const float* a_scale, const float* b_scale,
+                          int want_ctas, cudaStream_t stream) {
   auto kern = m_grouped_pair_kernel<kBMnMajor, kFp8>;
   B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PairSmem::kDynamicBytes));
   static int cached_grid[64] = {0};
@@ -278,8 +279,8 @@ int launch_m_grouped_pair(const CUtensorMap& tm_a, const CUtensorMap& tm_b, cons
   if (want_ctas > 0 && (want_ctas & ~1) < grid) grid = want_ctas & ~1;
   if (grid < 2) return set_error(kErrUnsupported, "the CTA-pair kernel needs at least 2 SMs");
   kern<<<grid, kNumThreads, PairSmem::kDynamicBytes, stream>>>(tm_a, tm_b, tm_c, c, sizes, sizes_is_i64, num_groups,
-                                                               masked_stride, n, k, in_fmt, out_fp16, a_scale, b_scale,
-                                                               device_status_ptr());
+                                                               masked_stride, m_rows, n, k, in_fmt, out_fp16, a_scale,
+                                                               b_scale, device_status_ptr());
   B200_CUDA(cudaGetLastError());
   return 0;
 }
@@ -293,13 +294,13 @@ int pair_kernel_grid() {
 }
 
 template int launch_m_grouped_pair<false, false>(const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, void*,
-                                                 const void*, int, int, int, int, int, int, int, const float*,
+                                                 const void*, int, int, int, long long, int, int, int, int, const float*,
                                                  const float*, int, cudaStream_t);
 template int launch_m_grouped_pair<true, false>(const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, void*,
-                                                const void*, int, int, int, int, int, int, int, const float*,
+                                                const void*, int, int, int, long long, int, int, int, int, const float*,
                                                 const float*, int, cudaStream_t);
 template int launch_m_grouped_pair<false, true>(const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, void*,
-                                                const void*, int, int, int, int, int, int, int, const float*,
+                                                const void*, int, int, int, long long, int, int, int, int, const float*,
                                                 const float*, int, cudaStream_t);
 
 }  // namespace b200

@@ -134,9 +134,9 @@ __device__ __forceinline__ void store_zero_row_16bit(uint16_t* c_row, bool row_o
 // 64 x 64 (MN-major) boxes; tm_a 128-row boxes; tm_c 32 x 64 boxes.
 template <bool kBMnMajor, bool kFp8>
 int launch_m_grouped_pair(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const CUtensorMap& tm_c, void* c,
-                          const void* sizes, int sizes_is_i64, int num_groups, int masked_stride, int n, int k,
-                          int in_fmt, int out_fp16, const float* a_scale, const float* b_scale, int want_ctas,
-                          cudaStream_t stream);
+                          const void* sizes, int sizes_is_i64, int num_groups, int masked_stride, long long m_rows,
+                          int n, int k, int in_fmt, int out_fp16, const float* a_scale, const float* b_scale,
+                          int want_ctas, cudaStream_t stream);
 // Scratch of the balanced K-grouped scheduler (int32 words): [0] tile counter, [1..63] unused,
 // then starts[G], tokens[G], order[G] (written by the plan kernel in gemm_bf16_k.cu).
 constexpr int kPlanHeaderWords = 64;

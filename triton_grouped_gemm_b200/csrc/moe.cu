@@ -7,20 +7,28 @@
 
 #include "../../include/b200gemm.h"
 #include "common.cuh"
+#include "quant_math.cuh"
 
 namespace b200 {
 
 constexpr int kMoeThreads = 256;
 
-// dst[i, :] = src[idx[i], :] for i < rows; row_vecs = row bytes / 16
+// dst[i, :] = src[idx[i], :] for i < rows; row_vecs = row bytes / 16.  An index outside
+// [0, src_rows) (e.g. the -1 the routing plan gives a pair with a bad expert id) is skipped and
+// flagged: the destination row keeps its contents.
 __global__ void __launch_bounds__(kMoeThreads)
 gather_rows_kernel(const uint4* __restrict__ src, const long long* __restrict__ idx, uint4* __restrict__ dst,
-                   long long rows, int row_vecs) {
+                   long long rows, int row_vecs, long long src_rows, unsigned* status) {
   const int lane = threadIdx.x & 31;
   const long long warp = (static_cast<long long>(blockIdx.x) * kMoeThreads + threadIdx.x) >> 5;
   const long long warps = (static_cast<long long>(gridDim.x) * kMoeThreads) >> 5;
   for (long long r = warp; r < rows; r += warps) {
-    const uint4* s = src + idx[r] * row_vecs;
+    const long long sr = idx[r];
+    if (sr < 0 || sr >= src_rows) {
+      if (lane == 0 && status) atomicOr(status, kDevBadRowIndex);
+      continue;
+    }
+    const uint4* s = src + sr * row_vecs;
     uint4* d = dst + r * row_vecs;
     int v = lane;
     for (; v + 96 < row_vecs; v += 128) {  // four independent 16-byte loads in flight per lane
@@ -37,7 +45,8 @@ gather_rows_kernel(const uint4* __restrict__ src, const long long* __restrict__ 
 // out[t, :] = bf16( sum_k w[t,k] * y[pos[t,k], :] ), fp32 accumulation in k order
 __global__ void __launch_bounds__(kMoeThreads)
 combine_topk_kernel(const uint4* __restrict__ y, const long long* __restrict__ pos, const float* __restrict__ w,
-                    uint4* __restrict__ out, long long tokens, int top_k, int row_vecs) {
+                    uint4* __restrict__ out, long long tokens, int top_k, int row_vecs, long long y_rows,
+                    unsigned* status) {
   const int lane = threadIdx.x & 31;
   const long long warp = (static_cast<long long>(blockIdx.x) * kMoeThreads + threadIdx.x) >> 5;
   const long long warps = (static_cast<long long>(gridDim.x) * kMoeThreads) >> 5;
@@ -47,7 +56,12 @@ combine_topk_kernel(const uint4* __restrict__ y, const long long* __restrict__ p
 #pragma unroll
       for (int e = 0; e < 8; ++e) acc[e] = 0.f;
       for (int k = 0; k < top_k; ++k) {
-        const uint4 q = __ldg(y + pos[t * top_k + k] * row_vecs + v);
+        const long long yr = pos[t * top_k + k];
+        if (yr < 0 || yr >= y_rows) {  // a pair the routing plan rejected: it contributes nothing
+          if (v == lane && lane == 0 && status) atomicOr(status, kDevBadRowIndex);
+          continue;
+        }
+        const uint4 q = __ldg(y + yr * row_vecs + v);
         const float wk = w[t * top_k + k];
         const uint32_t p[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
@@ -142,11 +156,13 @@ route_scatter_kernel(const long long* __restrict__ expert, long long n, int num_
   __syncthreads();
 #pragma unroll
   for (int j = 0; j < kPlanItems; ++j) {
+    const long long i = base + j * kPlanThreads + threadIdx.x;
     if (ex[j] >= 0) {
-      const long long i = base + j * kPlanThreads + threadIdx.x;
       const long long p = atomicAdd(&hist[ex[j]], 1);
       order[p] = i;
       pos[i] = p;
+    } else if (i < n) {
+      pos[i] = -1;  // rejected pair: the row movers skip negative indices
     }
   }
 }
@@ -160,10 +176,6 @@ route_scatter_kernel(const long long* __restrict__ expert, long long n, int num_
 // (rank < world, row < capacity): a bad index sets a status bit and is skipped, it cannot fault
 // a peer.
 constexpr int kMaxPeers = 16;
-// > 0: the multi-buffer movers run as that many 1024-thread blocks (at most one per SM), so that a
-// persistent GEMM launched beside them on the remaining SMs is never kept off an SM by a mover
-// block that happened to start there first
-static int g_mover_background_blocks = 0;
 struct PeerBases {
   void* base[kMaxPeers];
 };
@@ -172,18 +184,19 @@ struct PeerBases {
 __global__ void __launch_bounds__(1024)
 scatter_rows_multi_kernel(const uint4* __restrict__ src, const long long* __restrict__ src_idx, PeerBases bases,
                           const int* __restrict__ rank, const long long* __restrict__ row, long long rows,
-                          int row_vecs, int world, long long capacity_rows, unsigned* status) {
+                          int row_vecs, int world, long long capacity_rows, long long src_rows, unsigned* status) {
   const int lane = threadIdx.x & 31;
   const long long warp = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
   for (long long r = warp; r < rows; r += warps) {
     const int dst_rank = rank[r];
     const long long dst_row = row[r];
-    if (dst_rank < 0 || dst_rank >= world || dst_row < 0 || dst_row >= capacity_rows) {
+    const long long sr = src_idx[r];
+    if (dst_rank < 0 || dst_rank >= world || dst_row < 0 || dst_row >= capacity_rows || sr < 0 || sr >= src_rows) {
       if (lane == 0 && status) atomicOr(status, kDevBadRowIndex);
       continue;
     }
-    const uint4* s = src + src_idx[r] * row_vecs;
+    const uint4* s = src + sr * row_vecs;
     uint4* d = static_cast<uint4*>(bases.base[dst_rank]) + dst_row * row_vecs;
     int v = lane;
     for (; v + 96 < row_vecs; v += 128) {
@@ -194,6 +207,102 @@ scatter_rows_multi_kernel(const uint4* __restrict__ src, const long long* __rest
       d[v + 96] = e;
     }
     for (; v < row_vecs; v += 32) d[v] = __ldg(s + v);
+  }
+}
+
+// Quantise-on-dispatch: pair i (first <= i < first + count, send order) takes the 16-bit row of
+// token token_of_pair[i], quantises it 1x128 exactly like quant_act_1x128_kernel (same operation
+// order, so bytes and scales equal per_token_cast_to_fp8 followed by a row scatter), and stores
+// the e4m3 row, its hidden/128 fp32 scales and the pair's return address (i, my_rank) into the
+// owning rank's three buffers at row dst_row[i].  One warp per pair; 16 lanes share a 128-wide
+// block (8 elements each), so a warp does two blocks per step, four steps in flight.
+constexpr int kDqUnroll = 4;
+
+__global__ void __launch_bounds__(1024)
+dispatch_quant_rows_multi_kernel(const uint4* __restrict__ x, const long long* __restrict__ token_of_pair,
+                                 PeerBases rows8, PeerBases scales, PeerBases meta, const int* __restrict__ rank,
+                                 const long long* __restrict__ row, long long first, long long count,
+                                 long long tokens, int hidden, int is_fp16, int world, long long capacity_rows,
+                                 int my_rank, unsigned* status) {
+  const int lane = threadIdx.x & 31;
+  const long long warp = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  const int chunks = hidden >> 3;   // 8-element chunks per row (a multiple of 16: hidden % 128 == 0)
+  const int nb = hidden >> 7;       // 1x128 blocks per row (<= 64)
+  const int steps = (chunks + 31) >> 5;
+  for (long long p = warp; p < count; p += warps) {
+    const long long i = first + p;
+    const int dst_rank = rank[i];
+    const long long dst_row = row[i];
+    const long long t = token_of_pair[i];
+    if (dst_rank < 0 || dst_rank >= world || dst_row < 0 || dst_row >= capacity_rows || t < 0 || t >= tokens) {
+      if (lane == 0 && status) atomicOr(status, kDevBadRowIndex);
+      continue;
+    }
+    const uint4* src = x + t * chunks;
+    uint2* d8 = reinterpret_cast<uint2*>(static_cast<uint8_t*>(rows8.base[dst_rank]) + dst_row * hidden);
+    float* ds = static_cast<float*>(scales.base[dst_rank]) + dst_row * nb;
+    float s_lo = 0.f, s_hi = 0.f;  // lane L ends up holding the scales of blocks L and L + 32
+    for (int st0 = 0; st0 < steps; st0 += kDqUnroll) {
+      uint4 v[kDqUnroll];
+#pragma unroll
+      for (int u = 0; u < kDqUnroll; ++u) {
+        const int c = (st0 + u) * 32 + lane;
+        v[u] = (st0 + u < steps && c < chunks) ? __ldg(src + c) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int u = 0; u < kDqUnroll; ++u) {
+        const int st = st0 + u;
+        if (st >= steps) break;  // uniform over the warp
+        float amax = abs_max8(v[u], is_fp16);
+#pragma unroll
+        for (int o = 8; o >= 1; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+        amax = fmaxf(amax, 1e-4f);
+        const int c = st * 32 + lane;
+        if (c < chunks) d8[c] = quant8_e4m3(v[u], inv_scale_448(amax), is_fp16);
+        // blocks 2 st (lanes 0..15) and 2 st + 1 (lanes 16..31): lane L keeps the scale of block L mod 32
+        const float sc = __shfl_sync(0xFFFFFFFFu, __fdiv_rn(amax, 448.0f), (lane & 1) << 4);
+        if ((lane >> 1) == (st & 15)) {
+          if (st < 16) s_lo = sc;
+          else s_hi = sc;
+        }
+      }
+    }
+    if (lane < nb) ds[lane] = s_lo;
+    if (lane + 32 < nb) ds[lane + 32] = s_hi;
+    if (lane == 0)
+      *reinterpret_cast<longlong2*>(static_cast<long long*>(meta.base[dst_rank]) + 2 * dst_row) =
+          make_longlong2(i, static_cast<long long>(my_rank));
+  }
+}
+
+// The way back: dst[meta[r].rank][meta[r].row, :] = src[r, :] for r < rows, meta [rows, 2] int64 being
+// the return addresses the dispatch kernel left beside the rows (row in the owner's return
+// buffer, owner rank).
+__global__ void __launch_bounds__(1024)
+return_rows_multi_kernel(const uint4* __restrict__ src, const longlong2* __restrict__ meta, PeerBases bases,
+                         long long rows, int row_vecs, int world, long long capacity_rows, unsigned* status) {
+  const int lane = threadIdx.x & 31;
+  const long long warp = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  for (long long r = warp; r < rows; r += warps) {
+    const longlong2 m = meta[r];
+    const long long dst_row = m.x, dst_rank = m.y;
+    if (dst_rank < 0 || dst_rank >= world || dst_row < 0 || dst_row >= capacity_rows) {
+      if (lane == 0 && status) atomicOr(status, kDevBadRowIndex);
+      continue;
+    }
+    const uint4* s = src + r * row_vecs;
+    uint4* d = static_cast<uint4*>(bases.base[dst_rank]) + dst_row * row_vecs;
+    int v = lane;
+    for (; v + 96 < row_vecs; v += 128) {
+      const uint4 a = s[v], b = s[v + 32], c = s[v + 64], e = s[v + 96];
+      d[v] = a;
+      d[v + 32] = b;
+      d[v + 64] = c;
+      d[v + 96] = e;
+    }
+    for (; v < row_vecs; v += 32) d[v] = s[v];
   }
 }
 
@@ -265,6 +374,9 @@ int b200moe_route_plan(const int64_t* expert, int64_t n, int num_experts, int* c
   B200_CUDA(cudaMemsetAsync(counts, 0, sizeof(int) * num_experts, stream));
   if (n > 0) {
     B200_REQUIRE(expert && order && pos, "%s: null pointer", who);
+    // pairs with an expert id outside [0, num_experts) get no slot: the slots left over at the end
+    // of `order` then read -1, which every row mover skips
+    B200_CUDA(cudaMemsetAsync(order, 0xFF, sizeof(int64_t) * static_cast<size_t>(n), stream));
     const long long per_block = static_cast<long long>(kPlanThreads) * kPlanItems;
     const long long blocks = (n + per_block - 1) / per_block;
     B200_REQUIRE(blocks < (1ll << 31), "%s: too many pairs", who);
@@ -281,17 +393,26 @@ int b200moe_route_plan(const int64_t* expert, int64_t n, int num_experts, int* c
   return 0;
 }
 
-int b200moe_set_background_blocks(int blocks) {
-  b200::g_mover_background_blocks = blocks > 0 ? blocks : 0;
-  return 0;
+// grid of a multi-buffer mover: `blocks` > 0 = that many 1024-thread blocks (at most one per SM),
+// for running beside a persistent GEMM that was given the other SMs; otherwise fill the GPU
+static void mover_grid(int blocks_arg, long long rows, int sms, int* blocks, int* threads) {
+  if (blocks_arg > 0) {
+    *threads = 1024;
+    *blocks = blocks_arg < sms ? blocks_arg : sms;
+    return;
+  }
+  long long b = (rows + b200::kMoeThreads / 32 - 1) / (b200::kMoeThreads / 32);
+  if (b > 16ll * sms) b = 16ll * sms;
+  *threads = b200::kMoeThreads;
+  *blocks = static_cast<int>(b);
 }
 
 int b200moe_scatter_rows_multi(const void* src, const int64_t* src_idx, void* const* dst_bases, const int* dst_rank,
                                const int64_t* dst_row, int64_t rows, int64_t row_bytes, int world,
-                               int64_t capacity_rows, void* stream) {
+                               int64_t capacity_rows, int64_t src_rows, int blocks_arg, void* stream) {
   using namespace b200;
   const char* who = "b200moe_scatter_rows_multi";
-  B200_REQUIRE(rows >= 0 && row_bytes >= 0 && capacity_rows >= 0, "%s: negative size", who);
+  B200_REQUIRE(rows >= 0 && row_bytes >= 0 && capacity_rows >= 0 && src_rows >= 0, "%s: negative size", who);
   if (rows == 0 || row_bytes == 0) return 0;
   B200_REQUIRE(src && src_idx && dst_rank && dst_row, "%s: null pointer", who);
   B200_REQUIRE(row_bytes % 16 == 0 && row_bytes / 16 < (1ll << 30), "%s: row_bytes (%lld) must be a multiple of 16", who,
@@ -302,17 +423,71 @@ int b200moe_scatter_rows_multi(const void* src, const int64_t* src_idx, void* co
   if (rc) return rc;
   const int sms = sm_count();
   B200_REQUIRE(sms > 0, "%s: no CUDA device", who);
-  long long blocks = (rows + kMoeThreads / 32 - 1) / (kMoeThreads / 32);
-  if (blocks > 16ll * sms) blocks = 16ll * sms;
-  int threads = kMoeThreads;
-  if (g_mover_background_blocks > 0) {
-    threads = 1024;
-    blocks = g_mover_background_blocks < sms ? g_mover_background_blocks : sms;
-  }
-  scatter_rows_multi_kernel<<<static_cast<int>(blocks), threads, 0, static_cast<cudaStream_t>(stream)>>>(
+  int blocks, threads;
+  mover_grid(blocks_arg, rows, sms, &blocks, &threads);
+  scatter_rows_multi_kernel<<<blocks, threads, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(src), reinterpret_cast<const long long*>(src_idx), pb, dst_rank,
       reinterpret_cast<const long long*>(dst_row), rows, static_cast<int>(row_bytes / 16), world, capacity_rows,
-      device_status_ptr());
+      src_rows, device_status_ptr());
+  B200_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int b200moe_dispatch_quant_rows_multi(const void* x, const int64_t* token_of_pair, void* const* row_bases,
+                                      void* const* scale_bases, void* const* meta_bases, const int* dst_rank,
+                                      const int64_t* dst_row, int64_t first_pair, int64_t num_pairs, int64_t tokens,
+                                      int hidden, int dtype, int world, int64_t capacity_rows, int my_rank,
+                                      int blocks_arg, void* stream) {
+  using namespace b200;
+  const char* who = "b200moe_dispatch_quant_rows_multi";
+  B200_REQUIRE(first_pair >= 0 && num_pairs >= 0 && tokens >= 0 && capacity_rows >= 0, "%s: negative size", who);
+  B200_REQUIRE(dtype == 0 || dtype == 1, "%s: dtype must be 0 (bf16) or 1 (fp16)", who);
+  B200_REQUIRE(hidden > 0 && hidden % 128 == 0 && hidden <= 8192,
+               "%s: hidden (%d) must be a multiple of 128, at most 8192", who, hidden);
+  B200_REQUIRE(my_rank >= 0 && my_rank < world, "%s: my_rank (%d) outside [0, world)", who, my_rank);
+  if (num_pairs == 0) return 0;
+  B200_REQUIRE(x && token_of_pair && dst_rank && dst_row, "%s: null pointer", who);
+  B200_REQUIRE((reinterpret_cast<uintptr_t>(x) & 15) == 0, "%s: x must be 16-byte aligned", who);
+  PeerBases pr, ps, pm;
+  int rc = fill_bases(&pr, const_cast<const void* const*>(row_bases), world, who);
+  if (rc) return rc;
+  rc = fill_bases(&ps, const_cast<const void* const*>(scale_bases), world, who);
+  if (rc) return rc;
+  rc = fill_bases(&pm, const_cast<const void* const*>(meta_bases), world, who);
+  if (rc) return rc;
+  const int sms = sm_count();
+  B200_REQUIRE(sms > 0, "%s: no CUDA device", who);
+  int blocks, threads;
+  mover_grid(blocks_arg, num_pairs, sms, &blocks, &threads);
+  dispatch_quant_rows_multi_kernel<<<blocks, threads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(x), reinterpret_cast<const long long*>(token_of_pair), pr, ps, pm, dst_rank,
+      reinterpret_cast<const long long*>(dst_row), first_pair, num_pairs, tokens, hidden, dtype, world, capacity_rows,
+      my_rank, device_status_ptr());
+  B200_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int b200moe_return_rows_multi(const void* src, const int64_t* meta, void* const* dst_bases, int64_t rows,
+                              int64_t row_bytes, int world, int64_t capacity_rows, int blocks_arg, void* stream) {
+  using namespace b200;
+  const char* who = "b200moe_return_rows_multi";
+  B200_REQUIRE(rows >= 0 && row_bytes >= 0 && capacity_rows >= 0, "%s: negative size", who);
+  if (rows == 0 || row_bytes == 0) return 0;
+  B200_REQUIRE(src && meta, "%s: null pointer", who);
+  B200_REQUIRE(row_bytes % 16 == 0 && row_bytes / 16 < (1ll << 30), "%s: row_bytes (%lld) must be a multiple of 16", who,
+               (long long)row_bytes);
+  B200_REQUIRE((reinterpret_cast<uintptr_t>(src) & 15) == 0 && (reinterpret_cast<uintptr_t>(meta) & 15) == 0,
+               "%s: src and meta must be 16-byte aligned", who);
+  PeerBases pb;
+  int rc = fill_bases(&pb, const_cast<const void* const*>(dst_bases), world, who);
+  if (rc) return rc;
+  const int sms = sm_count();
+  B200_REQUIRE(sms > 0, "%s: no CUDA device", who);
+  int blocks, threads;
+  mover_grid(blocks_arg, rows, sms, &blocks, &threads);
+  return_rows_multi_kernel<<<blocks, threads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(src), reinterpret_cast<const longlong2*>(meta), pb, rows,
+      static_cast<int>(row_bytes / 16), world, capacity_rows, device_status_ptr());
   B200_CUDA(cudaGetLastError());
   return 0;
 }
@@ -342,9 +517,9 @@ int b200moe_combine_topk_multi(const void* const* src_bases, const int* pair_ran
 }
 
 int b200moe_gather_rows(const void* src, const int64_t* idx, void* dst, int64_t rows, int64_t row_bytes,
-                        void* stream) {
+                        int64_t src_rows, void* stream) {
   using namespace b200;
-  B200_REQUIRE(rows >= 0 && row_bytes >= 0, "b200moe_gather_rows: negative size");
+  B200_REQUIRE(rows >= 0 && row_bytes >= 0 && src_rows >= 0, "b200moe_gather_rows: negative size");
   if (rows == 0 || row_bytes == 0) return 0;
   B200_REQUIRE(src && idx && dst, "b200moe_gather_rows: null pointer");
   B200_REQUIRE(row_bytes % 16 == 0 && row_bytes / 16 < (1ll << 30), "b200moe_gather_rows: row_bytes (%lld) must be a multiple of 16",
@@ -357,15 +532,15 @@ int b200moe_gather_rows(const void* src, const int64_t* idx, void* dst, int64_t 
   if (blocks > 16ll * sms) blocks = 16ll * sms;
   gather_rows_kernel<<<static_cast<int>(blocks), kMoeThreads, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(src), reinterpret_cast<const long long*>(idx), static_cast<uint4*>(dst), rows,
-      static_cast<int>(row_bytes / 16));
+      static_cast<int>(row_bytes / 16), src_rows, device_status_ptr());
   B200_CUDA(cudaGetLastError());
   return 0;
 }
 
 int b200moe_combine_topk(const void* y, const int64_t* pos, const float* weights, void* out, int64_t tokens, int top_k,
-                         int hidden, void* stream) {
+                         int hidden, int64_t y_rows, void* stream) {
   using namespace b200;
-  B200_REQUIRE(tokens >= 0 && top_k > 0 && hidden >= 0, "b200moe_combine_topk: bad size");
+  B200_REQUIRE(tokens >= 0 && top_k > 0 && hidden >= 0 && y_rows >= 0, "b200moe_combine_topk: bad size");
   if (tokens == 0 || hidden == 0) return 0;
   B200_REQUIRE(y && pos && weights && out, "b200moe_combine_topk: null pointer");
   B200_REQUIRE(hidden % 8 == 0, "b200moe_combine_topk: hidden (%d) must be a multiple of 8", hidden);
@@ -377,7 +552,7 @@ int b200moe_combine_topk(const void* y, const int64_t* pos, const float* weights
   if (blocks > 16ll * sms) blocks = 16ll * sms;
   combine_topk_kernel<<<static_cast<int>(blocks), kMoeThreads, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(y), reinterpret_cast<const long long*>(pos), weights, static_cast<uint4*>(out), tokens,
-      top_k, hidden / 8);
+      top_k, hidden / 8, y_rows, device_status_ptr());
   B200_CUDA(cudaGetLastError());
   return 0;
 }

@@ -14,22 +14,6 @@
 
 namespace b200 {
 
-__device__ __forceinline__ float to_f32(uint16_t raw, int is_fp16) {
-  if (is_fp16) return __half2float(__ushort_as_half(raw));
-  return __uint_as_float(static_cast<uint32_t>(raw) << 16);
-}
-
-__device__ __forceinline__ float abs_max8(const uint4& v, int is_fp16) {
-  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-  float m = 0.f;
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    m = fmaxf(m, fabsf(to_f32(static_cast<uint16_t>(w[i] & 0xFFFFu), is_fp16)));
-    m = fmaxf(m, fabsf(to_f32(static_cast<uint16_t>(w[i] >> 16), is_fp16)));
-  }
-  return m;
-}
-
 // ------------------------------------------------------------------ 1x128 (activations)
 // Follows per_token_cast_to_fp8 (gemm/FP8/m_grouped_gemm_channel_expert.py:217-222):
 //   amax = max|x| over the block, clamped below at 1e-4
@@ -315,7 +299,7 @@ template <bool kFp16>
 __global__ void __launch_bounds__(kBlkThreads)
 quant_trans_expand_kernel(const uint16_t* __restrict__ x, const void* __restrict__ sizes, int sizes_i64,
                           int num_groups, uint8_t* __restrict__ q, float* __restrict__ s,
-                          long long* __restrict__ padded_sizes_out, int n, long long m_expand) {
+                          long long* __restrict__ padded_sizes_out, long long m_rows, int n, long long m_expand) {
   __shared__ uint32_t red[kBlkThreads / 32];
   __shared__ __align__(16) uint8_t stage[128 * kTqPitch];
   const int n_tiles = n / 128;
@@ -337,7 +321,7 @@ quant_trans_expand_kernel(const uint16_t* __restrict__ x, const void* __restrict
   }
 
   GroupWalker w;
-  w.init(sizes, sizes_i64, num_groups, 0, 128);
+  w.init(sizes, sizes_i64, num_groups, 0, 128, m_rows);  // no row of x at or past m_rows is read
   bool in_groups = true;
   for (long long tile = blockIdx.x; tile < static_cast<long long>(m_tiles_total) * n_tiles; tile += gridDim.x) {
     const int mt = static_cast<int>(tile / n_tiles);
@@ -525,11 +509,11 @@ int b200quant_trans_expand_128x(const void* x, const void* sizes, int sizes_is_i
   if (dtype == 1)
     quant_trans_expand_kernel<true><<<grid, kBlkThreads, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const uint16_t*>(x), sizes, sizes_is_i64, num_groups, static_cast<uint8_t*>(q), scales,
-        reinterpret_cast<long long*>(padded_sizes_out), n, m_expand);
+        reinterpret_cast<long long*>(padded_sizes_out), m_rows, n, m_expand);
   else
     quant_trans_expand_kernel<false><<<grid, kBlkThreads, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const uint16_t*>(x), sizes, sizes_is_i64, num_groups, static_cast<uint8_t*>(q), scales,
-        reinterpret_cast<long long*>(padded_sizes_out), n, m_expand);
+        reinterpret_cast<long long*>(padded_sizes_out), m_rows, n, m_expand);
   B200_CUDA(cudaGetLastError());
   return 0;
 }

@@ -47,7 +47,8 @@ def _gather_rows(rows: torch.Tensor, idx: torch.Tensor) -> torch.Tensor:
         idx64 = idx.to(torch.int64).contiguous()
         with torch.cuda.device(rows.device):
             rc = _lib.load().b200moe_gather_rows(rows.data_ptr(), idx64.data_ptr(), out.data_ptr(), idx64.numel(),
-                                                 rows.shape[1] * rows.element_size(), _lib.stream_ptr(rows.device))
+                                                 rows.shape[1] * rows.element_size(), rows.shape[0],
+                                                 _lib.stream_ptr(rows.device))
         _lib.check(rc, "b200moe_gather_rows")
         return out
     return rows[idx]
@@ -56,7 +57,9 @@ def _gather_rows(rows: torch.Tensor, idx: torch.Tensor) -> torch.Tensor:
 def route_plan(keys: torch.Tensor, num_keys: int):
     """Counting sort of ``keys`` (int64, values in [0, num_keys)): returns (counts int64 [num_keys],
     order int64 [n] - indices grouped by key, pos = order^-1).  On CUDA one pass of the library's
-    routing-plan kernels (order inside a key's range unspecified); on the host a stable argsort."""
+    routing-plan kernels (order inside a key's range unspecified); on the host a stable argsort.
+    A key outside the range (a dropped token's -1) is counted nowhere and gets pos = -1; the slots
+    it leaves at the end of ``order`` hold -1.  The row movers skip negative indices."""
     n = keys.numel()
     if keys.is_cuda and num_keys <= 1024:
         from .. import _lib
@@ -71,10 +74,15 @@ def route_plan(keys: torch.Tensor, num_keys: int):
                                                 order.data_ptr(), pos.data_ptr(), _lib.stream_ptr(keys.device))
         _lib.check(rc, "b200moe_route_plan")
         return counts.to(torch.int64), order, pos
-    order = torch.argsort(keys, stable=True)
-    pos = torch.empty_like(order)
-    pos[order] = torch.arange(n, device=keys.device)
-    return torch.bincount(keys, minlength=num_keys), order, pos
+    # host tensors (the gloo tests): a stable argsort; keys outside [0, num_keys) are rejected like
+    # the kernels do - counted nowhere, pos = -1, their slots at the end of `order` = -1
+    ok = (keys >= 0) & (keys < num_keys)
+    order = torch.argsort(torch.where(ok, keys, torch.full_like(keys, num_keys)), stable=True)
+    n_ok = int(ok.sum())
+    pos = torch.full_like(order, -1)
+    pos[order[:n_ok]] = torch.arange(n_ok, device=keys.device)
+    order = torch.cat([order[:n_ok], order.new_full((n - n_ok,), -1)])
+    return torch.bincount(keys[ok], minlength=num_keys), order, pos
 
 
 def _all_to_all(out: torch.Tensor, inp: torch.Tensor, out_splits, in_splits, group) -> None:
@@ -251,7 +259,8 @@ def combine(plan: DispatchPlan, expert_rows: torch.Tensor, topk_weight: torch.Te
         w32 = topk_weight.reshape(-1).to(torch.float32).contiguous()
         with torch.cuda.device(ret.device):
             rc = _lib.load().b200moe_combine_topk(ret.data_ptr(), pos.data_ptr(), w32.data_ptr(), out.data_ptr(),
-                                                  plan.num_tokens, plan.top_k, ret.shape[1], _lib.stream_ptr(ret.device))
+                                                  plan.num_tokens, plan.top_k, ret.shape[1], ret.shape[0],
+                                                  _lib.stream_ptr(ret.device))
         _lib.check(rc, "b200moe_combine_topk")
         return out
     pair_rows = ret[pos]                                              # (token, k) order

@@ -33,7 +33,10 @@ class Fp8MoELayer:
         GEMMs, which then leave ``comm_sms`` SMs to the collective's kernels.
         ``transport="p2p"`` replaces the all-to-alls by kernels that store / load rows in the
         other ranks' memory directly (``ep/p2p.py``); it needs ``tokens_per_rank`` and ``top_k`` to
-        size its buffers: ``capacity_factor`` x the mean number of rows a rank receives."""
+        size its buffers: ``capacity_factor`` x the mean number of rows a rank receives.  There the
+        received rows are laid out [local expert][source rank], one row group per expert, and
+        ``chunks`` (any number up to the local expert count) splits the experts into nearly equal
+        runs.  Call ``close()`` on every rank when done with a p2p layer."""
         assert w13.dim() == 3 and w2.dim() == 3 and w13.shape[0] == w2.shape[0]
         self.group = group
         self.num_experts = num_experts
@@ -49,41 +52,81 @@ class Fp8MoELayer:
         # activation already bound the kernel: 10.4 ms against 9.0 + 1.05 ms), so forward() keeps
         # the product and the separate SwiGLU quantiser.
         self.fused_swiglu = self.inter % 128 == 0
-        self.w13_interleaved = per_block_cast_to_fp8(interleave_gate_up(w13)) if self.fused_swiglu else None
+        self._w13_interleaved = None   # built by the first decode()
         world = 1 if group is None else dist.get_world_size(group)
-        while chunks > 1 and self.e_local % chunks:
-            chunks -= 1
         self.world = world
-        self.chunks = chunks if world > 1 else 1
         self.comm_sms = comm_sms
         assert transport in ("nccl", "p2p")
         self.transport = transport if world > 1 else "nccl"
+        if self.transport == "nccl":
+            while chunks > 1 and self.e_local % chunks:
+                chunks -= 1
+        self.chunks = max(1, min(chunks, self.e_local)) if world > 1 else 1
+        self._peer_buffers = []
         if self.transport == "p2p":
-            from .p2p import PeerBuffer
+            from .p2p import PeerBuffer, chunk_bounds
 
             assert tokens_per_rank > 0 and top_k > 0, "the p2p transport sizes its buffers from tokens_per_rank and top_k"
+            assert self.hidden % 128 == 0, "the p2p transport moves 1x128-quantised rows: hidden must be a multiple of 128"
             cap = (int(tokens_per_rank * top_k * capacity_factor) + 255) // 256 * 256
             dev = w13.device
+            self.bounds = chunk_bounds(self.e_local, self.chunks)
             self.recv8 = PeerBuffer(cap, self.hidden, torch.uint8, dev, group)
-            self.recvs = PeerBuffer(cap, (self.hidden + 127) // 128, torch.float32, dev, group)
+            self.recvs = PeerBuffer(cap, self.hidden // 128, torch.float32, dev, group)
             self.ybuf = PeerBuffer(cap, self.hidden, torch.bfloat16, dev, group)
+            self._peer_buffers = [self.recv8, self.recvs, self.ybuf]
             self._flag = torch.zeros(1, dtype=torch.int32, device=dev)
             if self.chunks > 1:
                 # pipelined form: results are pushed back into the token owner's buffer chunk by chunk
                 self.meta = PeerBuffer(cap, 2, torch.int64, dev, group)
                 self.ret = PeerBuffer(tokens_per_rank * top_k, self.hidden, torch.bfloat16, dev, group)
+                self._peer_buffers += [self.meta, self.ret]
                 self._side = (torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev))
+
+    @property
+    def w13_interleaved(self):
+        """Gate and up rows interleaved in 128-row blocks, quantised: the weight layout of the
+        gate+up GEMM with the SwiGLU epilogue.  Only decode() needs it, so this second quantised
+        copy of w13 is built on first use."""
+        if self._w13_interleaved is None and self.fused_swiglu:
+            # 128x128 quantisation commutes with the interleave (whole scale blocks move): permute the
+            # quantised bytes in 128-row blocks and the scale matrix in single rows
+            q, sc = self.w13
+            e, two_i, _ = q.shape
+            sc_il = sc.reshape(e, 2, two_i // 256, sc.shape[-1]).transpose(1, 2).reshape(e, two_i // 128, -1)
+            self._w13_interleaved = (interleave_gate_up(q.view(torch.uint8)).view(q.dtype), sc_il.contiguous())
+        return self._w13_interleaved
+
+    def close(self) -> None:
+        """Releases the peer-memory buffers of transport="p2p".  Collective: every rank calls it,
+        after its last forward().  The last step of forward() reads or writes the other ranks'
+        buffers, and nothing after it orders those accesses against a rank that goes on to free
+        its memory; so this waits for the device, meets the other ranks at a barrier, and only then
+        unmaps and frees (a rank must not leave or free between its last forward() and that
+        barrier).  Safe to call twice; a layer with another transport has nothing to release."""
+        if not self._peer_buffers:
+            return
+        torch.cuda.synchronize(self.recv8.local.device)
+        dist.barrier(group=self.group)
+        for buf in self._peer_buffers:
+            buf.close(self.group)
+        self._peer_buffers = []
 
     def experts(self, x8: torch.Tensor, xs: torch.Tensor, size_per_group: torch.Tensor,
                 group_to_expert: Optional[torch.Tensor] = None, num_sms: int = -1,
-                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                out: Optional[torch.Tensor] = None, first_expert: int = 0) -> torch.Tensor:
         """Rows grouped by local expert: [R, H] fp8 + scales -> [R, H] bf16.  With
         ``group_to_expert`` (int32) the row groups are arbitrary blocks, block i using the
-        weights of local expert ``group_to_expert[i]``."""
-        h = m_grouped_fp8_block_scaled((x8, xs), self.w13, size_per_group, num_sms=num_sms,
-                                       group_to_b=group_to_expert)
+        weights of local expert ``group_to_expert[i]``; without it, group i uses local expert
+        ``first_expert + i`` (``size_per_group`` may cover a run of the experts only)."""
+        w13, w2 = self.w13, self.w2
+        if group_to_expert is None and (first_expert or size_per_group.numel() != self.e_local):
+            hi = first_expert + size_per_group.numel()
+            w13 = (w13[0][first_expert:hi], w13[1][first_expert:hi])
+            w2 = (w2[0][first_expert:hi], w2[1][first_expert:hi])
+        h = m_grouped_fp8_block_scaled((x8, xs), w13, size_per_group, num_sms=num_sms, group_to_b=group_to_expert)
         a8, a_s = swiglu_per_token_cast_to_fp8(h)
-        return m_grouped_fp8_block_scaled((a8, a_s), self.w2, size_per_group, num_sms=num_sms,
+        return m_grouped_fp8_block_scaled((a8, a_s), w2, size_per_group, num_sms=num_sms,
                                           group_to_b=group_to_expert, out=out)
 
     def _forward_p2p(self, x8, xs, topk_idx, topk_weight) -> torch.Tensor:
@@ -96,17 +139,17 @@ class Fp8MoELayer:
         scatter_rows(plan, xs, self.recvs)
         dist.all_reduce(self._flag, group=self.group)       # every rank's rows have landed everywhere
         r = plan.rows_here
-        self.experts(self.recv8.local[:r].view(torch.float8_e4m3fn), self.recvs.local[:r], plan.block_sizes,
-                     group_to_expert=plan.block_expert, out=self.ybuf.local[:r])
+        self.experts(self.recv8.local[:r].view(torch.float8_e4m3fn), self.recvs.local[:r], plan.size_per_group,
+                     out=self.ybuf.local[:r])
         dist.all_reduce(self._flag, group=self.group)       # every rank's results are written
         return combine_rows(plan, self.ybuf, topk_weight)
 
     def forward(self, x: torch.Tensor, topk_idx: torch.Tensor, topk_weight: torch.Tensor) -> torch.Tensor:
         """x [T, H] bf16, topk_idx/topk_weight [T, k] -> [T, H] bf16."""
+        if self.transport == "p2p" and self.chunks > 1:
+            return self._forward_p2p_pipelined(x.contiguous(), topk_idx, topk_weight)  # quantises while it dispatches
         x8, xs = per_token_cast_to_fp8(x.contiguous())
         if self.transport == "p2p":
-            if self.chunks > 1:
-                return self._forward_p2p_pipelined(x8, xs, topk_idx, topk_weight)
             return self._forward_p2p(x8, xs, topk_idx, topk_weight)
         if self.world > 1:
             return self._forward_pipelined(x8, xs, topk_idx, topk_weight)
@@ -147,71 +190,66 @@ class Fp8MoELayer:
         w32 = topk_weight.reshape(-1).to(torch.float32).contiguous()
         with torch.cuda.device(x8.device):
             rc = _lib.load().b200moe_combine_topk(ret.data_ptr(), pos.data_ptr(), w32.data_ptr(), out.data_ptr(),
-                                                  plan.num_tokens, plan.top_k, self.hidden, _lib.stream_ptr(x8.device))
+                                                  plan.num_tokens, plan.top_k, self.hidden, ret.shape[0],
+                                                  _lib.stream_ptr(x8.device))
         _lib.check(rc, "b200moe_combine_topk")
         return out
 
-    def _forward_p2p_pipelined(self, x8, xs, topk_idx, topk_weight) -> torch.Tensor:
-        """Peer memory in both directions, beside the GEMMs: a dispatch stream scatters chunk after
-        chunk into the owners' buffers (rows, scales and each row's return address), the main
-        stream runs chunk c's GEMMs as soon as its rows have landed everywhere, a return stream
-        pushes chunk c's results into the token owners' buffers; the movers run as a few large
-        blocks on the SMs the GEMMs leave free.  A local weighted sum finishes the step."""
+    def _forward_p2p_pipelined(self, x, topk_idx, topk_weight) -> torch.Tensor:
+        """Peer memory in both directions, beside the GEMMs.  A dispatch stream sends chunk after
+        chunk: one kernel per chunk quantises each pair's bf16 token row 1x128 and stores the fp8
+        row, its scales and the pair's return address into the owner's buffers.  The main stream
+        runs chunk c's GEMMs (one row group per expert) as soon as its rows have landed
+        everywhere; a return stream pushes chunk c's results into the token owners' buffers through
+        the return addresses.  Movers that run beside a GEMM are a few large blocks on the SMs the
+        GEMMs leave free; the first dispatch and the last return use the whole GPU.  A local
+        weighted sum finishes the step."""
         from .. import _lib
-        from .p2p import make_peer_chunk_plan, scatter_range
+        from .p2p import dispatch_quant_range, make_peer_chunk_plan, return_rows
 
         lib = _lib.load()
-        dev = x8.device
-        plan = make_peer_chunk_plan(topk_idx, self.num_experts, self.group, self.recv8.capacity, self.chunks)
+        dev = x.device
+        plan = make_peer_chunk_plan(topk_idx, self.num_experts, self.group, self.recv8.capacity, self.bounds)
         assert plan.pos.numel() <= self.ret.capacity, "more (token, k) pairs than the return buffer holds"
+        chunks = plan.chunks
         sms = lib.b200gemm_sm_count()
         gemm_sms = sms - self.comm_sms if 0 < self.comm_sms < sms - 2 else -1
         main = torch.cuda.current_stream(dev)
         s_disp, s_ret = self._side
         ready = torch.cuda.Event()
         ready.record(main)
-        landed = [torch.cuda.Event() for _ in range(self.chunks)]
-        computed = [torch.cuda.Event() for _ in range(self.chunks)]
-        # movers that run beside a GEMM use `comm_sms` large blocks (one per SM the GEMM leaves free);
-        # the first dispatch and the last return have the GPU to themselves and use the full grid
+        landed = [torch.cuda.Event() for _ in range(chunks)]
+        computed = [torch.cuda.Event() for _ in range(chunks)]
         background = max(self.comm_sms, 1)
-        try:
-            with torch.cuda.stream(s_disp):
-                s_disp.wait_event(ready)
-                for c in range(self.chunks):
-                    lo, hi = plan.send_offsets[c], plan.send_offsets[c + 1]
-                    tok, dr, dw = plan.token_of_pair[lo:hi], plan.dst_rank[lo:hi], plan.dst_row[lo:hi]
-                    lib.b200moe_set_background_blocks(0 if c == 0 else background)
-                    scatter_range(x8, tok, dr, dw, self.recv8)
-                    scatter_range(xs, tok, dr, dw, self.recvs)
-                    scatter_range(plan.meta, torch.arange(lo, hi, device=dev), dr, dw, self.meta)
-                    dist.all_reduce(self._flag, group=self.group)      # chunk c has landed on every rank
-                    landed[c].record(s_disp)
-            for c in range(self.chunks):
-                lo, hi = plan.recv_offsets[c], plan.recv_offsets[c + 1]
-                main.wait_event(landed[c])
-                self.experts(self.recv8.local[lo:hi].view(torch.float8_e4m3fn), self.recvs.local[lo:hi],
-                             plan.block_sizes[c], group_to_expert=plan.block_expert[c], num_sms=gemm_sms,
-                             out=self.ybuf.local[lo:hi])
-                computed[c].record(main)
-                with torch.cuda.stream(s_ret):
-                    s_ret.wait_event(computed[c])
-                    back_row = self.meta.local[lo:hi, 0].contiguous()
-                    back_rank = self.meta.local[lo:hi, 1].to(torch.int32).contiguous()
-                    lib.b200moe_set_background_blocks(0 if c == self.chunks - 1 else background)
-                    scatter_range(self.ybuf.local, torch.arange(lo, hi, device=dev), back_rank, back_row, self.ret)
+        with torch.cuda.stream(s_disp):
+            s_disp.wait_event(ready)
+            for c in range(chunks):
+                dispatch_quant_range(x, plan, plan.send_offsets[c], plan.send_offsets[c + 1], self.recv8, self.recvs,
+                                     self.meta, blocks=0 if c == 0 else background)
+                dist.all_reduce(self._flag, group=self.group)      # chunk c has landed on every rank
+                landed[c].record(s_disp)
+        for c in range(chunks):
+            lo, hi = plan.recv_offsets[c], plan.recv_offsets[c + 1]
+            main.wait_event(landed[c])
+            self.experts(self.recv8.local[lo:hi].view(torch.float8_e4m3fn), self.recvs.local[lo:hi],
+                         plan.size_per_group[self.bounds[c]:self.bounds[c + 1]], num_sms=gemm_sms,
+                         out=self.ybuf.local[lo:hi], first_expert=self.bounds[c])
+            computed[c].record(main)
             with torch.cuda.stream(s_ret):
-                dist.all_reduce(self._flag, group=self.group)          # every rank's results have been pushed
-                done = torch.cuda.Event()
-                done.record(s_ret)
-            main.wait_event(done)
-        finally:
-            lib.b200moe_set_background_blocks(0)
+                s_ret.wait_event(computed[c])
+                return_rows(self.ybuf.local[lo:hi], self.meta.local[lo:hi], self.ret,
+                            blocks=0 if c == chunks - 1 else background)
+        with torch.cuda.stream(s_ret):
+            dist.all_reduce(self._flag, group=self.group)          # every rank's results have been pushed
+            done = torch.cuda.Event()
+            done.record(s_ret)
+        main.wait_event(done)
         out = torch.empty((plan.num_tokens, self.hidden), dtype=torch.bfloat16, device=dev)
         w32 = topk_weight.reshape(-1).to(torch.float32).contiguous()
         with torch.cuda.device(dev):
             rc = lib.b200moe_combine_topk(self.ret.local.data_ptr(), plan.pos.data_ptr(), w32.data_ptr(), out.data_ptr(),
-                                          plan.num_tokens, plan.top_k, self.hidden, _lib.stream_ptr(dev))
+                                          plan.num_tokens, plan.top_k, self.hidden, self.ret.capacity,
+                                          _lib.stream_ptr(dev))
         _lib.check(rc, "b200moe_combine_topk")
         return out
 

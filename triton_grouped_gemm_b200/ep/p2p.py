@@ -3,8 +3,9 @@
 Every rank owns three buffers of fixed capacity - received fp8 rows, their 1x128 scales, and the
 bf16 results of its experts - and maps the other ranks' buffers into its address space (CUDA
 IPC through the library's `b200ipc_*` helpers).  Dispatch is then ONE kernel per payload that stores each
-(token, k) row straight into the owning rank's receive buffer at its final position (arrival
-order: [source rank][local expert] blocks, what the mapped grouped GEMM consumes), and combine is
+(token, k) row straight into the owning rank's receive buffer at its final position
+([local expert][source rank] order: every expert's rows are contiguous, so the grouped GEMM sees
+one row group per expert whatever the number of ranks), and combine is
 ONE kernel that loads each (token, k) result from the rank that computed it while it forms the
 router-weighted sum.  The bytes cross NVLink once, as plain stores / loads of those kernels; there
 is no send-side gather, no staging copy and no permutation.  Ranks synchronise with two one-word
@@ -70,7 +71,10 @@ class PeerBuffer:
         dist.barrier(group=group)
 
     def close(self, group=None) -> None:
-        """Unmaps the other ranks' buffers, then (after a barrier) frees this rank's."""
+        """Unmaps the other ranks' buffers, then (after a barrier) frees this rank's.  Collective:
+        every rank of the group must call it, with no kernel that touches the buffers in flight."""
+        if not self._own_ptr and not self._opened:
+            return
         for p in self._opened:
             self._lib.b200ipc_close(ctypes.c_void_p(p))
         self._opened = []
@@ -92,8 +96,22 @@ class PeerPlan:
     pair_rank: torch.Tensor       # [T*k] int32, (token, k) order
     pair_row: torch.Tensor        # [T*k] int64, (token, k) order
     rows_here: int                # rows this rank receives
-    block_sizes: torch.Tensor     # [world * e_loc] int64 rows of each [source rank][local expert] block here
-    block_expert: torch.Tensor    # [world * e_loc] int32 local expert of each block
+    size_per_group: torch.Tensor  # [e_loc] int64 rows of each local expert here (all source ranks together)
+
+
+def _arrival_layout(counts: torch.Tensor, group, num_experts: int):
+    """All-gathers the per-expert pair counts and lays every rank's receive buffer out as
+    [local expert][source rank] blocks.  Returns (by_dest [d, l, s] block sizes, dst_block_start
+    [num_experts]: where THIS rank's rows for each global expert start in the owner's buffer,
+    totals [world]: rows every rank receives)."""
+    world, me = dist.get_world_size(group), dist.get_rank(group)
+    e_loc = num_experts // world
+    counts_flat = torch.empty(world * num_experts, dtype=counts.dtype, device=counts.device)
+    dist.all_gather_into_tensor(counts_flat, counts.contiguous(), group=group)
+    by_dest = counts_flat.view(world, world, e_loc).permute(1, 2, 0).contiguous()       # [d, l, s]
+    flat_blocks = by_dest.view(world, e_loc * world)
+    starts = (flat_blocks.cumsum(1) - flat_blocks).view(world, e_loc, world)            # [d, l, s]
+    return by_dest, starts[:, :, me].reshape(num_experts), flat_blocks.sum(1)
 
 
 def make_peer_plan(topk_idx: torch.Tensor, num_experts: int, group, capacity_rows: int) -> PeerPlan:
@@ -106,26 +124,23 @@ def make_peer_plan(topk_idx: torch.Tensor, num_experts: int, group, capacity_row
 
     flat = topk_idx.reshape(-1).to(torch.int64)
     counts, send_order, pos = route_plan(flat, num_experts)
-    counts_flat = torch.empty(world * num_experts, dtype=counts.dtype, device=dev)
-    dist.all_gather_into_tensor(counts_flat, counts, group=group)
-    counts_all = counts_flat.view(world, num_experts)
-    # arrival layout at destination d: blocks (source s, local expert j) in that order
-    by_dest = counts_all.view(world, world, e_loc).permute(1, 0, 2).contiguous()      # [d, s, j]
-    flat_blocks = by_dest.view(world, world * e_loc)
-    starts = (flat_blocks.cumsum(1) - flat_blocks).view(world, world, e_loc)           # [d, s, j]
-    dst_block_start = starts[:, me, :].reshape(num_experts)                            # by global expert
-    totals = flat_blocks.sum(1).cpu()                                                  # the one host sync
-    if int(totals.max()) > capacity_rows:
-        raise RuntimeError(f"a rank would receive {int(totals.max())} rows, more than the exchange buffers hold "
-                           f"({capacity_rows}); raise capacity_factor")
+    by_dest, dst_block_start, totals_dev = _arrival_layout(counts, group, num_experts)
+    totals = torch.cat([totals_dev, counts.sum()[None]]).cpu()                         # the one host sync
+    if int(totals[:world].max()) > capacity_rows:
+        raise RuntimeError(f"a rank would receive {int(totals[:world].max())} rows, more than the exchange buffers "
+                           f"hold ({capacity_rows}); raise capacity_factor")
     my_send_start = counts.cumsum(0) - counts
-    e_sorted = flat[send_order]
+    valid = send_order[:int(totals[world])]            # pairs with an expert id out of range are not sent
+    e_sorted = flat[valid]
     dst_rank = (e_sorted // e_loc).to(torch.int32)
-    dst_row = dst_block_start[e_sorted] + (torch.arange(t * k, device=dev) - my_send_start[e_sorted])
-    return PeerPlan(num_tokens=t, top_k=k, token_of_pair=(send_order // k).contiguous(), dst_rank=dst_rank.contiguous(),
-                    dst_row=dst_row.contiguous(), pair_rank=dst_rank[pos].contiguous(), pair_row=dst_row[pos].contiguous(),
-                    rows_here=int(totals[me]), block_sizes=by_dest[me].reshape(-1).to(torch.int64).contiguous(),
-                    block_expert=torch.arange(e_loc, device=dev, dtype=torch.int32).repeat(world).contiguous())
+    dst_row = dst_block_start[e_sorted] + (torch.arange(valid.numel(), device=dev) - my_send_start[e_sorted])
+    ok = pos >= 0
+    safe = pos.clamp(min=0)
+    pair_rank = torch.where(ok, dst_rank[safe], torch.full_like(dst_rank[safe], -1))   # -1: skipped by the combine
+    pair_row = torch.where(ok, dst_row[safe], torch.full_like(dst_row[safe], -1))
+    return PeerPlan(num_tokens=t, top_k=k, token_of_pair=(valid // k).contiguous(), dst_rank=dst_rank.contiguous(),
+                    dst_row=dst_row.contiguous(), pair_rank=pair_rank.contiguous(), pair_row=pair_row.contiguous(),
+                    rows_here=int(totals[me]), size_per_group=by_dest[me].sum(-1).to(torch.int64).contiguous())
 
 
 def scatter_rows(plan: PeerPlan, rows: torch.Tensor, buf: PeerBuffer) -> None:
@@ -138,7 +153,7 @@ def scatter_rows(plan: PeerPlan, rows: torch.Tensor, buf: PeerBuffer) -> None:
         rc = _lib.load().b200moe_scatter_rows_multi(src.data_ptr(), plan.token_of_pair.data_ptr(), buf.bases,
                                                     plan.dst_rank.data_ptr(), plan.dst_row.data_ptr(),
                                                     plan.token_of_pair.numel(), row_bytes, buf.world, buf.capacity,
-                                                    _lib.stream_ptr(src.device))
+                                                    src.shape[0], 0, _lib.stream_ptr(src.device))
     _lib.check(rc, "b200moe_scatter_rows_multi")
 
 
@@ -157,78 +172,114 @@ def combine_rows(plan: PeerPlan, buf: PeerBuffer, topk_weight: torch.Tensor) -> 
 
 @dataclass
 class PeerChunkPlan:
-    """Peer-memory plan split into ``chunks`` groups of local experts (chunk c = local experts
-    [c*ec, (c+1)*ec) on every rank).  Send order and every rank's receive buffers are chunk-major:
-    [chunk][source rank][expert of the chunk], so a chunk is one contiguous row range everywhere."""
+    """Peer-memory plan split into chunks of consecutive local experts (chunk c = local experts
+    [bounds[c], bounds[c+1]) on every rank).  Send order is chunk-major ([chunk][destination
+    rank][expert]); every rank's receive buffers are [local expert][source rank], so a chunk is one
+    contiguous row range everywhere and each of its experts is one contiguous row group."""
     num_tokens: int
     top_k: int
-    chunks: int
+    bounds: List[int]                # [chunks + 1] local-expert boundaries of the chunks
     token_of_pair: torch.Tensor      # [T*k] send order
     dst_rank: torch.Tensor           # [T*k] int32
     dst_row: torch.Tensor            # [T*k] int64
     pos: torch.Tensor                # [T*k] position of pair (t, k) in send order = its row in this rank's return buffer
     send_offsets: List[int]          # [chunks + 1] send-order ranges of the chunks
     recv_offsets: List[int]          # [chunks + 1] row ranges of the chunks in this rank's receive buffers
-    block_sizes: List[torch.Tensor]  # per chunk [world * ec] int64
-    block_expert: List[torch.Tensor] # per chunk [world * ec] int32 (local expert index)
-    meta: torch.Tensor               # [T*k, 2] int64: (send-order position, this rank) of each pair
+    size_per_group: torch.Tensor     # [e_loc] int64 rows of each local expert here
+
+    @property
+    def chunks(self) -> int:
+        return len(self.bounds) - 1
+
+
+def chunk_bounds(e_loc: int, chunks: int) -> List[int]:
+    """Boundaries of `chunks` nearly equal runs of consecutive local experts."""
+    chunks = max(1, min(chunks, e_loc))
+    return [(c * e_loc) // chunks for c in range(chunks + 1)]
 
 
 def make_peer_chunk_plan(topk_idx: torch.Tensor, num_experts: int, group, capacity_rows: int,
-                         chunks: int) -> PeerChunkPlan:
+                         bounds: List[int]) -> PeerChunkPlan:
     from .dispatch import route_plan
 
     world, me = dist.get_world_size(group), dist.get_rank(group)
     assert num_experts % world == 0
     e_loc = num_experts // world
-    assert e_loc % chunks == 0
-    ec = e_loc // chunks
+    chunks = len(bounds) - 1
+    assert bounds[0] == 0 and bounds[-1] == e_loc and all(bounds[c] < bounds[c + 1] for c in range(chunks))
     t, k = topk_idx.shape
     n = t * k
     dev = topk_idx.device
     flat = topk_idx.reshape(-1).to(torch.int64)
-    rank_of = flat // e_loc
-    local = flat - rank_of * e_loc
-    chunk_of = local // ec
-    key = chunk_of * (world * ec) + rank_of * ec + (local - chunk_of * ec)
+    # sort key of global expert (rank r, local l): its place in (chunk of l, r, l) order, so the send
+    # order is chunk-major and inside a chunk grouped by destination rank, then expert
+    b = torch.tensor(bounds, device=dev)
+    l_ids = torch.arange(e_loc, device=dev)
+    chunk_of_l = torch.bucketize(l_ids, b[1:], right=True)
+    width = (b[1:] - b[:-1])[chunk_of_l]                                  # experts in l's chunk
+    key_rl = (world * b[:-1][chunk_of_l])[None, :] + torch.arange(world, device=dev)[:, None] * width[None, :] \
+        + (l_ids - b[:-1][chunk_of_l])[None, :]                            # [r, l]
+    key_of_expert = key_rl.reshape(num_experts)
+    key = key_of_expert[flat.clamp(0, num_experts - 1)]
+    key = torch.where((flat >= 0) & (flat < num_experts), key, torch.full_like(key, -1))
     counts_by_key, send_order, pos = route_plan(key, num_experts)
-    e_ids = torch.arange(num_experts, device=dev)
-    key_of_expert = ((e_ids % e_loc) // ec) * (world * ec) + (e_ids // e_loc) * ec + (e_ids % e_loc) % ec
-    counts = counts_by_key[key_of_expert]                                             # by global expert
-    counts_flat = torch.empty(world * num_experts, dtype=counts.dtype, device=dev)
-    dist.all_gather_into_tensor(counts_flat, counts, group=group)
-    # arrival layout at destination d: blocks (chunk c, source s, expert j of the chunk) in that order
-    by_dest = counts_flat.view(world, world, chunks, ec).permute(1, 2, 0, 3).contiguous()   # [d, c, s, j]
-    flat_blocks = by_dest.view(world, chunks * world * ec)
-    starts = (flat_blocks.cumsum(1) - flat_blocks).view(world, chunks, world, ec)            # [d, c, s, j]
-    dst_block_start = starts[:, :, me, :].reshape(num_experts)                               # (d, c, j) = global expert
-    totals = flat_blocks.sum(1)
-    host = torch.cat([totals, by_dest[me].sum((1, 2)), counts_by_key.view(chunks, world * ec).sum(1)]).cpu()  # one sync
+    counts = counts_by_key[key_of_expert]                                 # by global expert
+    by_dest, dst_block_start, totals = _arrival_layout(counts, group, num_experts)
+    size_per_group = by_dest[me].sum(-1).to(torch.int64).contiguous()     # [e_loc]
+    recv_cum = torch.cat([size_per_group.new_zeros(1), size_per_group.cumsum(0)])[b]           # [chunks + 1]
+    send_cum = torch.cat([counts_by_key.new_zeros(1), counts_by_key.cumsum(0)])[world * b]     # [chunks + 1]
+    host = torch.cat([totals, recv_cum, send_cum]).cpu()                  # the one host sync
     if int(host[:world].max()) > capacity_rows:
         raise RuntimeError(f"a rank would receive {int(host[:world].max())} rows, more than the exchange buffers hold "
                            f"({capacity_rows}); raise capacity_factor")
-    recv_offsets, send_offsets = [0], [0]
-    for c in range(chunks):
-        recv_offsets.append(recv_offsets[-1] + int(host[world + c]))
-        send_offsets.append(send_offsets[-1] + int(host[world + chunks + c]))
+    recv_offsets = [int(v) for v in host[world:world + chunks + 1]]
+    send_offsets = [int(v) for v in host[world + chunks + 1:]]
     send_start_by_key = counts_by_key.cumsum(0) - counts_by_key
-    key_sorted = key[send_order]
-    e_sorted = flat[send_order]
-    idx = torch.arange(n, device=dev)
+    valid = send_order[:send_offsets[-1]]
+    key_sorted = key[valid]
+    e_sorted = flat[valid]
+    idx = torch.arange(valid.numel(), device=dev)
     dst_rank = (e_sorted // e_loc).to(torch.int32)
     dst_row = dst_block_start[e_sorted] + (idx - send_start_by_key[key_sorted])
-    meta = torch.stack([idx, torch.full_like(idx, me)], dim=1).contiguous()
-    return PeerChunkPlan(num_tokens=t, top_k=k, chunks=chunks, token_of_pair=(send_order // k).contiguous(),
+    return PeerChunkPlan(num_tokens=t, top_k=k, bounds=list(bounds), token_of_pair=(valid // k).contiguous(),
                          dst_rank=dst_rank.contiguous(), dst_row=dst_row.contiguous(), pos=pos,
-                         send_offsets=send_offsets, recv_offsets=recv_offsets,
-                         block_sizes=[by_dest[me, c].reshape(-1).to(torch.int64).contiguous() for c in range(chunks)],
-                         block_expert=[(torch.arange(ec, device=dev, dtype=torch.int32) + c * ec).repeat(world).contiguous()
-                                       for c in range(chunks)],
-                         meta=meta)
+                         send_offsets=send_offsets, recv_offsets=recv_offsets, size_per_group=size_per_group)
+
+
+def dispatch_quant_range(x: torch.Tensor, plan: PeerChunkPlan, lo: int, hi: int, rows8: PeerBuffer,
+                         scales: PeerBuffer, meta: PeerBuffer, blocks: int = 0) -> None:
+    """Pairs [lo, hi) of the send order: quantise each pair's token row of ``x`` (bf16 / fp16
+    [T, H]) 1x128 and store the e4m3 row, its scales and the pair's return address at the pair's
+    row of the owning rank's three buffers (one kernel; ``blocks`` > 0 = that many large blocks,
+    for running beside a GEMM)."""
+    assert x.is_cuda and x.is_contiguous() and x.dim() == 2 and x.dtype in (torch.bfloat16, torch.float16)
+    hidden = x.shape[1]
+    assert rows8.local.shape[1] * rows8.local.element_size() == hidden
+    assert scales.local.dtype == torch.float32 and scales.local.shape[1] == hidden // 128
+    assert meta.local.dtype == torch.int64 and meta.local.shape[1] == 2
+    assert rows8.capacity == scales.capacity == meta.capacity
+    with torch.cuda.device(x.device):
+        rc = _lib.load().b200moe_dispatch_quant_rows_multi(
+            x.data_ptr(), plan.token_of_pair.data_ptr(), rows8.bases, scales.bases, meta.bases, plan.dst_rank.data_ptr(),
+            plan.dst_row.data_ptr(), lo, hi - lo, x.shape[0], hidden, 0 if x.dtype == torch.bfloat16 else 1, rows8.world,
+            rows8.capacity, rows8.rank, int(blocks), _lib.stream_ptr(x.device))
+    _lib.check(rc, "b200moe_dispatch_quant_rows_multi")
+
+
+def return_rows(src: torch.Tensor, meta: torch.Tensor, ret: PeerBuffer, blocks: int = 0) -> None:
+    """ret[meta[r, 1]][meta[r, 0]] = src[r] for every row of ``src`` (this rank's results of a
+    chunk) - ``meta`` holds the return addresses that arrived beside the rows."""
+    assert src.is_contiguous() and meta.is_contiguous() and meta.dtype == torch.int64 and meta.shape == (src.shape[0], 2)
+    row_bytes = src.shape[1] * src.element_size()
+    assert row_bytes == ret.local.shape[1] * ret.local.element_size()
+    with torch.cuda.device(src.device):
+        rc = _lib.load().b200moe_return_rows_multi(src.data_ptr(), meta.data_ptr(), ret.bases, src.shape[0], row_bytes,
+                                                   ret.world, ret.capacity, int(blocks), _lib.stream_ptr(src.device))
+    _lib.check(rc, "b200moe_return_rows_multi")
 
 
 def scatter_range(src: torch.Tensor, src_idx: torch.Tensor, dst_rank: torch.Tensor, dst_row: torch.Tensor,
-                  buf: PeerBuffer) -> None:
+                  buf: PeerBuffer, blocks: int = 0) -> None:
     """buf[dst_rank[i]][dst_row[i]] = src[src_idx[i]] for the given index vectors (contiguous tensors
     that the caller keeps alive until the stream has run the kernel)."""
     src2 = src.view(torch.uint8) if src.dtype in (torch.float8_e4m3fn, torch.float8_e5m2) else src
@@ -238,5 +289,6 @@ def scatter_range(src: torch.Tensor, src_idx: torch.Tensor, dst_rank: torch.Tens
     with torch.cuda.device(src2.device):
         rc = _lib.load().b200moe_scatter_rows_multi(src2.data_ptr(), src_idx.data_ptr(), buf.bases, dst_rank.data_ptr(),
                                                     dst_row.data_ptr(), src_idx.numel(), row_bytes, buf.world,
-                                                    buf.capacity, _lib.stream_ptr(src2.device))
+                                                    buf.capacity, src2.shape[0], int(blocks),
+                                                    _lib.stream_ptr(src2.device))
     _lib.check(rc, "b200moe_scatter_rows_multi")
