@@ -15,6 +15,16 @@ Prints ONE JSON line (rank 0).  ``value`` = device-timed TFLOP/s with inputs res
 ``e2e`` = the same metric through the public Python operator with HOST (pinned) inputs and a
 host result, copies inside the timed region.  ``--impl reference`` times the reference's CPU
 path (torch per-group loop, restated in oracle/) on this host's cores on a bounded sample.
+
+Beside the headline the default line carries (``--no-extras`` drops them):
+  roofline.sustained  the same step back to back for >= 2 s (power-capped clocks, sampled)
+  also                the FP8 block-scaled gate+up GEMM (K=4096, N=3072) on the same routing, with a
+                      parity figure against the CPU oracle taken inside the run
+  gpu_reference       N=1 only: the reference's own Triton kernel, autotuned, timed in a child
+                      process on the same sizes when an installed copy sits in baseline/_ref
+  ep                  N>1 only: the expert-parallel FP8 MoE layer (81 920 tokens per rank, top-8) on
+                      the same process group, both transports, with its result compared to the
+                      single-rank layer, and the masked decode step
 """
 
 from __future__ import annotations
@@ -38,6 +48,10 @@ WORKLOADS = {
     # name: (kind, K, N, trans_b)
     "bf16_m_grouped_gate_up": ("m_grouped", 2048, 1536, True),
     "bf16_m_grouped_gate_up_nn": ("m_grouped", 2048, 1536, False),
+    # the reference's own benchmark case (gemm/BF16/m_grouped_gemm_TMA.py:474-493 of the reference):
+    # 128 uniform groups of 5120 rows, N(0,1) data - like for like with its README / its B200 run
+    "bf16_m_grouped_uniform": ("m_grouped", 2048, 1536, True),
+    "bf16_m_grouped_uniform_down": ("m_grouped", 768, 2048, True),
     "bf16_m_grouped_down": ("m_grouped", 768, 2048, True),
     "bf16_k_grouped_wgrad": ("k_grouped", 2048, 768, False),
     "fp8_block_m_grouped_gate_up": ("fp8_block", 4096, 3072, True),
@@ -62,6 +76,9 @@ TOTAL_ROWS = 655360
 NUM_EXPERTS = 128
 ROUTING_SEED = 2026
 ROWS_USED = [TOTAL_ROWS]
+UNIFORM_WORKLOADS = ("bf16_m_grouped_uniform", "bf16_m_grouped_uniform_down")
+UNIFORM = [False]
+DATA_SCALE = [0.02]  # std of the 16-bit GEMM operands; the uniform workloads use the reference's N(0,1)
 
 
 def measured_peaks():
@@ -148,6 +165,8 @@ def rank_sizes(world: int, rank: int, total_rows: int = TOTAL_ROWS, experts: int
     """Row counts of the experts this rank owns.  Every rank keeps `total_rows` routed rows over
     its experts/world experts (routing seed varies with the rank)."""
     g_local = max(experts // world, 1)
+    if UNIFORM[0]:
+        return torch.full((g_local,), total_rows // g_local, dtype=torch.int64)
     gen = torch.Generator().manual_seed(ROUTING_SEED + rank)
     logits = 0.5 * torch.randn(g_local, generator=gen)
     draws = torch.multinomial(torch.softmax(logits, dim=0), total_rows, replacement=True, generator=gen)
@@ -179,8 +198,8 @@ def make_inputs(kind, k, n, trans_b, sizes, device, seed):
         return out
 
     if kind == "m_grouped":
-        a = randn((m, k), 0.02)
-        b = randn((g, n, k) if trans_b else (g, k, n), 0.02, chunk_rows=8)
+        a = randn((m, k), DATA_SCALE[0])
+        b = randn((g, n, k) if trans_b else (g, k, n), DATA_SCALE[0], chunk_rows=8)
         return {"a": a, "b": b}
     if kind == "k_grouped":
         return {"a": randn((m, k), 0.02), "b": randn((m, n), 0.02)}
@@ -225,8 +244,9 @@ def algorithmic_work(kind, k, n, sizes):
     raise ValueError(kind)
 
 
-EP_CHUNKS = 4  # set from --ep-chunks
+EP_CHUNKS = 8  # set from --ep-chunks
 EP_TRANSPORT = "p2p"  # set from --ep-transport
+EP_COMM_SMS = 16  # set from --ep-comm-sms
 
 
 def build_step(kind, k, n, trans_b, sizes_dev, inp):
@@ -295,7 +315,7 @@ def build_step(kind, k, n, trans_b, sizes_dev, inp):
         rank = dist.get_rank() if dist.is_initialized() else 0
         dev = inp["w13"].device
         layer = Fp8MoELayer(inp.pop("w13"), inp.pop("w2"), NUM_EXPERTS if kind == "moe_ep" else sizes_dev.numel(), group,
-                            chunks=EP_CHUNKS, transport=EP_TRANSPORT if kind == "moe_ep" else "nccl",
+                            chunks=EP_CHUNKS, comm_sms=EP_COMM_SMS, transport=EP_TRANSPORT if kind == "moe_ep" else "nccl",
                             tokens_per_rank=ROWS_USED[0] // TOP_K, top_k=TOP_K)
         inp["layer"] = layer
         gen = torch.Generator(device=dev).manual_seed(500 + rank)
@@ -304,8 +324,9 @@ def build_step(kind, k, n, trans_b, sizes_dev, inp):
             x = torch.randn(tokens, k, device=dev, generator=gen, dtype=torch.bfloat16)
             idx, w = synthetic_routing(tokens, NUM_EXPERTS, TOP_K, seed=ROUTING_SEED + rank, device=dev)
             inp.update(x=x, idx=idx, w=w)
-            # launches per step: 1 act quantiser + 2 GEMMs + 1 SwiGLU quantiser (ours); permutes are torch
-            return (lambda: inp.__setitem__("c", layer.forward(x, idx, w))), 4
+            # kernels of this library per step on one rank: routing plan (3), activation quantiser, two row
+            # gathers, two GEMMs, SwiGLU quantiser, weighted combine (more with several ranks: per-chunk movers)
+            return (lambda: inp.__setitem__("c", layer.forward(x, idx, w))), 10
         e_loc = sizes_dev.numel()
         x = torch.randn(e_loc * DECODE_M_MAX, k, device=dev, generator=gen, dtype=torch.bfloat16)
         x8, xs = per_token_cast_to_fp8(x)
@@ -393,16 +414,264 @@ def unit_of(kind):
     return ("TFLOP/s", 1e12) if kind not in ("quant_act", "quant_trans") else ("GB/s", 1e9)
 
 
-def run_reference(args):
-    rank, world, _ = dist_env()
-    if rank != 0:
-        return
-    # torchrun exports OMP_NUM_THREADS=1 to its workers; the reference arm is the only CPU work of
-    # the job (the other ranks have exited), so give it every core the process may run on
+def use_all_host_threads():
+    """torchrun exports OMP_NUM_THREADS=1 to its workers; the CPU legs are the only host work while
+    they run, so give them every core the process may run on."""
     try:
         torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
     except (AttributeError, OSError):
         torch.set_num_threads(max(1, os.cpu_count() or 1))
+
+
+def timed_steps(step, steps, warmup):
+    """W untimed + K timed steps on the current stream, one CUDA-event pair per step (ms each)."""
+    for _ in range(warmup):
+        step()
+    torch.cuda.synchronize()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    for s_ev, e_ev in evs:
+        s_ev.record()
+        step()
+        e_ev.record()
+    torch.cuda.synchronize()
+    return [a.elapsed_time(b) for a, b in evs]
+
+
+def sustained_leg(step, work, div, burst_ms, local, peaks, seconds):
+    """The same step back to back for >= `seconds` (no gaps, no host sync inside): long enough for
+    the power cap to pull the SM clock to its sustained value and for nvidia-smi to see it."""
+    n = max(10, int(seconds * 1e3 / max(burst_ms, 1e-3) * 1.15) + 1)
+    sampler = ClockSampler(local)
+    sampler.start()
+    time.sleep(0.15)
+    torch.cuda.synchronize()
+    s_ev, e_ev = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.time()
+    s_ev.record()
+    for _ in range(n):
+        step()
+    e_ev.record()
+    torch.cuda.synchronize()
+    t1 = time.time()
+    clocks = sampler.stop(t0, t1)
+    ms = s_ev.elapsed_time(e_ev) / n
+    rate = work / (ms * 1e-3) / div
+    out = {"steps": n, "seconds": (t1 - t0), "ms_per_step": ms, "tflops": rate,
+           "sm_mhz_median": clocks.get("sm_mhz"), "power_w": clocks.get("power_w"),
+           "samples_in_region": clocks.get("samples_in_timed_region"), "reasons": clocks.get("reasons")}
+    if peaks.get("bf16_sustained"):
+        out["frac"] = rate / peaks["bf16_sustained"]
+        out["peak"] = peaks["bf16_sustained"]
+        out["peak_source"] = f"{peaks['source']} cuBLAS bf16 sustained"
+    if clocks.get("sm_mhz"):
+        out["tflops_per_ghz"] = rate / (clocks["sm_mhz"] / 1e3)
+    return out
+
+
+def also_fp8_block(sizes, sizes_dev, dev, rank, peaks, steps, warmup):
+    """The other half of the metric: the block-scaled FP8 gate+up GEMM (K=4096, N=3072) on the same
+    routing, device-timed, with a parity figure taken inside the run: for EVERY group 8 rows (first,
+    middle, last) x the first and last 128 output columns against the CPU oracle."""
+    import oracle as O
+
+    name = "fp8_block_m_grouped_gate_up"
+    kind, k, n, trans_b = WORKLOADS[name]
+    inp = make_inputs(kind, k, n, trans_b, sizes, dev, seed=300 + rank)
+    step, _ = build_step(kind, k, n, trans_b, sizes_dev, inp)
+    per = timed_steps(step, steps, max(warmup, 3))
+    work, _ = algorithmic_work(kind, k, n, sizes)
+    mean_ms = statistics.mean(per)
+    rate = work / (mean_ms * 1e-3) / 1e12
+    starts = (torch.cumsum(sizes, 0) - sizes).tolist()
+    num = den = 0.0
+    checked = 0
+    cols = [(0, 128), (n - 128, n)]
+    for g, (s0, sz) in enumerate(zip(starts, sizes.tolist())):
+        if sz <= 0:
+            continue
+        pick = sorted({0, 1, 2, sz // 2, sz // 2 + 1, sz - 3, sz - 2, sz - 1} & set(range(sz)))
+        rows = torch.tensor([s0 + r for r in pick], device=dev)
+        a8, a_s, got = inp["a8"][rows].cpu(), inp["a_s"][rows].cpu(), inp["c"][rows].cpu().float()
+        for c0, c1 in cols:
+            ref = O.fp8_block_m_grouped_ref(a8, a_s, inp["b8"][g:g + 1, c0:c1].cpu(),
+                                            inp["b_s"][g:g + 1, c0 // 128:c1 // 128].cpu(), [len(pick)]).float()
+            num += float((got[:, c0:c1] - ref).abs().sum())
+            den += float(ref.abs().sum())
+        checked += 1
+    peak = 2.0 * peaks["bf16"]
+    return {"workload": name, "K": k, "N": n, "dtype": "fp8_e4m3", "steps": steps, "ms_per_step": mean_ms,
+            "min_ms": min(per), "value": rate, "unit": "TFLOP/s",
+            "roofline": {"bound": "tensor", "achieved": rate, "peak": peak, "frac": rate / peak,
+                         "peak_source": f"{peaks['source']} cuBLAS bf16 burst x2 (no fp8 peak measured)",
+                         "frac_of_nominal": rate / 4500.0},
+            "parity": {"rdiff_vs_oracle": num / max(den, 1e-30), "groups_checked": checked, "rows_per_group": 8,
+                       "columns": "first and last 128", "tolerance": 2e-3}}
+
+
+REFERENCE_GPU_CHILD = r"""
+import json, sys, torch
+sys.path.insert(0, sys.argv[1])
+sizes = json.loads(sys.argv[2]); k = int(sys.argv[3]); n = int(sys.argv[4]); scale = float(sys.argv[5])
+from gemm.BF16.m_grouped_gemm_TMA import _build_m_grouped_metadata, _m_grouped_gemm_launch
+dev = torch.device('cuda', 0)
+gen = torch.Generator(device=dev).manual_seed(100)
+sz = torch.tensor(sizes, device=dev, dtype=torch.int64)
+m = int(sum(sizes))
+a = torch.empty(m, k, device=dev, dtype=torch.bfloat16)
+for r in range(0, m, 65536):
+    rows = min(65536, m - r)
+    a[r:r + rows] = (torch.randn(rows, k, device=dev, generator=gen) * scale).bfloat16()
+b = (torch.randn(len(sizes), n, k, device=dev, generator=gen) * scale).bfloat16()
+c = torch.empty(m, n, device=dev, dtype=torch.bfloat16)
+meta = _build_m_grouped_metadata(sz)
+fn = lambda: _m_grouped_gemm_launch(a, b, c, sz, True, -1, metadata=meta, use_fixed_sm90_config=False)
+for _ in range(5):
+    fn()
+torch.cuda.synchronize()
+ts = []
+for _ in range(10):
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record(); fn(); e.record(); e.synchronize()
+    ts.append(s.elapsed_time(e))
+g0 = sizes[0]
+ref = (a[:min(g0, 256)].float() @ b[0].float().t())
+err = ((c[:min(g0, 256)].float() - ref).abs().sum() / ref.abs().sum()).item()
+print('REFJSON ' + json.dumps({'min_ms': min(ts), 'mean_ms': sum(ts) / len(ts), 'rdiff_group0_vs_fp32': err}))
+"""
+
+
+def gpu_reference_leg(sizes, k, n, work):
+    """The reference's own Triton kernel (unmodified, autotuned) on the same sizes and data
+    distribution, in a child process (its module registers the same torch operator name as this
+    package, so the two cannot share an interpreter), metadata prebuilt as in its benchmark main."""
+    ref_root = ROOT / "baseline" / "_ref"
+    if not (ref_root / "gemm" / "BF16" / "m_grouped_gemm_TMA.py").exists():
+        return {"unavailable": "no installed copy of the reference under baseline/_ref"}
+    try:
+        r = subprocess.run([sys.executable, "-c", REFERENCE_GPU_CHILD, str(ref_root), json.dumps([int(v) for v in sizes.tolist()]),
+                            str(k), str(n), str(DATA_SCALE[0])], stdout=subprocess.PIPE, stderr=subprocess.PIPE,
+                           text=True, timeout=420)
+    except Exception as exc:  # timeout, missing interpreter
+        return {"unavailable": f"{type(exc).__name__}: {exc}"[:300]}
+    for line in r.stdout.splitlines():
+        if line.startswith("REFJSON "):
+            d = json.loads(line[8:])
+            d.update(impl="reference Triton kernel m_grouped_gemm_bKmajor_kernel (baseline/_ref), autotuned; 5 warm-ups, 10 timed",
+                     value=work / (d["mean_ms"] * 1e-3) / 1e12, value_min_time=work / (d["min_ms"] * 1e-3) / 1e12,
+                     unit="TFLOP/s")
+            return d
+    return {"unavailable": ("rc=%d: " % r.returncode + (r.stderr or r.stdout)[-300:]).replace("\n", " | ")}
+
+
+def ep_leg(dev, rank, world, steps, warmup, chunks, comm_sms):
+    """The expert-parallel FP8 MoE layer of the benchmark configuration on this process group:
+    128 experts split over the ranks, 81 920 tokens x hidden 4096 per rank, top-8, intermediate
+    1536; dispatch and combine over NVLink inside every step.  Both transports are timed (max over
+    ranks); `gemm_only_ms` is the same rank's expert GEMMs + SwiGLU quantiser on the rows it
+    received, with no exchange and every SM.  Each transport's result is first compared with the
+    single-rank layer on a small step (must be identical).  Ends with the masked decode step."""
+    import torch.distributed as dist
+
+    from triton_grouped_gemm_b200 import _lib
+    from triton_grouped_gemm_b200.ep.moe_layer import Fp8MoELayer, synthetic_routing
+
+    group = dist.group.WORLD
+    hidden, inter, tokens = 4096, 1536, 81920
+    e_loc = NUM_EXPERTS // world
+    res = {"tokens_per_rank": tokens, "top_k": TOP_K, "hidden": hidden, "intermediate": inter,
+           "experts_per_rank": e_loc, "steps": steps, "transports": {}}
+
+    def max_over_ranks(v):
+        t = torch.tensor([v], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t[0])
+
+    # ---- parity: a small layer against the single-rank layer, per transport (as the 2-GPU test does)
+    se, sh, si, sk, st = 32, 512, 256, 4, 1024
+    g0 = torch.Generator().manual_seed(0)
+    sw13 = (torch.randn(se, 2 * si, sh, generator=g0) * 0.05).bfloat16()
+    sw2 = (torch.randn(se, sh, si, generator=g0) * 0.05).bfloat16()
+    sl = se // world
+    full = Fp8MoELayer(sw13.to(dev), sw2.to(dev), se, None)
+    sx = torch.randn(st, sh, generator=torch.Generator().manual_seed(100 + rank)).bfloat16().to(dev)
+    sidx, sw = synthetic_routing(st, se, sk, seed=200 + rank, device=dev)
+    ref = full.forward(sx, sidx, sw)
+    small_rdiff = {}
+    for transport, ch in (("p2p", min(chunks, sl)), ("nccl", min(4, sl))):
+        lay = Fp8MoELayer(sw13[rank * sl:(rank + 1) * sl].to(dev), sw2[rank * sl:(rank + 1) * sl].to(dev), se, group,
+                          transport=transport, chunks=ch, tokens_per_rank=st, top_k=sk, capacity_factor=2.0)
+        out = lay.forward(sx, sidx, sw)
+        small_rdiff[transport] = max_over_ranks(((out.float() - ref.float()).abs().sum() / ref.float().abs().sum()).item())
+        lay.close()
+    del full
+
+    # ---- the benchmark-size layer
+    gen = torch.Generator(device=dev).manual_seed(700 + rank)
+
+    def randn(shape, scale):
+        out = torch.empty(shape, device=dev, dtype=torch.bfloat16)
+        for i in range(shape[0]):
+            out[i] = (torch.randn(shape[1:], device=dev, generator=gen) * scale).bfloat16()
+        return out
+
+    w13, w2 = randn((e_loc, 2 * inter, hidden), 0.02), randn((e_loc, hidden, inter), 0.02)
+    x = torch.randn(tokens, hidden, device=dev, generator=gen, dtype=torch.bfloat16)
+    idx, w = synthetic_routing(tokens, NUM_EXPERTS, TOP_K, seed=ROUTING_SEED + rank, device=dev)
+    work_rank = 2.0 * tokens * TOP_K * (2 * inter * hidden + hidden * inter)
+    for transport, ch in (("p2p", chunks), ("nccl", 4)):
+        layer = Fp8MoELayer(w13, w2, NUM_EXPERTS, group, chunks=ch, comm_sms=comm_sms, transport=transport,
+                            tokens_per_rank=tokens, top_k=TOP_K)
+        dist.barrier()
+        per = timed_steps(lambda: layer.forward(x, idx, w), steps, max(warmup, 3))
+        ms = max_over_ranks(statistics.mean(per))
+        entry = {"chunks": layer.chunks, "comm_sms": comm_sms, "ms_per_step": ms,
+                 "tflops": work_rank * world / (ms * 1e-3) / 1e12, "rdiff_vs_single_rank": small_rdiff[transport]}
+        if transport == "p2p":
+            # the same rows without any exchange: this rank's expert GEMMs + SwiGLU quantiser, all SMs
+            rows, sizes = layer.last_rows
+            a8 = layer.recv8.local[:rows].view(torch.float8_e4m3fn)
+            per_g = timed_steps(lambda: layer.experts(a8, layer.recvs.local[:rows], sizes, out=layer.ybuf.local[:rows]),
+                                steps, 3)
+            gemm_ms = max_over_ranks(statistics.mean(per_g))
+            entry.update(gemm_only_ms=gemm_ms, efficiency=gemm_ms / ms, exposed_comm_ms=ms - gemm_ms,
+                         rows_received_rank0=int(rows))
+        st_word = torch.tensor([_lib.device_status()], device=dev, dtype=torch.int64)
+        dist.all_reduce(st_word, op=dist.ReduceOp.MAX)
+        entry["device_status"] = int(st_word[0])
+        res["transports"][transport] = entry
+        if transport == "p2p":
+            res.update(ms_per_step=ms, tflops=entry["tflops"], gemm_only_ms=entry["gemm_only_ms"],
+                       efficiency=entry["efficiency"], exposed_comm_ms=entry["exposed_comm_ms"],
+                       rdiff_vs_single_rank=entry["rdiff_vs_single_rank"], device_status=entry["device_status"],
+                       transport="p2p")
+            # ---- decode: masked layout [experts per rank, 256 slots, hidden], valid counts uniform in [0, 256]
+            from triton_grouped_gemm_b200.quant.per_block_cast import per_token_cast_to_fp8
+
+            masked = torch.randint(0, DECODE_M_MAX + 1, (e_loc,), generator=torch.Generator().manual_seed(ROUTING_SEED + rank),
+                                   dtype=torch.int64)
+            xd = torch.randn(e_loc * DECODE_M_MAX, hidden, device=dev, generator=gen, dtype=torch.bfloat16)
+            x8, xs = per_token_cast_to_fp8(xd)
+            outd = torch.zeros(e_loc * DECODE_M_MAX, hidden, device=dev, dtype=torch.bfloat16)
+            md = masked.to(dev)
+            per_d = timed_steps(lambda: layer.decode(x8, xs, md, DECODE_M_MAX, out=outd), max(steps, 10), 3)
+            dms = max_over_ranks(statistics.mean(per_d))
+            valid = torch.tensor([float(masked.sum())], device=dev, dtype=torch.float64)
+            dist.all_reduce(valid)
+            res["decode"] = {"layout": [e_loc, DECODE_M_MAX, hidden], "ms_per_step": dms,
+                             "valid_rows_all_ranks": int(valid[0]),
+                             "tflops": 2.0 * float(valid[0]) * (2 * inter * hidden + hidden * inter) / (dms * 1e-3) / 1e12,
+                             "weights_gb_per_rank": e_loc * 3 * inter * hidden / 1e9,
+                             "note": "bound by streaming the expert weights (fp8) from HBM, not by the tensor cores"}
+        layer.close()
+        del layer
+    return res
+
+
+def run_reference(args):
+    rank, world, _ = dist_env()
+    if rank != 0:
+        return
+    use_all_host_threads()  # the other ranks have exited: this is the only CPU work of the job
     kind, k, n, trans_b = WORKLOADS[args.workload]
     sizes = (moe_sizes(kind, max(args.gpus, 1), 0, args.rows) if kind in ("moe_ep", "moe_decode")
              else rank_sizes(max(args.gpus, 1), 0, args.rows, args.experts))
@@ -449,9 +718,15 @@ def dtype_name(kind):
 
 
 def config_of(name, kind, k, n, trans_b, sizes, gpus):
+    if kind == "moe_ep" and gpus > 1:
+        partition = (f"experts split {NUM_EXPERTS}/{gpus} per GPU; every step dispatches fp8 rows to the expert owners and "
+                     f"returns bf16 results over NVLink (transport {EP_TRANSPORT}, {EP_CHUNKS} chunks)")
+    elif kind in ("moe_ep", "moe_decode"):
+        partition = f"experts split {NUM_EXPERTS}/{gpus} per GPU; no exchange in this workload at this GPU count"
+    else:
+        partition = f"experts split {NUM_EXPERTS}/{gpus} per GPU, no data-path collective"
     return {"workload": name, "groups_per_gpu": int(sizes.numel()), "routed_rows_per_gpu": int(ROWS_USED[0]),
-            "padded_rows_rank0": int(sizes.sum()), "K": k, "N": n, "trans_b": trans_b,
-            "partition": f"experts split {NUM_EXPERTS}/{gpus} per GPU, no data-path collective",
+            "padded_rows_rank0": int(sizes.sum()), "K": k, "N": n, "trans_b": trans_b, "partition": partition,
             "l2": "inputs (>2.7 GB per step) exceed the 126 MB L2; no explicit flush"}
 
 
@@ -475,6 +750,9 @@ def run_b200(args):
 
     _lib.load()
     kind, k, n, trans_b = WORKLOADS[args.workload]
+    if args.workload in UNIFORM_WORKLOADS:
+        UNIFORM[0] = True
+        DATA_SCALE[0] = 1.0
     sizes = (moe_sizes(kind, world, rank, args.rows) if kind in ("moe_ep", "moe_decode")
              else rank_sizes(world, rank, args.rows, args.experts))
     if kind == "masked":  # valid rows per 4096-row slot, ~1/4 full, every fifth slot empty
@@ -482,9 +760,10 @@ def run_b200(args):
         sizes = torch.randint(0, 2049, (sizes.numel(),), generator=gen_m, dtype=torch.int64)
         sizes[::5] = 0
     sizes_dev = sizes.to(dev)
-    global EP_CHUNKS, EP_TRANSPORT
+    global EP_CHUNKS, EP_TRANSPORT, EP_COMM_SMS
     EP_CHUNKS = args.ep_chunks
     EP_TRANSPORT = args.ep_transport
+    EP_COMM_SMS = args.ep_comm_sms
     if args.cta_pair != -1:
         from triton_grouped_gemm_b200 import _lib
 
@@ -538,6 +817,12 @@ def run_b200(args):
         total_ms_max, work_all = total_ms, work
     ms_per_step = total_ms_max / args.steps
     value = work_all / (ms_per_step * 1e-3) / div
+    extras = not (args.no_extras or args.profile)
+    sustained = None
+    if extras and args.sustain_seconds > 0 and kind not in ("moe_ep", "moe_decode"):
+        barrier()
+        sustained = sustained_leg(step, work, div, statistics.mean(per_step), local, measured_peaks(), args.sustain_seconds)
+        barrier()
 
     # ---- end to end through the public operator with host (pinned) buffers
     if args.profile:
@@ -584,6 +869,7 @@ def run_b200(args):
                     "min_ms": min(per_step), "mean_ms": statistics.mean(per_step)}
         cpu = None
         if not args.no_cpu_baseline:
+            use_all_host_threads()  # under torchrun OMP_NUM_THREADS is 1; the other ranks idle at a barrier meanwhile
             fn, cwork, desc = cpu_reference_step(kind, k, n, trans_b, sizes, 0.6e12 if unit == "TFLOP/s" else 1.5e9)
             fn()
             best = float("inf")
@@ -606,7 +892,41 @@ def run_b200(args):
                     "steps": e2e["steps"], "ms_per_step": e2e["ms"]},
             "gpu_launches": launches * args.steps, "clocks": clocks, "wall_s_timed_region": t_wall,
         }
+        if sustained is not None and unit == "TFLOP/s":
+            line["roofline"]["sustained"] = sustained
+        elif sustained is not None:
+            sustained["gbs"] = sustained.pop("tflops")
+            sustained.pop("frac", None), sustained.pop("peak", None), sustained.pop("peak_source", None)
+            sustained.pop("tflops_per_ghz", None)
+            line["roofline"]["sustained"] = sustained
+    # ---- the rest of the metric, measured in the same run
+    also = gpu_ref = ep = None
+    layer = inp.get("layer")
+    if extras and args.workload == "bf16_m_grouped_gate_up":
+        inp.clear()
+        step = None  # the closure holds the operands
+        torch.cuda.empty_cache()
+        if use_dist:
+            dist.barrier()
+        also = also_fp8_block(sizes, sizes_dev, dev, rank, measured_peaks(), min(args.steps, 10), 3)
+        torch.cuda.empty_cache()
+        if not use_dist and rank == 0:
+            gpu_ref = gpu_reference_leg(sizes, k, n, work)
+        if use_dist:
+            dist.barrier()
+            ep = ep_leg(dev, rank, world, min(args.steps, 8), 3, args.ep_chunks, args.ep_comm_sms)
+    if rank == 0:
+        if also is not None:
+            line["also"] = also
+        if gpu_ref is not None:
+            line["gpu_reference"] = gpu_ref
+            if "value" in gpu_ref:
+                line["gpu_reference"]["this_build_over_reference"] = value / gpu_ref["value"]
+        if ep is not None:
+            line["ep"] = ep
         print(json.dumps(line), flush=True)
+    if layer is not None:
+        layer.close()  # collective; releases the peer-memory buffers before the process group goes away
     if use_dist:
         dist.barrier()
         dist.destroy_process_group()
@@ -741,13 +1061,19 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--rows", type=int, default=TOTAL_ROWS, help="routed rows per GPU (default: the benchmark's 655360)")
     ap.add_argument("--experts", type=int, default=NUM_EXPERTS, help="experts over all GPUs (default 128)")
-    ap.add_argument("--ep-chunks", type=int, default=4,
+    ap.add_argument("--ep-chunks", type=int, default=8,
                     help="moe_ep_fp8 with more than one GPU: groups of local experts whose exchange overlaps the GEMMs")
     ap.add_argument("--ep-transport", choices=["p2p", "nccl"], default="p2p",
                     help="moe_ep_fp8 with more than one GPU: rows move by kernels over peer memory (p2p) or by "
                          "NCCL all-to-all (nccl)")
     ap.add_argument("--cta-pair", type=int, default=-1, choices=[-1, 0, 1],
                     help="kernel form: -1 chosen by problem size (default), 0 single-CTA tiles, 1 CTA pairs")
+    ap.add_argument("--ep-comm-sms", type=int, default=16,
+                    help="moe_ep_fp8 with more than one GPU: SMs the expert GEMMs leave to the row movers / collectives")
+    ap.add_argument("--sustain-seconds", type=float, default=2.0,
+                    help="length of the back-to-back (sustained) leg after the timed steps; 0 = skip")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="only the headline measurement: no sustained leg, no FP8 / reference-kernel / expert-parallel legs")
     ap.add_argument("--profile", action="store_true",
                     help="for ncu captures: honour --warmup as given, skip the host-buffer and CPU legs")
     args = ap.parse_args()

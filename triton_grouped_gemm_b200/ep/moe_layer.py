@@ -139,6 +139,7 @@ class Fp8MoELayer:
         scatter_rows(plan, xs, self.recvs)
         dist.all_reduce(self._flag, group=self.group)       # every rank's rows have landed everywhere
         r = plan.rows_here
+        self.last_rows = (r, plan.size_per_group)   # rows received this step and their split over the experts
         self.experts(self.recv8.local[:r].view(torch.float8_e4m3fn), self.recvs.local[:r], plan.size_per_group,
                      out=self.ybuf.local[:r])
         dist.all_reduce(self._flag, group=self.group)       # every rank's results are written
@@ -211,6 +212,7 @@ class Fp8MoELayer:
         dev = x.device
         plan = make_peer_chunk_plan(topk_idx, self.num_experts, self.group, self.recv8.capacity, self.bounds)
         assert plan.pos.numel() <= self.ret.capacity, "more (token, k) pairs than the return buffer holds"
+        self.last_rows = (plan.recv_offsets[-1], plan.size_per_group)
         chunks = plan.chunks
         sms = lib.b200gemm_sm_count()
         gemm_sms = sms - self.comm_sms if 0 < self.comm_sms < sms - 2 else -1
