@@ -59,6 +59,8 @@ WORKLOADS = {
     # FP8 with per-row x per-channel scales (e4m3 x e4m3), M-grouped and K-grouped (tokens padded to 128)
     "fp8_rowcol_m_grouped": ("fp8_rowcol", 4096, 3072, True),
     "fp8_rowcol_k_grouped": ("fp8_rowcol_k", 2048, 768, False),
+    # FP8 weight gradient: both operands from the transposing 128x128 quantiser, 2048 x 768 per expert
+    "fp8_block_k_grouped_wgrad": ("fp8_block_k", 2048, 768, False),
     # masked layout: 128 slots of 4096 rows, ~1/4 of them valid (the reference's masked benchmark)
     "bf16_masked_m_grouped": ("masked", 2048, 1536, True),
     "quant_act_1x128": ("quant_act", 4096, 0, True),
@@ -218,6 +220,8 @@ def make_inputs(kind, k, n, trans_b, sizes, device, seed):
         y8 = (randn((n, m), 50.0, chunk_rows=256).float().clamp(-400, 400)).to(torch.float8_e4m3fn)
         return {"x8": x8, "y8": y8, "xs": (torch.rand(g, k, device=device, generator=gen) * 0.01 + 1e-3).t(),
                 "ys": (torch.rand(g, n, device=device, generator=gen) * 0.01 + 1e-3).t()}
+    if kind == "fp8_block_k":
+        return {"a": randn((m, k), 1.0), "dy": randn((m, n), 0.1)}
     if kind == "masked":
         e = 4096
         return {"a": randn((g * e, k), 0.02), "b": randn((g, n, k), 0.02, chunk_rows=8)}
@@ -229,7 +233,7 @@ def make_inputs(kind, k, n, trans_b, sizes, device, seed):
 
 def algorithmic_work(kind, k, n, sizes):
     rows = int(sizes.sum())
-    if kind in ("m_grouped", "fp8_block", "fp8_rowcol", "fp8_rowcol_k", "masked"):
+    if kind in ("m_grouped", "fp8_block", "fp8_rowcol", "fp8_rowcol_k", "masked", "fp8_block_k"):
         return 2.0 * rows * n * k, "flop"
     if kind == "k_grouped":
         return 2.0 * rows * n * k, "flop"  # M_DIM=k, N_DIM=n, K_total=rows
@@ -292,6 +296,16 @@ def build_step(kind, k, n, trans_b, sizes_dev, inp):
         x8, y8, xs, ys = inp["x8"], inp["y8"], inp["xs"], inp["ys"]
         s32 = sizes_dev.to(torch.int32)
         return (lambda: inp.__setitem__("c", matmul(x8, xs, y8, ys, s32, k, n, x8.shape[1], s32.numel()))), 1
+    if kind == "fp8_block_k":
+        from triton_grouped_gemm_b200.gemm.FP8.k_grouped_gemm_block_scaled import k_grouped_fp8_block_scaled
+        from triton_grouped_gemm_b200.quant.trans_per_block_quant_expand_128x import trans_per_block_quant_expand_128x
+
+        if "aq" not in inp:  # quantise once, outside the timed region (the quantiser has its own workload)
+            aq, a_s, padded = trans_per_block_quant_expand_128x(inp.pop("a"), sizes_dev)
+            gq, g_s, _ = trans_per_block_quant_expand_128x(inp.pop("dy"), sizes_dev)
+            inp.update(aq=aq, a_s=a_s, gq=gq, g_s=g_s, padded=padded)
+        aq, a_s, gq, g_s, padded = inp["aq"], inp["a_s"], inp["gq"], inp["g_s"], inp["padded"]
+        return (lambda: inp.__setitem__("c", k_grouped_fp8_block_scaled((aq, a_s), (gq, g_s), padded))), 1
     if kind == "masked":
         from triton_grouped_gemm_b200.gemm.BF16.m_grouped_gemm_masked_TMA import m_grouped_gemm_masked
 
@@ -379,6 +393,12 @@ def cpu_reference_step(kind, k, n, trans_b, sizes, budget_work, seed=7):
         y8 = (torch.randn(n, m, generator=gen) * 50).clamp(-400, 400).to(torch.float8_e4m3fn)
         xs, ys = (torch.rand(g, k, generator=gen) * 0.01 + 1e-3).t(), (torch.rand(g, n, generator=gen) * 0.01 + 1e-3).t()
         fn = lambda: O.fp8_rowcol_k_grouped_ref(x8, xs, y8, ys, ps, k, n, g)  # noqa: E731
+    elif kind == "fp8_block_k":
+        a = torch.randn(m, k, generator=gen).bfloat16()
+        dy = (torch.randn(m, n, generator=gen) * 0.1).bfloat16()
+        aq, a_s, pad = O.trans_quant_expand_ref(a, ps)
+        gq, g_s, _ = O.trans_quant_expand_ref(dy, ps)
+        fn = lambda: O.fp8_block_k_grouped_ref(aq, a_s, gq, g_s, pad)  # noqa: E731
     elif kind == "masked":
         e = 4096
         a = (torch.randn(g * e, k, generator=gen) * 0.02).bfloat16()
@@ -563,7 +583,21 @@ def gpu_reference_leg(sizes, k, n, work):
     return {"unavailable": ("rc=%d: " % r.returncode + (r.stderr or r.stdout)[-300:]).replace("\n", " | ")}
 
 
-def ep_leg(dev, rank, world, steps, warmup, chunks, comm_sms):
+def summarise_phases(marks, chunks):
+    """[(phase, ms since start)] of one traced step -> per-chunk durations and the exposed head / tail."""
+    t = dict(marks)
+    out = {"plan_ms": t.get("plan_done", 0.0),
+           "head_ms_until_first_gemm": t.get("gemm0>", 0.0), "step_ms": t.get("end", 0.0),
+           "tail_ms_after_last_gemm": t.get("end", 0.0) - t.get(f"gemm{chunks - 1}<", 0.0),
+           "final_combine_ms": t.get("end", 0.0) - t.get("returned_everywhere", 0.0)}
+    for name in ("dispatch", "gemm", "return"):
+        out[name + "_ms"] = [round(t[f"{name}{c}<"] - t[f"{name}{c}>"], 3) for c in range(chunks) if f"{name}{c}<" in t]
+    out["gemm_wait_ms"] = [round(t[f"gemm{c}>"] - (t[f"gemm{c - 1}<"] if c else t.get("plan_done", 0.0)), 3)
+                           for c in range(chunks) if f"gemm{c}>" in t]
+    return out
+
+
+def ep_leg(dev, rank, world, steps, warmup, chunks, comm_sms, qod=False, return_path="copy"):
     """The expert-parallel FP8 MoE layer of the benchmark configuration on this process group:
     128 experts split over the ranks, 81 920 tokens x hidden 4096 per rank, top-8, intermediate
     1536; dispatch and combine over NVLink inside every step.  Both transports are timed (max over
@@ -599,7 +633,8 @@ def ep_leg(dev, rank, world, steps, warmup, chunks, comm_sms):
     small_rdiff = {}
     for transport, ch in (("p2p", min(chunks, sl)), ("nccl", min(4, sl))):
         lay = Fp8MoELayer(sw13[rank * sl:(rank + 1) * sl].to(dev), sw2[rank * sl:(rank + 1) * sl].to(dev), se, group,
-                          transport=transport, chunks=ch, tokens_per_rank=st, top_k=sk, capacity_factor=2.0)
+                          transport=transport, chunks=ch, tokens_per_rank=st, top_k=sk, capacity_factor=2.0,
+                          quantise_on_dispatch=qod, return_path=return_path)
         out = lay.forward(sx, sidx, sw)
         small_rdiff[transport] = max_over_ranks(((out.float() - ref.float()).abs().sum() / ref.float().abs().sum()).item())
         lay.close()
@@ -620,11 +655,13 @@ def ep_leg(dev, rank, world, steps, warmup, chunks, comm_sms):
     work_rank = 2.0 * tokens * TOP_K * (2 * inter * hidden + hidden * inter)
     for transport, ch in (("p2p", chunks), ("nccl", 4)):
         layer = Fp8MoELayer(w13, w2, NUM_EXPERTS, group, chunks=ch, comm_sms=comm_sms, transport=transport,
-                            tokens_per_rank=tokens, top_k=TOP_K)
+                            tokens_per_rank=tokens, top_k=TOP_K, quantise_on_dispatch=qod, return_path=return_path)
         dist.barrier()
         per = timed_steps(lambda: layer.forward(x, idx, w), steps, max(warmup, 3))
         ms = max_over_ranks(statistics.mean(per))
-        entry = {"chunks": layer.chunks, "comm_sms": comm_sms, "ms_per_step": ms,
+        entry = {"chunks": layer.chunks, "comm_sms": comm_sms, "quantise_on_dispatch": bool(qod and transport == "p2p"),
+                 "return_path": return_path if transport == "p2p" else "all_to_all",
+                 "ms_per_step": ms,
                  "tflops": work_rank * world / (ms * 1e-3) / 1e12, "rdiff_vs_single_rank": small_rdiff[transport]}
         if transport == "p2p":
             # the same rows without any exchange: this rank's expert GEMMs + SwiGLU quantiser, all SMs
@@ -635,6 +672,13 @@ def ep_leg(dev, rank, world, steps, warmup, chunks, comm_sms):
             gemm_ms = max_over_ranks(statistics.mean(per_g))
             entry.update(gemm_only_ms=gemm_ms, efficiency=gemm_ms / ms, exposed_comm_ms=ms - gemm_ms,
                          rows_received_rank0=int(rows))
+            if layer.chunks > 1:
+                # one more step with CUDA events around every phase (rank 0's view)
+                layer.trace = True
+                dist.barrier()
+                layer.forward(x, idx, w)
+                entry["phases_rank0"] = summarise_phases(layer.phase_times(), layer.chunks)
+                layer.trace = False
         st_word = torch.tensor([_lib.device_status()], device=dev, dtype=torch.int64)
         dist.all_reduce(st_word, op=dist.ReduceOp.MAX)
         entry["device_status"] = int(st_word[0])
@@ -704,6 +748,7 @@ def metric_name(kind):
             "fp8_block": "grouped-GEMM TFLOP/s (FP8 block-scaled M-grouped)",
             "fp8_rowcol": "grouped-GEMM TFLOP/s (FP8 row x channel scales, M-grouped)",
             "fp8_rowcol_k": "grouped-GEMM TFLOP/s (FP8 row x channel scales, K-grouped)",
+            "fp8_block_k": "grouped-GEMM TFLOP/s (FP8 block-scaled K-grouped, weight gradient)",
             "masked": "grouped-GEMM TFLOP/s (BF16 masked M-grouped)",
             "quant_act": "per-block quantiser GB/s (1x128 e4m3)",
             "quant_trans": "per-block quantiser GB/s (transposing 128x128 e4m3 with expansion)",
@@ -713,7 +758,7 @@ def metric_name(kind):
 
 def dtype_name(kind):
     return {"m_grouped": "bf16", "k_grouped": "bf16", "fp8_block": "fp8_e4m3", "fp8_rowcol": "fp8_e4m3",
-            "fp8_rowcol_k": "fp8_e4m3", "masked": "bf16", "quant_act": "bf16->fp8_e4m3",
+            "fp8_rowcol_k": "fp8_e4m3", "fp8_block_k": "fp8_e4m3", "masked": "bf16", "quant_act": "bf16->fp8_e4m3",
             "quant_trans": "bf16->fp8_e4m3", "moe_ep": "fp8_e4m3", "moe_decode": "fp8_e4m3"}[kind]
 
 
@@ -749,6 +794,13 @@ def run_b200(args):
     from triton_grouped_gemm_b200 import _lib
 
     _lib.load()
+    if args.ep_only and use_dist:
+        ep = ep_leg(dev, rank, world, min(args.steps, 8), 3, args.ep_chunks, args.ep_comm_sms, args.ep_quantise_on_dispatch, args.ep_return_path)
+        if rank == 0:
+            print(json.dumps({"ep_only": True, "n_gpus": world, "ep": ep}), flush=True)
+        dist.barrier()
+        dist.destroy_process_group()
+        return 0
     kind, k, n, trans_b = WORKLOADS[args.workload]
     if args.workload in UNIFORM_WORKLOADS:
         UNIFORM[0] = True
@@ -849,7 +901,7 @@ def run_b200(args):
         # a multi-kernel step (MoE layer) is judged as a whole: flops of its GEMMs over the step time
         launch_ms = statistics.mean(per_step) / (1 if kind in ("moe_ep", "moe_decode") else launches)
         if unit == "TFLOP/s":
-            fp8 = kind in ("fp8_block", "moe_ep", "moe_decode", "fp8_rowcol", "fp8_rowcol_k")
+            fp8 = kind in ("fp8_block", "moe_ep", "moe_decode", "fp8_rowcol", "fp8_rowcol_k", "fp8_block_k")
             peak = peaks["bf16"] * (2.0 if fp8 else 1.0)
             achieved = work / (launch_ms * 1e-3) / 1e12
             # DRAM bytes per launch from the ncu capture of the 82 560-row case of this kernel
@@ -914,7 +966,8 @@ def run_b200(args):
             gpu_ref = gpu_reference_leg(sizes, k, n, work)
         if use_dist:
             dist.barrier()
-            ep = ep_leg(dev, rank, world, min(args.steps, 8), 3, args.ep_chunks, args.ep_comm_sms)
+            ep = ep_leg(dev, rank, world, min(args.steps, 8), 3, args.ep_chunks, args.ep_comm_sms,
+                        args.ep_quantise_on_dispatch, args.ep_return_path)
     if rank == 0:
         if also is not None:
             line["also"] = also
@@ -969,7 +1022,7 @@ def run_e2e(args, kind, k, n, trans_b, sizes, inp, dev, use_dist, _unused, work)
             d = {kk: v.to(dev, non_blocking=True) for kk, v in host.items()}
             c = m_grouped_fp8_block_scaled((d["a8"], d["a_s"]), (d["b8"], d["b_s"]), d["s"])
             out_host.copy_(c, non_blocking=True)
-    elif kind in ("fp8_rowcol", "fp8_rowcol_k", "masked"):
+    elif kind in ("fp8_rowcol", "fp8_rowcol_k", "masked", "fp8_block_k"):
         # generic: every operand from pinned host memory, the operator, the result back to the host
         names = [kk for kk, v in inp.items() if isinstance(v, torch.Tensor) and kk != "c"]
         # scale matrices of the K-grouped workload are transposed views of group-major memory
@@ -1070,6 +1123,12 @@ def main():
                     help="kernel form: -1 chosen by problem size (default), 0 single-CTA tiles, 1 CTA pairs")
     ap.add_argument("--ep-comm-sms", type=int, default=16,
                     help="moe_ep_fp8 with more than one GPU: SMs the expert GEMMs leave to the row movers / collectives")
+    ap.add_argument("--ep-quantise-on-dispatch", action="store_true",
+                    help="expert-parallel p2p transport: quantise each pair's bf16 row inside the dispatch kernel")
+    ap.add_argument("--ep-return-path", choices=["copy", "kernel"], default="copy",
+                    help="expert-parallel p2p transport: results go home by copy engine (copy) or by the mover kernel")
+    ap.add_argument("--ep-only", action="store_true",
+                    help="with more than one GPU: run only the expert-parallel leg and print its JSON (tuning runs)")
     ap.add_argument("--sustain-seconds", type=float, default=2.0,
                     help="length of the back-to-back (sustained) leg after the timed steps; 0 = skip")
     ap.add_argument("--no-extras", action="store_true",

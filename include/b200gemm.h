@@ -205,6 +205,22 @@ int b200gemm_fp8_m_grouped_masked_block(const void* a, const float* a_scale, con
                                         void* out, const void* masked_m, int sizes_is_i64, int num_groups,
                                         int expected_m, int n, int k, int num_sms, void* stream);
 
+/* Block-scaled FP8 K-grouped GEMM: the expert weight gradient from two outputs of the transposing
+ * 128x128 quantiser (b200quant_trans_expand_128x below).
+ *   out[g, m, n] = sum_{kb in group g} (sum_{t in kb} x8[m,t] * y8[n,t]) * x_scale[m/128, kb] * y_scale[n/128, kb] -> bf16
+ *   x8 [m_dim, m_expand], y8 [n_dim, m_expand] e4m3 (tokens along the inner axis, each expert's
+ *   tokens padded to a multiple of 128); x_scale [m_dim/128, m_expand/128], y_scale
+ *   [n_dim/128, m_expand/128] fp32; padded_sizes [G]: padded token count of each expert (the
+ *   quantiser's third output), k-blocks of group g = the running prefix / 128; out [G, m_dim, n_dim]
+ *   bf16, an expert without tokens gives zeros.  m_dim, n_dim, m_expand multiples of 128.
+ * The reference ships the quantiser that produces this layout
+ * (quant/trans_per_block_quant_expand_128x.py:135-208) but no kernel that consumes it; the
+ * skeleton (K-major operands, 128-token blocks, tile -> (group, m tile, n tile)) is that of its
+ * per-channel kernel gemm/FP8/k_grouped_gemm_channel_expert.py:64-140. */
+int b200gemm_fp8_k_grouped_block(const void* x8, const float* x_scale, const void* y8, const float* y_scale, void* out,
+                                 const void* padded_sizes, int sizes_is_i64, int num_groups, int64_t m_expand,
+                                 int m_dim, int n_dim, int num_sms, void* stream);
+
 /* ---- per-block FP8 (e4m3) quantisers: bytes and fp32 scales identical to the reference's
  *      torch functions ------------------------------------------------------------------ */
 
@@ -297,6 +313,17 @@ int b200moe_dispatch_quant_rows_multi(const void* x, const int64_t* token_of_pai
                                       const int64_t* dst_row, int64_t first_pair, int64_t num_pairs, int64_t tokens,
                                       int hidden, int dtype, int world, int64_t capacity_rows, int my_rank, int blocks,
                                       void* stream);
+/* The same dispatch for rows that are already quantised: x8 [tokens, hidden] e4m3 bytes and
+ * x_scales [tokens, hidden/128] fp32 (as b200quant_act_1x128 writes them) are copied to the
+ * pair's row of the owner's buffers together with the return address - one launch per chunk
+ * instead of one scatter per payload.  Cheaper than quantising per pair when few SMs run the
+ * mover beside a GEMM (a token's row is quantised once, not once per expert it goes to).
+ * No counterpart in the reference. */
+int b200moe_dispatch_rows_multi(const void* x8, const float* x_scales, const int64_t* token_of_pair,
+                                void* const* row_bases, void* const* scale_bases, void* const* meta_bases,
+                                const int* dst_rank, const int64_t* dst_row, int64_t first_pair, int64_t num_pairs,
+                                int64_t tokens, int hidden, int world, int64_t capacity_rows, int my_rank, int blocks,
+                                void* stream);
 /* The way back: dst_bases[meta[r][1]][meta[r][0], :] = src[r, :] for r < rows, meta [rows, 2] int64
  * being the return addresses left by b200moe_dispatch_quant_rows_multi beside the rows
  * (capacity_rows = rows of each return buffer).  No counterpart in the reference. */
@@ -313,6 +340,12 @@ int b200ipc_free(void* p);
 int b200ipc_export(const void* p, void* handle64);
 int b200ipc_open(const void* handle64, void** out);
 int b200ipc_close(void* p);
+/* n contiguous device-to-device copies queued on `stream`, each its own copy-engine transfer
+ * (dst / src / bytes: HOST arrays of n entries; either side may be a buffer from b200ipc_open).
+ * An expert-parallel layer returns each (expert, source rank) block of results with one such
+ * copy: contiguous on both sides, so no kernel and no SM is needed for the way back.
+ * No counterpart in the reference. */
+int b200ipc_copy_many_async(int n, void* const* dst, const void* const* src, const int64_t* bytes, void* stream);
 
 /* ---- integer layouts on the device ------------------------------------------------------- */
 

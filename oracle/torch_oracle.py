@@ -39,6 +39,7 @@ __all__ = [
     "fp8_rowcol_k_grouped_ref",
     "fp8_block_m_grouped_ref",
     "fp8_block_m_grouped_masked_ref",
+    "fp8_block_k_grouped_ref",
     "dequant_1x128",
     "dequant_128x128",
     "layout_round_up",
@@ -326,6 +327,27 @@ def fp8_block_m_grouped_ref(a8, a_s, b8, b_s, sizes) -> torch.Tensor:
     for g, size in enumerate(_sizes_list(sizes)):
         w = dequant_128x128(b8[g], b_s[g])
         out[start:start + size] = (a[start:start + size] @ w.t()).to(torch.bfloat16)
+        start += size
+    return out
+
+
+def fp8_block_k_grouped_ref(x8, xs, y8, ys, padded_sizes) -> torch.Tensor:
+    """Block-scaled FP8 K-grouped GEMM (the FP8 weight gradient) on two outputs of the transposing
+    quantiser (quant/trans_per_block_quant_expand_128x.py:135-208): ``x8`` [M_DIM, M_EXPAND],
+    ``y8`` [N_DIM, M_EXPAND] with one scale per 128x128 block; expert g owns the tokens after those
+    of the experts before it (``padded_sizes``, multiples of 128).  out[g] = dequant(x)[:, tokens
+    of g] @ dequant(y)[:, tokens of g]^T in fp32, one rounding to bf16; an expert without tokens
+    gives zeros.  PARITY UNPINNED: the reference ships the quantiser but no kernel that consumes
+    its output, so there is no reference arithmetic to pin; the contract restated here is the
+    dequantised product."""
+    xd = dequant_128x128(x8, xs)
+    yd = dequant_128x128(y8, ys)
+    sz = _sizes_list(padded_sizes)
+    out = torch.zeros(len(sz), x8.shape[0], y8.shape[0], dtype=torch.bfloat16)
+    start = 0
+    for g, size in enumerate(sz):
+        if size:
+            out[g] = (xd[:, start:start + size] @ yd[:, start:start + size].t()).to(torch.bfloat16)
         start += size
     return out
 

@@ -235,7 +235,8 @@ def _peer_chunk_plan_worker(rank, world, port, results):
         plan = make_peer_chunk_plan(idx, e, dist.group.WORLD, cap, bounds)
         mine = dict(x=x, idx=idx, token_of_pair=plan.token_of_pair, dst_rank=plan.dst_rank, dst_row=plan.dst_row,
                     recv_offsets=plan.recv_offsets, send_offsets=plan.send_offsets,
-                    size_per_group=plan.size_per_group, n=int(plan.token_of_pair.numel()), pairs=t * k)
+                    size_per_group=plan.size_per_group, n=int(plan.token_of_pair.numel()), pairs=t * k,
+                    blk_count=plan.blk_count, blk_start=plan.blk_start, ret_row0=plan.ret_row0)
         everyone = [None] * world
         dist.all_gather_object(everyone, mine)
         bufs = [torch.full((cap, h), float("nan")) for _ in range(world)]
@@ -282,6 +283,20 @@ def _peer_chunk_plan_worker(rank, world, port, results):
             y = bufs[d][:r_tot] * (row_expert[d][:r_tot].float()[:, None] + 1.0)
             for r in range(r_tot):
                 rets[int(metas[d][r][1])][int(metas[d][r][0])] = y[r]
+        # the copy-engine way back: block (expert l, source s) of rank d's results is one contiguous
+        # copy into s's return buffer at ret_row0[l, s]; it must deliver exactly what the return
+        # addresses deliver
+        rets_copy = [torch.zeros(p["pairs"], h) for p in everyone]
+        for d, p in enumerate(everyone):
+            r_tot = p["recv_offsets"][-1]
+            y = bufs[d][:r_tot] * (row_expert[d][:r_tot].float()[:, None] + 1.0)
+            ok &= p["blk_count"].shape == (e_loc, world) and int(p["blk_count"].sum()) == r_tot
+            for l in range(e_loc):
+                for s_rank in range(world):
+                    n_rows, b0, r0 = int(p["blk_count"][l, s_rank]), int(p["blk_start"][l, s_rank]), int(p["ret_row0"][l, s_rank])
+                    rets_copy[s_rank][r0:r0 + n_rows] = y[b0:b0 + n_rows]
+        for a, b in zip(rets, rets_copy):
+            ok &= bool(torch.equal(a, b))
         pos = plan.pos
         contrib = torch.where((pos >= 0)[:, None], rets[rank][pos.clamp(min=0)], torch.zeros(1, h))
         out = (contrib.view(t, k, h) * w[:, :, None]).sum(1)

@@ -66,13 +66,24 @@ def test_fp8_forward_and_gradients():
     c_ref.backward(dc.float())
     ad = a.to(DEV).requires_grad_(True)
     bd = b.to(DEV).requires_grad_(True)
-    c = grouped_gemm_fp8(ad, bd, torch.tensor(sizes, device=DEV))
+    c = grouped_gemm_fp8(ad, bd, torch.tensor(sizes, device=DEV), fp8_wgrad=False)
     c.backward(dc.to(DEV))
     assert c.dtype == torch.bfloat16 and ad.grad.dtype == torch.bfloat16 and bd.grad.dtype == torch.bfloat16
     assert O.rdiff(c.detach().cpu().float(), c_ref.detach()) < 5e-2
     assert O.rdiff(ad.grad.cpu().float(), a32.grad) < 5e-2
     assert O.rdiff(bd.grad.cpu().float(), b32.grad) < 4e-3          # 16-bit weight gradient
     assert torch.all(bd.grad[1] == 0)
+    # the all-FP8 recipe (default): the weight gradient comes from e4m3 operands quantised in
+    # 128x128 blocks by the transposing quantiser - fp8 noise instead of bf16 noise
+    ad8 = a.to(DEV).requires_grad_(True)
+    bd8 = b.to(DEV).requires_grad_(True)
+    c8 = grouped_gemm_fp8(ad8, bd8, torch.tensor(sizes, device=DEV))
+    c8.backward(dc.to(DEV))
+    assert torch.equal(c8.detach(), c.detach()) and torch.equal(ad8.grad, ad.grad)
+    assert bd8.grad.dtype == torch.bfloat16 and bd8.grad.shape == bd.grad.shape
+    assert O.rdiff(bd8.grad.cpu().float(), b32.grad) < 5e-2
+    assert not torch.equal(bd8.grad, bd.grad)                        # it really took the FP8 route
+    assert torch.all(bd8.grad[1] == 0)
     # and the forward equals the explicit quantise + GEMM path bit for bit
     from triton_grouped_gemm_b200.gemm.FP8.m_grouped_gemm_block_scaled import m_grouped_fp8_block_scaled
     from triton_grouped_gemm_b200.quant.per_block_cast import per_block_cast_to_fp8, per_token_cast_to_fp8

@@ -1,8 +1,9 @@
 """Expert-parallel FP8 layer on two GPUs (skipped on a single-GPU box): both transports - NCCL
 all-to-all and the peer-memory row movers - must reproduce the single-rank layer exactly, over
 several steps that reuse the exchange buffers; each transport in its one-shot form (chunks = 1)
-and pipelined over groups of local experts (4 even groups; for peer memory also 3 uneven ones,
-where quantise-on-dispatch replaces the activation quantiser).  The peer-memory layers are
+and pipelined over groups of local experts (4 even groups; for peer memory also 3 uneven ones
+and 8, with the dispatch kernel quantising the bf16 rows itself; results going home by copy
+engine or by the return-address mover kernel).  The peer-memory layers are
 closed collectively before the process group goes away."""
 
 import os
@@ -14,7 +15,7 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _worker(rank, world, port, transport, chunks, results):
+def _worker(rank, world, port, transport, chunks, qod, return_path, results):
     import torch.distributed as dist
 
     from triton_grouped_gemm_b200 import _lib
@@ -32,7 +33,7 @@ def _worker(rank, world, port, transport, chunks, results):
         e_loc = e // world
         layer = Fp8MoELayer(w13[rank * e_loc:(rank + 1) * e_loc].to(dev), w2[rank * e_loc:(rank + 1) * e_loc].to(dev), e,
                             dist.group.WORLD, transport=transport, chunks=chunks, tokens_per_rank=t, top_k=k,
-                            capacity_factor=2.0)
+                            capacity_factor=2.0, quantise_on_dispatch=qod, return_path=return_path)
         full = Fp8MoELayer(w13.to(dev), w2.to(dev), e, None)
         worst = 0.0
         for step in range(3):
@@ -50,8 +51,10 @@ def _worker(rank, world, port, transport, chunks, results):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("transport,chunks", [("p2p", 1), ("p2p", 4), ("p2p", 3), ("nccl", 1), ("nccl", 4)])
-def test_two_gpu_layer_matches_single_rank(transport, chunks):
+@pytest.mark.parametrize("transport,chunks,qod,return_path", [
+    ("p2p", 1, False, "copy"), ("p2p", 4, False, "copy"), ("p2p", 3, True, "copy"), ("p2p", 8, True, "kernel"),
+    ("p2p", 4, False, "kernel"), ("nccl", 1, False, "copy"), ("nccl", 4, False, "copy")])
+def test_two_gpu_layer_matches_single_rank(transport, chunks, qod, return_path):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
@@ -62,7 +65,7 @@ def test_two_gpu_layer_matches_single_rank(transport, chunks):
     ctx = mp.get_context("spawn")
     with ctx.Manager() as mgr:
         results = mgr.dict()
-        procs = [ctx.Process(target=_worker, args=(r, 2, port, transport, chunks, results)) for r in range(2)]
+        procs = [ctx.Process(target=_worker, args=(r, 2, port, transport, chunks, qod, return_path, results)) for r in range(2)]
         for p in procs:
             p.start()
         for p in procs:

@@ -223,6 +223,20 @@ def test_quantise_on_dispatch_and_return_movers_on_one_gpu():
             assert torch.equal(bs[r].cpu().view(torch.int32), es.view(torch.int32))
             assert torch.equal(bm[r].cpu(), em)
         assert _lib.device_status() == 0
+        # the same stores from rows quantised beforehand (b200moe_dispatch_rows_multi)
+        q_d, s_d = q_ref.view(torch.uint8).to(DEV), s_ref.to(DEV)
+        c8 = [torch.zeros(cap, h, dtype=torch.uint8, device=DEV) for _ in range(world)]
+        cs = [torch.zeros(cap, h // 128, dtype=torch.float32, device=DEV) for _ in range(world)]
+        cm = [torch.full((cap, 2), -7, dtype=torch.int64, device=DEV) for _ in range(world)]
+        rc = lib.b200moe_dispatch_rows_multi(q_d.data_ptr(), s_d.data_ptr(), tok_d.data_ptr(), mk(c8), mk(cs), mk(cm),
+                                             rank_d.data_ptr(), row_d.data_ptr(), first, count, t, h, world, cap, me,
+                                             blocks, stream)
+        _lib.check(rc, "dispatch_rows")
+        torch.cuda.synchronize()
+        for r in range(world):
+            assert torch.equal(c8[r], b8[r]) and torch.equal(cs[r].view(torch.int32), bs[r].view(torch.int32))
+            assert torch.equal(cm[r], bm[r])
+        assert _lib.device_status() == 0
     # the way back: rows [0, m) of a result buffer go to (meta[r, 1], meta[r, 0])
     m = 300
     y = torch.randn(m, h, generator=gen).bfloat16().to(DEV)

@@ -52,11 +52,15 @@ _SIGNATURES = {
                                             c_int, c_void_p, c_int, c_int64, c_int, c_int, c_int, c_int, c_void_p],
     "b200gemm_fp8_m_grouped_masked_block": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                             c_int, c_int, c_int, c_int, c_void_p],
+    "b200gemm_fp8_k_grouped_block": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64,
+                                     c_int, c_int, c_int, c_void_p],
     "b200moe_route_plan": [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     "b200moe_scatter_rows_multi": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int64,
                                    c_int64, c_int, c_void_p],
     "b200moe_dispatch_quant_rows_multi": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
                                           c_int64, c_int64, c_int, c_int, c_int, c_int64, c_int, c_int, c_void_p],
+    "b200moe_dispatch_rows_multi": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
+                                    c_int64, c_int64, c_int, c_int, c_int64, c_int, c_int, c_void_p],
     "b200moe_return_rows_multi": [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int64, c_int, c_void_p],
     "b200moe_combine_topk_multi": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int,
                                    c_int64, c_void_p],
@@ -65,6 +69,7 @@ _SIGNATURES = {
     "b200ipc_export": [c_void_p, c_void_p],
     "b200ipc_open": [c_void_p, c_void_p],
     "b200ipc_close": [c_void_p],
+    "b200ipc_copy_many_async": [c_int, c_void_p, c_void_p, c_void_p, c_void_p],
     "b200layout_group_starts": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "b200layout_psum": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
     "b200layout_grouped_rows": [c_void_p, c_int, c_int, c_int, c_void_p, c_int64, c_void_p],

@@ -59,4 +59,20 @@ int b200ipc_close(void* p) {
   return 0;
 }
 
+// n contiguous device-to-device copies on `stream`, one cudaMemcpyAsync each (the copy engines
+// move them, over NVLink when a side is another rank's buffer, without occupying an SM).
+int b200ipc_copy_many_async(int n, void* const* dst, const void* const* src, const int64_t* bytes, void* stream) {
+  using namespace b200;
+  B200_REQUIRE(n >= 0, "b200ipc_copy_many_async: negative count");
+  if (n == 0) return 0;
+  B200_REQUIRE(dst && src && bytes, "b200ipc_copy_many_async: null pointer");
+  for (int i = 0; i < n; ++i) {
+    if (bytes[i] == 0) continue;
+    B200_REQUIRE(bytes[i] > 0 && dst[i] && src[i], "b200ipc_copy_many_async: copy %d has a null pointer or a negative size", i);
+    B200_CUDA(cudaMemcpyAsync(dst[i], src[i], static_cast<size_t>(bytes[i]), cudaMemcpyDeviceToDevice,
+                              static_cast<cudaStream_t>(stream)));
+  }
+  return 0;
+}
+
 }  // extern "C"

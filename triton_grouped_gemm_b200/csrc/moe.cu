@@ -276,6 +276,48 @@ dispatch_quant_rows_multi_kernel(const uint4* __restrict__ x, const long long* _
   }
 }
 
+// The same dispatch for rows that are already quantised (x8 [tokens, hidden] bytes, xs [tokens,
+// hidden/128] fp32): the pair's row, its scales and its return address in one pass - one launch
+// per chunk instead of one scatter per payload.  hidden % 16 == 0.
+__global__ void __launch_bounds__(1024)
+dispatch_rows_multi_kernel(const uint4* __restrict__ x8, const float* __restrict__ xs,
+                           const long long* __restrict__ token_of_pair, PeerBases rows8, PeerBases scales,
+                           PeerBases meta, const int* __restrict__ rank, const long long* __restrict__ row,
+                           long long first, long long count, long long tokens, int hidden, int nb, int world,
+                           long long capacity_rows, int my_rank, unsigned* status) {
+  const int lane = threadIdx.x & 31;
+  const long long warp = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  const int row_vecs = hidden >> 4;
+  for (long long p = warp; p < count; p += warps) {
+    const long long i = first + p;
+    const int dst_rank = rank[i];
+    const long long dst_row = row[i];
+    const long long t = token_of_pair[i];
+    if (dst_rank < 0 || dst_rank >= world || dst_row < 0 || dst_row >= capacity_rows || t < 0 || t >= tokens) {
+      if (lane == 0 && status) atomicOr(status, kDevBadRowIndex);
+      continue;
+    }
+    const uint4* s = x8 + t * row_vecs;
+    uint4* d = reinterpret_cast<uint4*>(static_cast<uint8_t*>(rows8.base[dst_rank]) + dst_row * hidden);
+    int v = lane;
+    for (; v + 96 < row_vecs; v += 128) {
+      const uint4 a = __ldg(s + v), b = __ldg(s + v + 32), c = __ldg(s + v + 64), e = __ldg(s + v + 96);
+      d[v] = a;
+      d[v + 32] = b;
+      d[v + 64] = c;
+      d[v + 96] = e;
+    }
+    for (; v < row_vecs; v += 32) d[v] = __ldg(s + v);
+    const float* ss = xs + t * nb;
+    float* ds = static_cast<float*>(scales.base[dst_rank]) + dst_row * nb;
+    for (int j = lane; j < nb; j += 32) ds[j] = __ldg(ss + j);
+    if (lane == 0)
+      *reinterpret_cast<longlong2*>(static_cast<long long*>(meta.base[dst_rank]) + 2 * dst_row) =
+          make_longlong2(i, static_cast<long long>(my_rank));
+  }
+}
+
 // The way back: dst[meta[r].rank][meta[r].row, :] = src[r, :] for r < rows, meta [rows, 2] int64 being
 // the return addresses the dispatch kernel left beside the rows (row in the owner's return
 // buffer, owner rank).
@@ -463,6 +505,38 @@ int b200moe_dispatch_quant_rows_multi(const void* x, const int64_t* token_of_pai
       static_cast<const uint4*>(x), reinterpret_cast<const long long*>(token_of_pair), pr, ps, pm, dst_rank,
       reinterpret_cast<const long long*>(dst_row), first_pair, num_pairs, tokens, hidden, dtype, world, capacity_rows,
       my_rank, device_status_ptr());
+  B200_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int b200moe_dispatch_rows_multi(const void* x8, const float* x_scales, const int64_t* token_of_pair,
+                                void* const* row_bases, void* const* scale_bases, void* const* meta_bases,
+                                const int* dst_rank, const int64_t* dst_row, int64_t first_pair, int64_t num_pairs,
+                                int64_t tokens, int hidden, int world, int64_t capacity_rows, int my_rank,
+                                int blocks_arg, void* stream) {
+  using namespace b200;
+  const char* who = "b200moe_dispatch_rows_multi";
+  B200_REQUIRE(first_pair >= 0 && num_pairs >= 0 && tokens >= 0 && capacity_rows >= 0, "%s: negative size", who);
+  B200_REQUIRE(hidden > 0 && hidden % 128 == 0, "%s: hidden (%d) must be a multiple of 128", who, hidden);
+  B200_REQUIRE(my_rank >= 0 && my_rank < world, "%s: my_rank (%d) outside [0, world)", who, my_rank);
+  if (num_pairs == 0) return 0;
+  B200_REQUIRE(x8 && x_scales && token_of_pair && dst_rank && dst_row, "%s: null pointer", who);
+  B200_REQUIRE((reinterpret_cast<uintptr_t>(x8) & 15) == 0, "%s: x8 must be 16-byte aligned", who);
+  PeerBases pr, ps, pm;
+  int rc = fill_bases(&pr, const_cast<const void* const*>(row_bases), world, who);
+  if (rc) return rc;
+  rc = fill_bases(&ps, const_cast<const void* const*>(scale_bases), world, who);
+  if (rc) return rc;
+  rc = fill_bases(&pm, const_cast<const void* const*>(meta_bases), world, who);
+  if (rc) return rc;
+  const int sms = sm_count();
+  B200_REQUIRE(sms > 0, "%s: no CUDA device", who);
+  int blocks, threads;
+  mover_grid(blocks_arg, num_pairs, sms, &blocks, &threads);
+  dispatch_rows_multi_kernel<<<blocks, threads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(x8), x_scales, reinterpret_cast<const long long*>(token_of_pair), pr, ps, pm, dst_rank,
+      reinterpret_cast<const long long*>(dst_row), first_pair, num_pairs, tokens, hidden, hidden / 128, world,
+      capacity_rows, my_rank, device_status_ptr());
   B200_CUDA(cudaGetLastError());
   return 0;
 }

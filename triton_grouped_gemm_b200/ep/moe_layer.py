@@ -24,7 +24,8 @@ from .dispatch import combine, dispatch, dispatch_chunk_async, make_chunked_plan
 class Fp8MoELayer:
     def __init__(self, w13: torch.Tensor, w2: torch.Tensor, num_experts: int,
                  group: Optional[dist.ProcessGroup] = None, chunks: int = 4, comm_sms: int = 16,
-                 transport: str = "nccl", capacity_factor: float = 1.5, tokens_per_rank: int = 0, top_k: int = 0):
+                 transport: str = "nccl", capacity_factor: float = 1.5, tokens_per_rank: int = 0, top_k: int = 0,
+                 quantise_on_dispatch: bool = False, return_path: str = "copy"):
         """w13 [E_local, 2*I, H] (gate rows then up rows), w2 [E_local, H, I], bf16, this rank's experts.
         With more than one rank the expert GEMMs consume rows in the order the all-to-all delivers
         them (every [source rank][expert] block is a row group of its own, mapped to its expert's
@@ -36,7 +37,15 @@ class Fp8MoELayer:
         size its buffers: ``capacity_factor`` x the mean number of rows a rank receives.  There the
         received rows are laid out [local expert][source rank], one row group per expert, and
         ``chunks`` (any number up to the local expert count) splits the experts into nearly equal
-        runs.  Call ``close()`` on every rank when done with a p2p layer."""
+        runs.  ``quantise_on_dispatch`` (pipelined p2p only) lets the dispatch kernel quantise each
+        pair's bf16 token row itself instead of quantising every token once beforehand: same bytes,
+        no fp8 copy of the activations in HBM, but a token's row is quantised once per expert it
+        goes to, which costs more than it saves when the mover runs on the few SMs beside a GEMM.
+        ``return_path`` (pipelined p2p only): "copy" sends every (expert, source rank) block of
+        results home with one copy-engine transfer - contiguous on both sides, so the way back
+        occupies no SM and the GEMMs keep all but the dispatch movers' SMs; "kernel" uses the
+        return-address mover kernel instead.
+        Call ``close()`` on every rank when done with a p2p layer."""
         assert w13.dim() == 3 and w2.dim() == 3 and w13.shape[0] == w2.shape[0]
         self.group = group
         self.num_experts = num_experts
@@ -63,6 +72,11 @@ class Fp8MoELayer:
                 chunks -= 1
         self.chunks = max(1, min(chunks, self.e_local)) if world > 1 else 1
         self._peer_buffers = []
+        self.quantise_on_dispatch = bool(quantise_on_dispatch)
+        assert return_path in ("copy", "kernel")
+        self.return_path = return_path
+        self.trace = False
+        self._marks = None
         if self.transport == "p2p":
             from .p2p import PeerBuffer, chunk_bounds
 
@@ -198,25 +212,41 @@ class Fp8MoELayer:
 
     def _forward_p2p_pipelined(self, x, topk_idx, topk_weight) -> torch.Tensor:
         """Peer memory in both directions, beside the GEMMs.  A dispatch stream sends chunk after
-        chunk: one kernel per chunk quantises each pair's bf16 token row 1x128 and stores the fp8
-        row, its scales and the pair's return address into the owner's buffers.  The main stream
-        runs chunk c's GEMMs (one row group per expert) as soon as its rows have landed
-        everywhere; a return stream pushes chunk c's results into the token owners' buffers through
-        the return addresses.  Movers that run beside a GEMM are a few large blocks on the SMs the
-        GEMMs leave free; the first dispatch and the last return use the whole GPU.  A local
-        weighted sum finishes the step."""
+        chunk: one kernel per chunk stores each pair's fp8 row, its scales and the pair's return
+        address into the owner's buffers (rows quantised once up front, or - with
+        ``quantise_on_dispatch`` - by that same kernel from the bf16 rows).  The main stream runs
+        chunk c's GEMMs (one row group per expert) as soon as its rows have landed everywhere; a
+        return stream sends chunk c's results to the token owners' buffers: one copy-engine
+        transfer per (expert, source rank) block, or the return-address mover kernel.  Movers that
+        run beside a GEMM are a few large blocks on the SMs the GEMMs leave free; the first
+        dispatch (and the last return kernel) use the whole GPU.  A local weighted sum
+        finishes the step.  With ``self.trace`` set, CUDA events bracket every phase on its stream
+        (``phase_times()`` reads them)."""
         from .. import _lib
-        from .p2p import dispatch_quant_range, make_peer_chunk_plan, return_rows
+        from .p2p import (dispatch_quant_range, dispatch_range, make_peer_chunk_plan, return_blocks_by_copy,
+                          return_rows)
 
         lib = _lib.load()
         dev = x.device
+        main = torch.cuda.current_stream(dev)
+        marks = [] if self.trace else None
+
+        def mark(name, stream):
+            if marks is not None:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record(stream)
+                marks.append((name, ev))
+
+        mark("start", main)
+        if not self.quantise_on_dispatch:
+            x8, xs = per_token_cast_to_fp8(x)   # queued first: runs while the host waits for the plan's counts
         plan = make_peer_chunk_plan(topk_idx, self.num_experts, self.group, self.recv8.capacity, self.bounds)
         assert plan.pos.numel() <= self.ret.capacity, "more (token, k) pairs than the return buffer holds"
         self.last_rows = (plan.recv_offsets[-1], plan.size_per_group)
+        mark("plan_done", main)
         chunks = plan.chunks
         sms = lib.b200gemm_sm_count()
         gemm_sms = sms - self.comm_sms if 0 < self.comm_sms < sms - 2 else -1
-        main = torch.cuda.current_stream(dev)
         s_disp, s_ret = self._side
         ready = torch.cuda.Event()
         ready.record(main)
@@ -226,25 +256,40 @@ class Fp8MoELayer:
         with torch.cuda.stream(s_disp):
             s_disp.wait_event(ready)
             for c in range(chunks):
-                dispatch_quant_range(x, plan, plan.send_offsets[c], plan.send_offsets[c + 1], self.recv8, self.recvs,
-                                     self.meta, blocks=0 if c == 0 else background)
+                lo, hi = plan.send_offsets[c], plan.send_offsets[c + 1]
+                blocks = 0 if c == 0 else background
+                mark(f"dispatch{c}>", s_disp)
+                if self.quantise_on_dispatch:
+                    dispatch_quant_range(x, plan, lo, hi, self.recv8, self.recvs, self.meta, blocks=blocks)
+                else:
+                    dispatch_range(x8, xs, plan, lo, hi, self.recv8, self.recvs, self.meta, blocks=blocks)
+                mark(f"dispatch{c}<", s_disp)
                 dist.all_reduce(self._flag, group=self.group)      # chunk c has landed on every rank
                 landed[c].record(s_disp)
+                mark(f"landed{c}", s_disp)
         for c in range(chunks):
             lo, hi = plan.recv_offsets[c], plan.recv_offsets[c + 1]
             main.wait_event(landed[c])
+            mark(f"gemm{c}>", main)
             self.experts(self.recv8.local[lo:hi].view(torch.float8_e4m3fn), self.recvs.local[lo:hi],
                          plan.size_per_group[self.bounds[c]:self.bounds[c + 1]], num_sms=gemm_sms,
                          out=self.ybuf.local[lo:hi], first_expert=self.bounds[c])
+            mark(f"gemm{c}<", main)
             computed[c].record(main)
             with torch.cuda.stream(s_ret):
                 s_ret.wait_event(computed[c])
-                return_rows(self.ybuf.local[lo:hi], self.meta.local[lo:hi], self.ret,
-                            blocks=0 if c == chunks - 1 else background)
+                mark(f"return{c}>", s_ret)
+                if self.return_path == "copy":
+                    return_blocks_by_copy(self.ybuf, self.ret, plan, self.bounds[c], self.bounds[c + 1])
+                else:
+                    return_rows(self.ybuf.local[lo:hi], self.meta.local[lo:hi], self.ret,
+                                blocks=0 if c == chunks - 1 else background)
+                mark(f"return{c}<", s_ret)
         with torch.cuda.stream(s_ret):
             dist.all_reduce(self._flag, group=self.group)          # every rank's results have been pushed
             done = torch.cuda.Event()
             done.record(s_ret)
+            mark("returned_everywhere", s_ret)
         main.wait_event(done)
         out = torch.empty((plan.num_tokens, self.hidden), dtype=torch.bfloat16, device=dev)
         w32 = topk_weight.reshape(-1).to(torch.float32).contiguous()
@@ -253,7 +298,18 @@ class Fp8MoELayer:
                                           plan.num_tokens, plan.top_k, self.hidden, self.ret.capacity,
                                           _lib.stream_ptr(dev))
         _lib.check(rc, "b200moe_combine_topk")
+        mark("end", main)
+        self._marks = marks
         return out
+
+    def phase_times(self):
+        """After a pipelined peer-memory step with ``trace`` set: [(phase, ms since the step's
+        start)] for every mark, in the order they were recorded (synchronises the device)."""
+        if not getattr(self, "_marks", None):
+            return []
+        torch.cuda.synchronize()
+        t0 = self._marks[0][1]
+        return [(name, t0.elapsed_time(ev)) for name, ev in self._marks]
 
     def decode(self, x8: torch.Tensor, xs: torch.Tensor, masked_m: torch.Tensor, m_max: int,
                out: Optional[torch.Tensor] = None) -> torch.Tensor:

@@ -186,6 +186,9 @@ class PeerChunkPlan:
     send_offsets: List[int]          # [chunks + 1] send-order ranges of the chunks
     recv_offsets: List[int]          # [chunks + 1] row ranges of the chunks in this rank's receive buffers
     size_per_group: torch.Tensor     # [e_loc] int64 rows of each local expert here
+    blk_count: "object" = None       # host int array [e_loc, world]: rows of block (local expert, source rank) here
+    blk_start: "object" = None       # host int array [e_loc, world]: first row of that block in this rank's buffers
+    ret_row0: "object" = None        # host int array [e_loc, world]: first row of that block in the SOURCE's return buffer
 
     @property
     def chunks(self) -> int:
@@ -196,6 +199,29 @@ def chunk_bounds(e_loc: int, chunks: int) -> List[int]:
     """Boundaries of `chunks` nearly equal runs of consecutive local experts."""
     chunks = max(1, min(chunks, e_loc))
     return [(c * e_loc) // chunks for c in range(chunks + 1)]
+
+
+_KEY_TABLES = {}
+
+
+def _key_tables(world: int, e_loc: int, bounds: tuple, dev):
+    """Sort key of global expert (rank r, local expert l) = its place in (chunk of l, r, l) order, so
+    that the send order is chunk-major and, inside a chunk, grouped by destination rank, then
+    expert.  Returns (key_of_expert on the host, its inverse on the host, key_of_expert on ``dev``);
+    cached, the tables depend only on the layer's shape."""
+    ck = (world, e_loc, bounds, str(dev))
+    if ck not in _KEY_TABLES:
+        import numpy as np
+
+        b = np.asarray(bounds)
+        l_ids = np.arange(e_loc)
+        chunk_of_l = np.searchsorted(b[1:], l_ids, side="right")
+        width = (b[1:] - b[:-1])[chunk_of_l]
+        key_rl = (world * b[:-1][chunk_of_l])[None, :] + np.arange(world)[:, None] * width[None, :] \
+            + (l_ids - b[:-1][chunk_of_l])[None, :]                        # [r, l]
+        key_h = key_rl.reshape(world * e_loc).astype(np.int64)
+        _KEY_TABLES[ck] = (key_h, np.argsort(key_h), torch.from_numpy(key_h).to(dev))
+    return _KEY_TABLES[ck]
 
 
 def make_peer_chunk_plan(topk_idx: torch.Tensor, num_experts: int, group, capacity_rows: int,
@@ -211,29 +237,35 @@ def make_peer_chunk_plan(topk_idx: torch.Tensor, num_experts: int, group, capaci
     n = t * k
     dev = topk_idx.device
     flat = topk_idx.reshape(-1).to(torch.int64)
-    # sort key of global expert (rank r, local l): its place in (chunk of l, r, l) order, so the send
-    # order is chunk-major and inside a chunk grouped by destination rank, then expert
-    b = torch.tensor(bounds, device=dev)
-    l_ids = torch.arange(e_loc, device=dev)
-    chunk_of_l = torch.bucketize(l_ids, b[1:], right=True)
-    width = (b[1:] - b[:-1])[chunk_of_l]                                  # experts in l's chunk
-    key_rl = (world * b[:-1][chunk_of_l])[None, :] + torch.arange(world, device=dev)[:, None] * width[None, :] \
-        + (l_ids - b[:-1][chunk_of_l])[None, :]                            # [r, l]
-    key_of_expert = key_rl.reshape(num_experts)
+    key_of_expert_h, expert_of_key, key_of_expert = _key_tables(world, e_loc, tuple(bounds), dev)
     key = key_of_expert[flat.clamp(0, num_experts - 1)]
     key = torch.where((flat >= 0) & (flat < num_experts), key, torch.full_like(key, -1))
     counts_by_key, send_order, pos = route_plan(key, num_experts)
     counts = counts_by_key[key_of_expert]                                 # by global expert
-    by_dest, dst_block_start, totals = _arrival_layout(counts, group, num_experts)
+    counts_flat = torch.empty(world * num_experts, dtype=counts.dtype, device=dev)
+    dist.all_gather_into_tensor(counts_flat, counts.contiguous(), group=group)
+    by_dest = counts_flat.view(world, world, e_loc).permute(1, 2, 0).contiguous()       # [d, l, s]
+    flat_blocks = by_dest.view(world, e_loc * world)
+    starts = (flat_blocks.cumsum(1) - flat_blocks).view(world, e_loc, world)            # [d, l, s]
+    dst_block_start = starts[:, :, me].reshape(num_experts)
     size_per_group = by_dest[me].sum(-1).to(torch.int64).contiguous()     # [e_loc]
-    recv_cum = torch.cat([size_per_group.new_zeros(1), size_per_group.cumsum(0)])[b]           # [chunks + 1]
-    send_cum = torch.cat([counts_by_key.new_zeros(1), counts_by_key.cumsum(0)])[world * b]     # [chunks + 1]
-    host = torch.cat([totals, recv_cum, send_cum]).cpu()                  # the one host sync
-    if int(host[:world].max()) > capacity_rows:
-        raise RuntimeError(f"a rank would receive {int(host[:world].max())} rows, more than the exchange buffers hold "
+    # ---- the one host synchronisation: every rank's per-expert counts (world x num_experts integers);
+    # all offsets the host needs follow from them
+    ca = counts_flat.cpu().view(world, world, e_loc).numpy()              # [s, d, l]
+    totals = ca.sum(axis=(0, 2))                                          # rows every rank receives
+    if int(totals.max()) > capacity_rows:
+        raise RuntimeError(f"a rank would receive {int(totals.max())} rows, more than the exchange buffers hold "
                            f"({capacity_rows}); raise capacity_factor")
-    recv_offsets = [int(v) for v in host[world:world + chunks + 1]]
-    send_offsets = [int(v) for v in host[world + chunks + 1:]]
+    blk_count = ca[:, me, :].T.copy()                                     # [l, s] rows of each block here
+    blk_start = (blk_count.reshape(-1).cumsum() - blk_count.reshape(-1)).reshape(e_loc, world)
+    rows_per_expert = blk_count.sum(axis=1)
+    recv_offsets = [int(rows_per_expert[:bb].sum()) for bb in bounds]
+    # send order of rank s: its counts in key order; where its pairs for expert (me, l) start
+    cbk = ca.reshape(world, num_experts)[:, expert_of_key]               # [s, key]
+    send_start = cbk.cumsum(axis=1) - cbk                                 # [s, key]
+    ret_row0 = send_start[:, key_of_expert_h[me * e_loc:(me + 1) * e_loc]].T.copy()   # [l, s]
+    my_cbk = cbk[me]
+    send_offsets = [int(my_cbk[:world * bb].sum()) for bb in bounds]
     send_start_by_key = counts_by_key.cumsum(0) - counts_by_key
     valid = send_order[:send_offsets[-1]]
     key_sorted = key[valid]
@@ -243,7 +275,34 @@ def make_peer_chunk_plan(topk_idx: torch.Tensor, num_experts: int, group, capaci
     dst_row = dst_block_start[e_sorted] + (idx - send_start_by_key[key_sorted])
     return PeerChunkPlan(num_tokens=t, top_k=k, bounds=list(bounds), token_of_pair=(valid // k).contiguous(),
                          dst_rank=dst_rank.contiguous(), dst_row=dst_row.contiguous(), pos=pos,
-                         send_offsets=send_offsets, recv_offsets=recv_offsets, size_per_group=size_per_group)
+                         send_offsets=send_offsets, recv_offsets=recv_offsets, size_per_group=size_per_group,
+                         blk_count=blk_count, blk_start=blk_start, ret_row0=ret_row0)
+
+
+def return_blocks_by_copy(ybuf: PeerBuffer, ret: PeerBuffer, plan: PeerChunkPlan, l_lo: int, l_hi: int) -> None:
+    """Results of local experts [l_lo, l_hi) back to their token owners by copy engine: block
+    (expert l, source rank s) is contiguous here ([expert][source] layout) and contiguous in s's
+    return buffer (s sent those pairs consecutively), so each block is one device-to-device copy
+    on the current stream - over NVLink for the other ranks - and no SM is involved."""
+    row_bytes = ybuf.local.shape[1] * ybuf.local.element_size()
+    assert row_bytes == ret.local.shape[1] * ret.local.element_size()
+    dsts, srcs, sizes = [], [], []
+    own = ybuf.local.data_ptr()
+    for l in range(l_lo, l_hi):
+        for s_rank in range(ybuf.world):
+            n = int(plan.blk_count[l, s_rank])
+            if n:
+                assert int(plan.ret_row0[l, s_rank]) + n <= ret.capacity
+                dsts.append(ret.bases[s_rank] + int(plan.ret_row0[l, s_rank]) * row_bytes)
+                srcs.append(own + int(plan.blk_start[l, s_rank]) * row_bytes)
+                sizes.append(n * row_bytes)
+    if not dsts:
+        return
+    m = len(dsts)
+    with torch.cuda.device(ybuf.local.device):
+        rc = _lib.load().b200ipc_copy_many_async(m, (ctypes.c_void_p * m)(*dsts), (ctypes.c_void_p * m)(*srcs),
+                                                 (ctypes.c_int64 * m)(*sizes), _lib.stream_ptr(ybuf.local.device))
+    _lib.check(rc, "b200ipc_copy_many_async")
 
 
 def dispatch_quant_range(x: torch.Tensor, plan: PeerChunkPlan, lo: int, hi: int, rows8: PeerBuffer,
@@ -264,6 +323,24 @@ def dispatch_quant_range(x: torch.Tensor, plan: PeerChunkPlan, lo: int, hi: int,
             plan.dst_row.data_ptr(), lo, hi - lo, x.shape[0], hidden, 0 if x.dtype == torch.bfloat16 else 1, rows8.world,
             rows8.capacity, rows8.rank, int(blocks), _lib.stream_ptr(x.device))
     _lib.check(rc, "b200moe_dispatch_quant_rows_multi")
+
+
+def dispatch_range(x8: torch.Tensor, xs: torch.Tensor, plan: PeerChunkPlan, lo: int, hi: int, rows8: PeerBuffer,
+                   scales: PeerBuffer, meta: PeerBuffer, blocks: int = 0) -> None:
+    """Pairs [lo, hi) of the send order, rows already quantised (``x8`` fp8 [T, H], ``xs`` fp32
+    [T, H/128]): copy each pair's row, scales and return address to the owning rank's buffers."""
+    src = x8.view(torch.uint8) if x8.dtype != torch.uint8 else x8
+    assert src.is_cuda and src.is_contiguous() and xs.is_contiguous() and xs.dtype == torch.float32
+    hidden = src.shape[1]
+    assert rows8.local.shape[1] == hidden and scales.local.shape[1] == hidden // 128 == xs.shape[1]
+    assert meta.local.dtype == torch.int64 and meta.local.shape[1] == 2
+    assert rows8.capacity == scales.capacity == meta.capacity
+    with torch.cuda.device(src.device):
+        rc = _lib.load().b200moe_dispatch_rows_multi(
+            src.data_ptr(), xs.data_ptr(), plan.token_of_pair.data_ptr(), rows8.bases, scales.bases, meta.bases,
+            plan.dst_rank.data_ptr(), plan.dst_row.data_ptr(), lo, hi - lo, src.shape[0], hidden, rows8.world,
+            rows8.capacity, rows8.rank, int(blocks), _lib.stream_ptr(src.device))
+    _lib.check(rc, "b200moe_dispatch_rows_multi")
 
 
 def return_rows(src: torch.Tensor, meta: torch.Tensor, ret: PeerBuffer, blocks: int = 0) -> None:

@@ -1,5 +1,5 @@
 """Differentiable grouped GEMM: forward and input gradient through the M-grouped kernel, weight
-gradient through the K-grouped kernel.
+gradient through the K-grouped kernel (16-bit, and block-scaled FP8 throughout in ``grouped_gemm_fp8``).
 
 The reference keeps forward (``m_grouped_gemm``) and weight gradient (``k_grouped_gemm``) as
 separate operators; its vendored baseline wraps the cuBLAS loop in an autograd function
@@ -54,11 +54,14 @@ def grouped_gemm(a: torch.Tensor, b: torch.Tensor, size_per_group: torch.Tensor,
 
 class _GroupedGemmFp8(torch.autograd.Function):
     """FP8 training recipe over the block-scaled kernels: forward and input gradient in e4m3 with
-    1x128 activation / 128x128 weight scales (quantised on the fly), weight gradient in the
-    16-bit K-grouped kernel.  ``b`` is [G, N, K] (the ``trans_b=True`` layout)."""
+    1x128 activation / 128x128 weight scales (quantised on the fly).  Weight gradient: in FP8 as
+    well when ``fp8_wgrad`` is set and K and N are multiples of 128 - both operands go through the
+    transposing 128x128 quantiser (quant/trans_per_block_quant_expand_128x.py:135-208 of the
+    reference, whose layout exists for this) into the block-scaled K-grouped kernel - otherwise
+    in the 16-bit K-grouped kernel.  ``b`` is [G, N, K] (the ``trans_b=True`` layout)."""
 
     @staticmethod
-    def forward(ctx, a, b, size_per_group):
+    def forward(ctx, a, b, size_per_group, fp8_wgrad=True):
         from ..quant.per_block_cast import per_block_cast_to_fp8, per_token_cast_to_fp8
         from .FP8.m_grouped_gemm_block_scaled import m_grouped_fp8_block_scaled
 
@@ -66,6 +69,7 @@ class _GroupedGemmFp8(torch.autograd.Function):
         b = b.contiguous()
         c = m_grouped_fp8_block_scaled(per_token_cast_to_fp8(a), per_block_cast_to_fp8(b), size_per_group)
         ctx.save_for_backward(a, b, size_per_group)
+        ctx.fp8_wgrad = bool(fp8_wgrad) and a.shape[1] % 128 == 0 and b.shape[1] % 128 == 0 and a.dtype == torch.bfloat16
         return c.to(a.dtype)
 
     @staticmethod
@@ -82,12 +86,18 @@ class _GroupedGemmFp8(torch.autograd.Function):
             da = m_grouped_fp8_block_scaled(per_token_cast_to_fp8(grad.to(torch.bfloat16)), bt8, size_per_group).to(a.dtype)
         if ctx.needs_input_grad[1]:
             sizes = size_per_group if size_per_group.dtype in (torch.int32, torch.int64) else size_per_group.long()
-            db = k_grouped_gemm(grad, a, sizes)   # [G, N, K], 16-bit operands, fp32 accumulation
-        return da, db, None
+            if ctx.fp8_wgrad:
+                from .FP8.k_grouped_gemm_block_scaled import fp8_wgrad
+
+                db = fp8_wgrad(grad.to(torch.bfloat16), a, sizes).to(b.dtype)   # [G, N, K] from e4m3 operands
+            else:
+                db = k_grouped_gemm(grad, a, sizes)   # [G, N, K], 16-bit operands, fp32 accumulation
+        return da, db, None, None
 
 
-def grouped_gemm_fp8(a: torch.Tensor, b: torch.Tensor, size_per_group: torch.Tensor):
+def grouped_gemm_fp8(a: torch.Tensor, b: torch.Tensor, size_per_group: torch.Tensor, fp8_wgrad: bool = True):
     """``C[rows of g] = a[rows of g] @ b[g].T`` computed in block-scaled FP8 (K and N multiples of
-    128 recommended; K % 16 == 0, N % 8 == 0 required), with an FP8 input gradient and a 16-bit
-    weight gradient.  ``a`` [M, K] and ``b`` [G, N, K] are bf16."""
-    return _GroupedGemmFp8.apply(a, b, size_per_group)
+    128 recommended; K % 16 == 0, N % 8 == 0 required), with an FP8 input gradient and an FP8
+    weight gradient (16-bit when ``fp8_wgrad`` is False or K / N are not multiples of 128).
+    ``a`` [M, K] and ``b`` [G, N, K] are bf16."""
+    return _GroupedGemmFp8.apply(a, b, size_per_group, fp8_wgrad)
