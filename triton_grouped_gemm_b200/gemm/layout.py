@@ -97,7 +97,10 @@ def make_group_starts(size_per_group: SizesLike, *, padded: bool = False, block_
 
 
 def make_deep_gemm_grouped_layout(size_per_group: SizesLike, *, block_m: int = 128, device=None) -> torch.Tensor:
-    """One int32 per padded M row: the expert id on real rows, -1 on padding rows."""
+    """One int32 per padded M row: the expert id on real rows, -1 on padding rows.  The length of
+    the result is data dependent, so this call synchronises the host once (``.item()``) to size
+    it, as the reference does (gemm/layout.py:73-98); the rows themselves are written by a kernel
+    when the sizes live on the device."""
     sizes = as_group_sizes(size_per_group, device=device, dtype=torch.int32)
     padded = round_up_to_alignment(sizes, block_m).to(torch.int64)
     total = int(padded.sum().item())
@@ -146,8 +149,10 @@ def validate_total_m(size_per_group: SizesLike, total_m: int) -> None:
 
 def device_group_metadata(size_per_group: torch.Tensor, block_m: int = 128):
     """(pad_start, pad_end, group_start, group_end, m_indices_pad, M_pad) -- the tuple the
-    reference's ``_build_m_grouped_metadata`` returns (gemm/BF16/m_grouped_gemm_TMA.py:297-326),
-    built without a host synchronisation except for sizing ``m_indices_pad``."""
+    reference's ``_build_m_grouped_metadata`` returns (gemm/BF16/m_grouped_gemm_TMA.py:297-326).
+    Kept for benchmark code that builds it and passes it as ``metadata=``; the B200 kernels never
+    read it.  Like the reference it synchronises the host once (``.item()``, to size
+    ``m_indices_pad``) - the GEMM entry points themselves do not call it and do not synchronise."""
     s = size_per_group.to(torch.int32)
     p = round_up_to_alignment(s, block_m)
     pad_end = p.cumsum(0).to(torch.int32)
