@@ -282,6 +282,28 @@ int b200moe_combine_topk(const void* y, const int64_t* pos, const float* weights
 int b200moe_route_plan(const int64_t* expert, int64_t n, int num_experts, int* counts, int* cursor, int64_t* order,
                        int64_t* pos, void* stream);
 
+/* The same counting sort on a permutation of the expert ids: the sort key of expert e is
+ * key_table[e] (int64 [num_experts], a permutation of 0 .. num_experts-1), counts / cursor / order
+ * are in key order.  An expert-parallel layer uses it to send its pairs chunk by chunk.
+ * No counterpart in the reference. */
+int b200moe_route_plan_mapped(const int64_t* expert, int64_t n, int num_experts, const int64_t* key_table, int* counts,
+                              int* cursor, int64_t* order, int64_t* pos, void* stream);
+
+/* Plan of the peer-memory exchange, on the device (no counterpart in the reference).  Given the
+ * all-gathered pair counts of every rank in key order (counts_all int32 [world, num_experts]), the
+ * permutation in both directions (expert_of_key int32, key_of_expert int64) and this rank's send
+ * order (order, from b200moe_route_plan_mapped) over its routing (expert int64 [n], n = tokens *
+ * top_k), it writes for the buffers laid out [local expert][source rank] on every rank:
+ *   dst_start / send_start int64 [num_experts] (scratch: first row of this rank's pairs of a key in
+ *   the owner's buffers / first position of the key in this rank's send order),
+ *   size_per_group int64 [num_experts / world]: rows of each local expert here,
+ *   token_of_pair int64 [n], dst_rank int32 [n], dst_row int64 [n]: per position of the send order
+ *   (-1 for a slot of a rejected pair). */
+int b200moe_peer_plan(const int* counts_all, const int* expert_of_key, const int64_t* key_of_expert, int world, int me,
+                      int num_experts, const int64_t* order, const int64_t* expert, int64_t n, int top_k,
+                      int64_t* dst_start, int64_t* send_start, int64_t* size_per_group, int64_t* token_of_pair,
+                      int* dst_rank, int64_t* dst_row, void* stream);
+
 /* The same row movers over the buffers of several ranks (peer memory mapped into this process):
  * dst_bases[dst_rank[i]][dst_row[i], :] = src[src_idx[i], :], and
  * out[t, :] = bf16(sum_k weights[t,k] * src_bases[pair_rank[t,k]][pair_row[t,k], :]).

@@ -286,3 +286,71 @@ def test_dropped_routing_pair_is_skipped_not_followed():
     ref = layer.forward(x.to(DEV), idx_ok.to(DEV), w_ok.to(DEV)).cpu()
     assert _lib.device_status() == 0
     assert torch.equal(out, ref)
+
+
+def test_peer_plan_kernels_match_the_host_formulas():
+    """b200moe_route_plan_mapped + b200moe_peer_plan for three pretended ranks on one GPU: counts in
+    key order, the [local expert][source rank] row of every pair and the per-expert row counts equal
+    what plain indexing gives."""
+    import numpy as np
+
+    from triton_grouped_gemm_b200.ep.p2p import _key_tables, chunk_bounds
+
+    lib = _lib.load()
+    stream = torch.cuda.current_stream().cuda_stream
+    world, e_loc, k = 3, 4, 2
+    E = world * e_loc
+    bounds = chunk_bounds(e_loc, 3)                      # uneven chunks of the local experts
+    key_h, inv_h, key_d, inv_d = _key_tables(world, e_loc, tuple(bounds), torch.device(DEV))
+    gen = torch.Generator().manual_seed(12)
+    routing = [torch.randint(0, E, (37 + 5 * r, k), generator=gen) for r in range(world)]
+    routing[2][4, 1] = -1                                # a dropped pair on rank 2
+    counts, orders, flats = [], [], []
+    for r in range(world):
+        flat = routing[r].reshape(-1).to(DEV)
+        n = flat.numel()
+        c = torch.empty(E, dtype=torch.int32, device=DEV)
+        cur = torch.empty(E, dtype=torch.int32, device=DEV)
+        order = torch.empty(n, dtype=torch.int64, device=DEV)
+        pos = torch.empty(n, dtype=torch.int64, device=DEV)
+        _lib.check(lib.b200moe_route_plan_mapped(flat.data_ptr(), n, E, key_d.data_ptr(), c.data_ptr(), cur.data_ptr(),
+                                                 order.data_ptr(), pos.data_ptr(), stream), "route_plan_mapped")
+        counts.append(c)
+        orders.append(order)
+        flats.append(flat)
+        ok = (routing[r].reshape(-1) >= 0)
+        ref_counts = np.bincount(key_h[routing[r].reshape(-1)[ok].numpy()], minlength=E)
+        assert c.cpu().tolist() == ref_counts.tolist()
+    assert _lib.device_status() == 1 << 5                # the dropped pair was flagged
+    counts_all = torch.stack(counts).contiguous()        # [s, key]
+    ca = counts_all.cpu().numpy()[:, key_h].reshape(world, world, e_loc)   # [s, d, l]
+    for me in range(world):
+        n = flats[me].numel()
+        scratch = torch.empty(2 * E + e_loc, dtype=torch.int64, device=DEV)
+        tok = torch.empty(n, dtype=torch.int64, device=DEV)
+        dr = torch.empty(n, dtype=torch.int32, device=DEV)
+        drow = torch.empty(n, dtype=torch.int64, device=DEV)
+        _lib.check(lib.b200moe_peer_plan(counts_all.data_ptr(), inv_d.data_ptr(), key_d.data_ptr(), world, me, E,
+                                         orders[me].data_ptr(), flats[me].data_ptr(), n, k, scratch.data_ptr(),
+                                         scratch[E:].data_ptr(), scratch[2 * E:].data_ptr(), tok.data_ptr(),
+                                         dr.data_ptr(), drow.data_ptr(), stream), "peer_plan")
+        torch.cuda.synchronize()
+        assert scratch[2 * E:].cpu().tolist() == ca[:, me, :].sum(axis=0).tolist()          # rows per local expert
+        order = orders[me].cpu().numpy()
+        flat = flats[me].cpu().numpy()
+        my_counts = counts_all[me].cpu().numpy()
+        send_start = my_counts.cumsum() - my_counts
+        seen = {}
+        for i in range(n):
+            p = order[i]
+            if p < 0:
+                assert tok[i].item() == -1 and dr[i].item() == -1
+                continue
+            e = flat[p]
+            d, l = divmod(e, e_loc)
+            key = key_h[e]
+            before = ca[:, d, :l].sum() + ca[:me, d, l].sum()                               # [l][s] layout at rank d
+            assert tok[i].item() == p // k and dr[i].item() == d
+            assert drow[i].item() == before + (i - send_start[key])
+            assert (d, drow[i].item()) not in seen
+            seen[(d, drow[i].item())] = True

@@ -98,9 +98,6 @@ fp8_block_m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
   auto xchg_empty_bar = [&](int q) { return bar_base + 8u * (2 * kStages + 12 + q); };
   volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(smem + L::kBarOffset + L::kNumBars * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kBarOffset + L::kNumBars * 8 + 4);
-#ifdef B200_EXP_RELAY
-  volatile unsigned* drain_cnt = reinterpret_cast<volatile unsigned*>(smem + L::kBarOffset + L::kNumBars * 8 + 8);
-#endif
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -119,12 +116,7 @@ fp8_block_m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tmem_full_bar(a), 1);
-#ifdef B200_EXP_RELAY
-      mbar_init(tmem_empty_bar(a), kCtas);
-      drain_cnt[a] = 0u;
-#else
       mbar_init(tmem_empty_bar(a), L::kPromoWarps * kCtas);
-#endif
       mbar_init(scale_full_bar(a), 1);
       mbar_init(scale_empty_bar(a), L::kPromoWarps);
     }
@@ -224,11 +216,7 @@ fp8_block_m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
       for (int kb = 0; kb < num_kb; ++kb, ++it) {
         const uint32_t buf = it & 1u;
         const uint32_t buf_phase = (it >> 1) & 1u;
-#ifdef B200_EXP_MMA_SPIN
-        if (!wait_bounded_spin(tmem_empty_bar(buf), buf_phase ^ 1u, abort_flag, status, kDevTimeoutMma) ||
-#else
         if (!wait_bounded(tmem_empty_bar(buf), buf_phase ^ 1u, abort_flag, status, kDevTimeoutMma) ||
-#endif
             !wait_bounded(full_bar(stage), phase, abort_flag, status, kDevTimeoutMma)) {
           ok = false;
           break;
@@ -260,40 +248,6 @@ fp8_block_m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
       }
     }
   }
-#ifdef B200_EXP_RELAY
-  else {
-    // warps 2 / 3: relay "every promotion warp of this CTA has drained buffer b" to the leader's barrier
-    GroupWalker w;
-    w.init(sizes, sizes_i64, num_groups, masked_stride, kTileM, m_rows);
-    const uint32_t b = static_cast<uint32_t>(warp - 2);
-    uint32_t it = 0, uses = 0;
-    bool ok = true;
-    for (int tile = first_tile; ok; tile += tile_step) {
-      const int mt = tile / n_tiles;
-      if (!w.seek(mt)) break;
-      for (int kb = 0; kb < num_kb && ok; ++kb, ++it) {
-        if ((it & 1u) != b) continue;
-        const unsigned target = static_cast<unsigned>(L::kPromoWarps) * (++uses);
-        uint32_t spins = 0;
-        uint64_t t0 = 0;
-        while (static_cast<int>(drain_cnt[b] - target) < 0) {
-          if ((++spins & 255u) == 0u) {
-            if (*abort_flag) { ok = false; break; }
-            const uint64_t now = global_timer_ns();
-            if (t0 == 0) t0 = now;
-            if (now - t0 > kWaitLimitNs) { *abort_flag = 1; if (status) atomicOr(status, kDevTimeoutPromote); ok = false; break; }
-          }
-        }
-        if (!ok) break;
-        if (lane == 0) {
-          if (kPair && rank != 0) mbar_arrive_cluster(tmem_empty_bar(b), 0);
-          else mbar_arrive(tmem_empty_bar(b));
-        }
-        __syncwarp();
-      }
-    }
-  }
-#endif
   } else {
     // ------------------------------------------------------------ promotion + epilogue
     if constexpr (L::kRebalance) warpgroup_reg_inc<224>();
@@ -400,19 +354,9 @@ fp8_block_m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
         // every column of this buffer is in registers now: hand it back to the MMA warp
         tc_fence_before_sync();
         __syncwarp();
-#ifdef B200_EXP_RELAY
-        if (lane == 0) atomicAdd(const_cast<unsigned*>(&drain_cnt[buf]), 1u);
-        if (false) {
-#else
         if (lane == 0) {
-#endif
-#ifdef B200_EXP_LOCAL_ARRIVE
-          if (kPair && rank != 0) mbar_arrive_cluster(tmem_empty_bar(buf), 0);
-          else mbar_arrive(tmem_empty_bar(buf));
-#else
           if constexpr (kPair) mbar_arrive_cluster(tmem_empty_bar(buf), 0);
           else mbar_arrive(tmem_empty_bar(buf));
-#endif
         }
 #pragma unroll
         for (int j = 0; j < 32; ++j) fma_f32x2(acc2[32 + j], s2, pack_f32x2(t[2 * j], t[2 * j + 1]));

@@ -92,7 +92,8 @@ constexpr int kPlanItems = 8;        // pairs per thread
 constexpr int kPlanMaxExperts = 1024;
 
 __global__ void __launch_bounds__(kPlanThreads)
-route_count_kernel(const long long* __restrict__ expert, long long n, int num_experts, int* __restrict__ counts) {
+route_count_kernel(const long long* __restrict__ expert, long long n, int num_experts,
+                   const long long* __restrict__ key_table, int* __restrict__ counts) {
   __shared__ int hist[kPlanMaxExperts];
   for (int e = threadIdx.x; e < num_experts; e += kPlanThreads) hist[e] = 0;
   __syncthreads();
@@ -101,8 +102,11 @@ route_count_kernel(const long long* __restrict__ expert, long long n, int num_ex
   for (int j = 0; j < kPlanItems; ++j) {
     const long long i = base + j * kPlanThreads + threadIdx.x;
     if (i < n) {
-      const long long e = expert[i];
-      if (e >= 0 && e < num_experts) atomicAdd(&hist[e], 1);
+      long long e = expert[i];
+      if (e >= 0 && e < num_experts) {
+        if (key_table) e = key_table[e];  // sort by a permutation of the expert ids instead
+        atomicAdd(&hist[e], 1);
+      }
     }
   }
   __syncthreads();
@@ -127,7 +131,8 @@ route_scan_kernel(const int* __restrict__ counts, int num_experts, int* __restri
 }
 
 __global__ void __launch_bounds__(kPlanThreads)
-route_scatter_kernel(const long long* __restrict__ expert, long long n, int num_experts, int* __restrict__ cursor,
+route_scatter_kernel(const long long* __restrict__ expert, long long n, int num_experts,
+                     const long long* __restrict__ key_table, int* __restrict__ cursor,
                      long long* __restrict__ order, long long* __restrict__ pos, unsigned* status) {
   __shared__ int hist[kPlanMaxExperts];   // first: this block's count per expert; then: next free position
   for (int e = threadIdx.x; e < num_experts; e += kPlanThreads) hist[e] = 0;
@@ -139,8 +144,9 @@ route_scatter_kernel(const long long* __restrict__ expert, long long n, int num_
     const long long i = base + j * kPlanThreads + threadIdx.x;
     ex[j] = -1;
     if (i < n) {
-      const long long e = expert[i];
+      long long e = expert[i];
       if (e >= 0 && e < num_experts) {
+        if (key_table) e = key_table[e];
         ex[j] = e;
         atomicAdd(&hist[e], 1);
       } else if (status) {
@@ -389,6 +395,63 @@ combine_topk_multi_kernel(PeerBases bases, const int* __restrict__ rank, const l
   }
 }
 
+// ---- plan of the peer-memory exchange, on the device -----------------------------------------
+// After the all-gather of every rank's per-key pair counts (keys = a fixed permutation of the
+// global expert ids that makes the send order chunk-major), one block derives what this rank needs
+// to address the other ranks' buffers, which are laid out [local expert][source rank]:
+//   dst_start[key]   first row, in the owning rank's buffers, of THIS rank's pairs with that key
+//   send_start[key]  first position of that key in this rank's send order
+//   size_per_group[l]  rows of local expert l here, all sources together
+__global__ void __launch_bounds__(1024)
+peer_layout_kernel(const int* __restrict__ counts_all /* [world, E] by key */, const int* __restrict__ expert_of_key,
+                   const long long* __restrict__ key_of_expert, int world, int me, int e_loc, int num_experts,
+                   long long* __restrict__ dst_start, long long* __restrict__ send_start,
+                   long long* __restrict__ size_per_group) {
+  for (int key = threadIdx.x; key < num_experts; key += blockDim.x) {
+    const int e = expert_of_key[key];
+    const int d = e / e_loc, l = e - d * e_loc;
+    long long before = 0;
+    for (int l2 = 0; l2 <= l; ++l2) {
+      const long long k2 = key_of_expert[d * e_loc + l2];
+      const int s_end = l2 < l ? world : me;  // whole earlier experts, then the lower source ranks of this one
+      for (int s = 0; s < s_end; ++s) before += counts_all[static_cast<long long>(s) * num_experts + k2];
+    }
+    dst_start[key] = before;
+    long long mine = 0;
+    for (int k2 = 0; k2 < key; ++k2) mine += counts_all[static_cast<long long>(me) * num_experts + k2];
+    send_start[key] = mine;
+  }
+  for (int l = threadIdx.x; l < e_loc; l += blockDim.x) {
+    const long long k2 = key_of_expert[me * e_loc + l];
+    long long rows = 0;
+    for (int s = 0; s < world; ++s) rows += counts_all[static_cast<long long>(s) * num_experts + k2];
+    size_per_group[l] = rows;
+  }
+}
+
+// per position i of the send order: the pair's token, owning rank and row in the owner's buffers
+// (a slot of the order that holds -1 - a rejected pair - becomes token -1, which the movers skip)
+__global__ void __launch_bounds__(256)
+peer_pairs_kernel(const long long* __restrict__ order, const long long* __restrict__ expert,
+                  const long long* __restrict__ key_of_expert, const long long* __restrict__ dst_start,
+                  const long long* __restrict__ send_start, long long n, int top_k, int e_loc, int num_experts,
+                  long long* __restrict__ token_of_pair, int* __restrict__ dst_rank, long long* __restrict__ dst_row) {
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const long long p = order[i];
+  long long e = p >= 0 && p < n ? expert[p] : -1;
+  if (e < 0 || e >= num_experts) {
+    token_of_pair[i] = -1;
+    dst_rank[i] = -1;
+    dst_row[i] = -1;
+    return;
+  }
+  const long long key = key_of_expert[e];
+  token_of_pair[i] = p / top_k;
+  dst_rank[i] = static_cast<int>(e / e_loc);
+  dst_row[i] = dst_start[key] + (i - send_start[key]);
+}
+
 static int fill_bases(PeerBases* out, const void* const* bases, int world, const char* who) {
   B200_REQUIRE(world >= 1 && world <= kMaxPeers, "%s: world (%d) must be in [1, %d]", who, world, kMaxPeers);
   B200_REQUIRE(bases, "%s: null pointer table", who);
@@ -405,10 +468,56 @@ static int fill_bases(PeerBases* out, const void* const* bases, int world, const
 
 extern "C" {
 
+static int route_plan_impl(const int64_t* expert, int64_t n, int num_experts, const int64_t* key_table, int* counts,
+                           int* cursor, int64_t* order, int64_t* pos, void* stream_v, const char* who);
+
 int b200moe_route_plan(const int64_t* expert, int64_t n, int num_experts, int* counts, int* cursor, int64_t* order,
                        int64_t* pos, void* stream_v) {
+  return route_plan_impl(expert, n, num_experts, nullptr, counts, cursor, order, pos, stream_v, "b200moe_route_plan");
+}
+
+int b200moe_route_plan_mapped(const int64_t* expert, int64_t n, int num_experts, const int64_t* key_table, int* counts,
+                              int* cursor, int64_t* order, int64_t* pos, void* stream_v) {
+  if (!key_table) return b200::set_error(b200::kErrInvalidArgument, "b200moe_route_plan_mapped: key_table is null");
+  return route_plan_impl(expert, n, num_experts, key_table, counts, cursor, order, pos, stream_v,
+                         "b200moe_route_plan_mapped");
+}
+
+int b200moe_peer_plan(const int* counts_all, const int* expert_of_key, const int64_t* key_of_expert, int world, int me,
+                      int num_experts, const int64_t* order, const int64_t* expert, int64_t n, int top_k,
+                      int64_t* dst_start, int64_t* send_start, int64_t* size_per_group, int64_t* token_of_pair,
+                      int* dst_rank, int64_t* dst_row, void* stream_v) {
   using namespace b200;
-  const char* who = "b200moe_route_plan";
+  const char* who = "b200moe_peer_plan";
+  B200_REQUIRE(world >= 1 && world <= kMaxPeers && me >= 0 && me < world, "%s: bad world / rank (%d, %d)", who, world, me);
+  B200_REQUIRE(num_experts > 0 && num_experts <= kPlanMaxExperts && num_experts % world == 0,
+               "%s: num_experts (%d) must be a multiple of world, at most %d", who, num_experts, kPlanMaxExperts);
+  B200_REQUIRE(n >= 0 && top_k > 0, "%s: bad pair count / top_k", who);
+  B200_REQUIRE(counts_all && expert_of_key && key_of_expert && dst_start && send_start && size_per_group,
+               "%s: null pointer", who);
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  const int e_loc = num_experts / world;
+  peer_layout_kernel<<<1, 1024, 0, stream>>>(counts_all, expert_of_key, reinterpret_cast<const long long*>(key_of_expert),
+                                             world, me, e_loc, num_experts, reinterpret_cast<long long*>(dst_start),
+                                             reinterpret_cast<long long*>(send_start),
+                                             reinterpret_cast<long long*>(size_per_group));
+  if (n > 0) {
+    B200_REQUIRE(order && expert && token_of_pair && dst_rank && dst_row, "%s: null pointer", who);
+    const long long blocks = (n + 255) / 256;
+    B200_REQUIRE(blocks < (1ll << 31), "%s: too many pairs", who);
+    peer_pairs_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(
+        reinterpret_cast<const long long*>(order), reinterpret_cast<const long long*>(expert),
+        reinterpret_cast<const long long*>(key_of_expert), reinterpret_cast<const long long*>(dst_start),
+        reinterpret_cast<const long long*>(send_start), n, top_k, e_loc, num_experts,
+        reinterpret_cast<long long*>(token_of_pair), dst_rank, reinterpret_cast<long long*>(dst_row));
+  }
+  B200_CUDA(cudaGetLastError());
+  return 0;
+}
+
+static int route_plan_impl(const int64_t* expert, int64_t n, int num_experts, const int64_t* key_table, int* counts,
+                           int* cursor, int64_t* order, int64_t* pos, void* stream_v, const char* who) {
+  using namespace b200;
   B200_REQUIRE(n >= 0 && num_experts > 0 && num_experts <= kPlanMaxExperts, "%s: num_experts (%d) must be in [1, %d]",
                who, num_experts, kPlanMaxExperts);
   B200_REQUIRE(counts && cursor, "%s: null pointer", who);
@@ -423,10 +532,11 @@ int b200moe_route_plan(const int64_t* expert, int64_t n, int num_experts, int* c
     const long long blocks = (n + per_block - 1) / per_block;
     B200_REQUIRE(blocks < (1ll << 31), "%s: too many pairs", who);
     route_count_kernel<<<static_cast<int>(blocks), kPlanThreads, 0, stream>>>(
-        reinterpret_cast<const long long*>(expert), n, num_experts, counts);
+        reinterpret_cast<const long long*>(expert), n, num_experts, reinterpret_cast<const long long*>(key_table), counts);
     route_scan_kernel<<<1, kPlanMaxExperts, 0, stream>>>(counts, num_experts, cursor);
     route_scatter_kernel<<<static_cast<int>(blocks), kPlanThreads, 0, stream>>>(
-        reinterpret_cast<const long long*>(expert), n, num_experts, cursor, reinterpret_cast<long long*>(order),
+        reinterpret_cast<const long long*>(expert), n, num_experts, reinterpret_cast<const long long*>(key_table), cursor,
+        reinterpret_cast<long long*>(order),
         reinterpret_cast<long long*>(pos), device_status_ptr());
   } else {
     route_scan_kernel<<<1, kPlanMaxExperts, 0, stream>>>(counts, num_experts, cursor);

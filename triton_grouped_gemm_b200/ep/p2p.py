@@ -207,8 +207,8 @@ _KEY_TABLES = {}
 def _key_tables(world: int, e_loc: int, bounds: tuple, dev):
     """Sort key of global expert (rank r, local expert l) = its place in (chunk of l, r, l) order, so
     that the send order is chunk-major and, inside a chunk, grouped by destination rank, then
-    expert.  Returns (key_of_expert on the host, its inverse on the host, key_of_expert on ``dev``);
-    cached, the tables depend only on the layer's shape."""
+    expert.  Returns (key_of_expert on the host, its inverse on the host, key_of_expert on ``dev``,
+    the inverse on ``dev`` as int32); cached, the tables depend only on the layer's shape."""
     ck = (world, e_loc, bounds, str(dev))
     if ck not in _KEY_TABLES:
         import numpy as np
@@ -220,7 +220,8 @@ def _key_tables(world: int, e_loc: int, bounds: tuple, dev):
         key_rl = (world * b[:-1][chunk_of_l])[None, :] + np.arange(world)[:, None] * width[None, :] \
             + (l_ids - b[:-1][chunk_of_l])[None, :]                        # [r, l]
         key_h = key_rl.reshape(world * e_loc).astype(np.int64)
-        _KEY_TABLES[ck] = (key_h, np.argsort(key_h), torch.from_numpy(key_h).to(dev))
+        inv_h = np.argsort(key_h)
+        _KEY_TABLES[ck] = (key_h, inv_h, torch.from_numpy(key_h).to(dev), torch.from_numpy(inv_h.astype(np.int32)).to(dev))
     return _KEY_TABLES[ck]
 
 
@@ -237,7 +238,10 @@ def make_peer_chunk_plan(topk_idx: torch.Tensor, num_experts: int, group, capaci
     n = t * k
     dev = topk_idx.device
     flat = topk_idx.reshape(-1).to(torch.int64)
-    key_of_expert_h, expert_of_key, key_of_expert = _key_tables(world, e_loc, tuple(bounds), dev)
+    key_of_expert_h, expert_of_key, key_of_expert, expert_of_key_dev = _key_tables(world, e_loc, tuple(bounds), dev)
+    if flat.is_cuda:
+        return _make_peer_chunk_plan_cuda(flat, t, k, num_experts, group, capacity_rows, list(bounds), key_of_expert_h,
+                                          expert_of_key, key_of_expert, expert_of_key_dev)
     key = key_of_expert[flat.clamp(0, num_experts - 1)]
     key = torch.where((flat >= 0) & (flat < num_experts), key, torch.full_like(key, -1))
     counts_by_key, send_order, pos = route_plan(key, num_experts)
@@ -252,6 +256,22 @@ def make_peer_chunk_plan(topk_idx: torch.Tensor, num_experts: int, group, capaci
     # ---- the one host synchronisation: every rank's per-expert counts (world x num_experts integers);
     # all offsets the host needs follow from them
     ca = counts_flat.cpu().view(world, world, e_loc).numpy()              # [s, d, l]
+    host = _host_tables(ca, world, me, e_loc, num_experts, bounds, capacity_rows, key_of_expert_h, expert_of_key)
+    send_offsets = host["send_offsets"]
+    send_start_by_key = counts_by_key.cumsum(0) - counts_by_key
+    valid = send_order[:send_offsets[-1]]
+    key_sorted = key[valid]
+    e_sorted = flat[valid]
+    idx = torch.arange(valid.numel(), device=dev)
+    dst_rank = (e_sorted // e_loc).to(torch.int32)
+    dst_row = dst_block_start[e_sorted] + (idx - send_start_by_key[key_sorted])
+    return PeerChunkPlan(num_tokens=t, top_k=k, bounds=list(bounds), token_of_pair=(valid // k).contiguous(),
+                         dst_rank=dst_rank.contiguous(), dst_row=dst_row.contiguous(), pos=pos,
+                         size_per_group=size_per_group, **host)
+
+
+def _host_tables(ca, world, me, e_loc, num_experts, bounds, capacity_rows, key_of_expert_h, expert_of_key) -> dict:
+    """Everything the host needs, from every rank's per-expert pair counts ``ca`` [s, d, l] (numpy)."""
     totals = ca.sum(axis=(0, 2))                                          # rows every rank receives
     if int(totals.max()) > capacity_rows:
         raise RuntimeError(f"a rank would receive {int(totals.max())} rows, more than the exchange buffers hold "
@@ -266,43 +286,47 @@ def make_peer_chunk_plan(topk_idx: torch.Tensor, num_experts: int, group, capaci
     ret_row0 = send_start[:, key_of_expert_h[me * e_loc:(me + 1) * e_loc]].T.copy()   # [l, s]
     my_cbk = cbk[me]
     send_offsets = [int(my_cbk[:world * bb].sum()) for bb in bounds]
-    send_start_by_key = counts_by_key.cumsum(0) - counts_by_key
-    valid = send_order[:send_offsets[-1]]
-    key_sorted = key[valid]
-    e_sorted = flat[valid]
-    idx = torch.arange(valid.numel(), device=dev)
-    dst_rank = (e_sorted // e_loc).to(torch.int32)
-    dst_row = dst_block_start[e_sorted] + (idx - send_start_by_key[key_sorted])
-    return PeerChunkPlan(num_tokens=t, top_k=k, bounds=list(bounds), token_of_pair=(valid // k).contiguous(),
-                         dst_rank=dst_rank.contiguous(), dst_row=dst_row.contiguous(), pos=pos,
-                         send_offsets=send_offsets, recv_offsets=recv_offsets, size_per_group=size_per_group,
-                         blk_count=blk_count, blk_start=blk_start, ret_row0=ret_row0)
+    return dict(send_offsets=send_offsets, recv_offsets=recv_offsets, blk_count=blk_count, blk_start=blk_start,
+                ret_row0=ret_row0)
 
 
-def return_blocks_by_copy(ybuf: PeerBuffer, ret: PeerBuffer, plan: PeerChunkPlan, l_lo: int, l_hi: int) -> None:
-    """Results of local experts [l_lo, l_hi) back to their token owners by copy engine: block
-    (expert l, source rank s) is contiguous here ([expert][source] layout) and contiguous in s's
-    return buffer (s sent those pairs consecutively), so each block is one device-to-device copy
-    on the current stream - over NVLink for the other ranks - and no SM is involved."""
-    row_bytes = ybuf.local.shape[1] * ybuf.local.element_size()
-    assert row_bytes == ret.local.shape[1] * ret.local.element_size()
-    dsts, srcs, sizes = [], [], []
-    own = ybuf.local.data_ptr()
-    for l in range(l_lo, l_hi):
-        for s_rank in range(ybuf.world):
-            n = int(plan.blk_count[l, s_rank])
-            if n:
-                assert int(plan.ret_row0[l, s_rank]) + n <= ret.capacity
-                dsts.append(ret.bases[s_rank] + int(plan.ret_row0[l, s_rank]) * row_bytes)
-                srcs.append(own + int(plan.blk_start[l, s_rank]) * row_bytes)
-                sizes.append(n * row_bytes)
-    if not dsts:
-        return
-    m = len(dsts)
-    with torch.cuda.device(ybuf.local.device):
-        rc = _lib.load().b200ipc_copy_many_async(m, (ctypes.c_void_p * m)(*dsts), (ctypes.c_void_p * m)(*srcs),
-                                                 (ctypes.c_int64 * m)(*sizes), _lib.stream_ptr(ybuf.local.device))
-    _lib.check(rc, "b200ipc_copy_many_async")
+def _make_peer_chunk_plan_cuda(flat, t, k, num_experts, group, capacity_rows, bounds, key_of_expert_h, expert_of_key,
+                               key_of_expert, expert_of_key_dev) -> PeerChunkPlan:
+    """The same plan with the library's kernels: a counting sort on the permuted expert ids, the
+    all-gather of the int32 counts, one layout kernel and one per-pair kernel - instead of some
+    thirty small tensor operations."""
+    world, me = dist.get_world_size(group), dist.get_rank(group)
+    e_loc = num_experts // world
+    dev = flat.device
+    n = flat.numel()
+    lib = _lib.load()
+    flat = flat.contiguous()
+    counts = torch.empty(num_experts, dtype=torch.int32, device=dev)
+    cursor = torch.empty(num_experts, dtype=torch.int32, device=dev)
+    order = torch.empty(n, dtype=torch.int64, device=dev)
+    pos = torch.empty(n, dtype=torch.int64, device=dev)
+    counts_all = torch.empty(world * num_experts, dtype=torch.int32, device=dev)
+    scratch = torch.empty(2 * num_experts + e_loc, dtype=torch.int64, device=dev)
+    token_of_pair = torch.empty(n, dtype=torch.int64, device=dev)
+    dst_rank = torch.empty(n, dtype=torch.int32, device=dev)
+    dst_row = torch.empty(n, dtype=torch.int64, device=dev)
+    stream = _lib.stream_ptr(dev)
+    with torch.cuda.device(dev):
+        rc = lib.b200moe_route_plan_mapped(flat.data_ptr(), n, num_experts, key_of_expert.data_ptr(), counts.data_ptr(),
+                                           cursor.data_ptr(), order.data_ptr(), pos.data_ptr(), stream)
+        _lib.check(rc, "b200moe_route_plan_mapped")
+        dist.all_gather_into_tensor(counts_all, counts, group=group)       # [s, key]
+        size_per_group = scratch[2 * num_experts:]
+        rc = lib.b200moe_peer_plan(counts_all.data_ptr(), expert_of_key_dev.data_ptr(), key_of_expert.data_ptr(), world, me,
+                                   num_experts, order.data_ptr(), flat.data_ptr(), n, k, scratch.data_ptr(),
+                                   scratch[num_experts:].data_ptr(), size_per_group.data_ptr(), token_of_pair.data_ptr(),
+                                   dst_rank.data_ptr(), dst_row.data_ptr(), stream)
+        _lib.check(rc, "b200moe_peer_plan")
+    # ---- the one host synchronisation (world x num_experts int32); by global expert for the host tables
+    ca = counts_all.cpu().view(world, num_experts).numpy()[:, key_of_expert_h].reshape(world, world, e_loc)
+    host = _host_tables(ca, world, me, e_loc, num_experts, bounds, capacity_rows, key_of_expert_h, expert_of_key)
+    return PeerChunkPlan(num_tokens=t, top_k=k, bounds=list(bounds), token_of_pair=token_of_pair, dst_rank=dst_rank,
+                         dst_row=dst_row, pos=pos, size_per_group=size_per_group, **host)
 
 
 def dispatch_quant_range(x: torch.Tensor, plan: PeerChunkPlan, lo: int, hi: int, rows8: PeerBuffer,
