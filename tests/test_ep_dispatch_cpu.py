@@ -322,3 +322,19 @@ def test_two_gloo_ranks_pipelined_peer_memory_plan():
             p.join(120)
             assert p.exitcode == 0
         assert results.get(0) is True and results.get(1) is True
+
+
+def test_layer_module_finds_every_helper_it_imports_lazily():
+    """The layer imports its transport helpers inside the forward paths (they need a GPU to run);
+    a missing name must show up here, on the CPU, not on the first multi-GPU step."""
+    import ast
+    import inspect
+
+    from triton_grouped_gemm_b200.ep import dispatch, moe_layer, p2p
+
+    tree = ast.parse(inspect.getsource(moe_layer))
+    for node in ast.walk(tree):
+        if isinstance(node, ast.ImportFrom) and node.module in ("p2p", "dispatch") and node.level == 1:
+            mod = p2p if node.module == "p2p" else dispatch
+            for alias in node.names:
+                assert hasattr(mod, alias.name), f"{node.module}.{alias.name} is imported by moe_layer but not defined"

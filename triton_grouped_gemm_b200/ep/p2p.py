@@ -329,6 +329,32 @@ def _make_peer_chunk_plan_cuda(flat, t, k, num_experts, group, capacity_rows, bo
                          dst_row=dst_row, pos=pos, size_per_group=size_per_group, **host)
 
 
+def return_blocks_by_copy(ybuf: PeerBuffer, ret: PeerBuffer, plan: PeerChunkPlan, l_lo: int, l_hi: int) -> None:
+    """Results of local experts [l_lo, l_hi) back to their token owners by copy engine: block
+    (expert l, source rank s) is contiguous here ([expert][source] layout) and contiguous in s's
+    return buffer (s sent those pairs consecutively), so each block is one device-to-device copy
+    on the current stream - over NVLink for the other ranks - and no SM is involved."""
+    row_bytes = ybuf.local.shape[1] * ybuf.local.element_size()
+    assert row_bytes == ret.local.shape[1] * ret.local.element_size()
+    dsts, srcs, sizes = [], [], []
+    own = ybuf.local.data_ptr()
+    for l in range(l_lo, l_hi):
+        for s_rank in range(ybuf.world):
+            n = int(plan.blk_count[l, s_rank])
+            if n:
+                assert int(plan.ret_row0[l, s_rank]) + n <= ret.capacity
+                dsts.append(ret.bases[s_rank] + int(plan.ret_row0[l, s_rank]) * row_bytes)
+                srcs.append(own + int(plan.blk_start[l, s_rank]) * row_bytes)
+                sizes.append(n * row_bytes)
+    if not dsts:
+        return
+    m = len(dsts)
+    with torch.cuda.device(ybuf.local.device):
+        rc = _lib.load().b200ipc_copy_many_async(m, (ctypes.c_void_p * m)(*dsts), (ctypes.c_void_p * m)(*srcs),
+                                                 (ctypes.c_int64 * m)(*sizes), _lib.stream_ptr(ybuf.local.device))
+    _lib.check(rc, "b200ipc_copy_many_async")
+
+
 def dispatch_quant_range(x: torch.Tensor, plan: PeerChunkPlan, lo: int, hi: int, rows8: PeerBuffer,
                          scales: PeerBuffer, meta: PeerBuffer, blocks: int = 0) -> None:
     """Pairs [lo, hi) of the send order: quantise each pair's token row of ``x`` (bf16 / fp16
