@@ -597,7 +597,8 @@ def summarise_phases(marks, chunks):
     return out
 
 
-def ep_leg(dev, rank, world, steps, warmup, chunks, comm_sms, qod=False, return_path="copy", transports=("p2p", "nccl")):
+def ep_leg(dev, rank, world, steps, warmup, chunks, comm_sms, qod=False, return_path="copy", transports=("p2p", "nccl"),
+           taper=False):
     """The expert-parallel FP8 MoE layer of the benchmark configuration on this process group:
     128 experts split over the ranks, 81 920 tokens x hidden 4096 per rank, top-8, intermediate
     1536; dispatch and combine over NVLink inside every step.  Both transports are timed (max over
@@ -655,7 +656,7 @@ def ep_leg(dev, rank, world, steps, warmup, chunks, comm_sms, qod=False, return_
     work_rank = 2.0 * tokens * TOP_K * (2 * inter * hidden + hidden * inter)
     for transport, ch in [tc for tc in (("p2p", chunks), ("nccl", 4)) if tc[0] in transports]:
         layer = Fp8MoELayer(w13, w2, NUM_EXPERTS, group, chunks=ch, comm_sms=comm_sms, transport=transport,
-                            tokens_per_rank=tokens, top_k=TOP_K, quantise_on_dispatch=qod, return_path=return_path)
+                            tokens_per_rank=tokens, top_k=TOP_K, quantise_on_dispatch=qod, return_path=return_path, taper=taper)
         dist.barrier()
         per = timed_steps(lambda: layer.forward(x, idx, w), steps, max(warmup, 3))
         ms = max_over_ranks(statistics.mean(per))
@@ -796,7 +797,7 @@ def run_b200(args):
     _lib.load()
     if args.ep_only and use_dist:
         ep = ep_leg(dev, rank, world, min(args.steps, 8), 3, args.ep_chunks, args.ep_comm_sms, args.ep_quantise_on_dispatch, args.ep_return_path,
-                    transports=("p2p",) if args.ep_skip_nccl else ("p2p", "nccl"))
+                    transports=("p2p",) if args.ep_skip_nccl else ("p2p", "nccl"), taper=args.ep_taper)
         if rank == 0:
             print(json.dumps({"ep_only": True, "n_gpus": world, "ep": ep}), flush=True)
         dist.barrier()
@@ -1128,6 +1129,7 @@ def main():
                     help="expert-parallel p2p transport: quantise each pair's bf16 row inside the dispatch kernel")
     ap.add_argument("--ep-return-path", choices=["copy", "kernel"], default="copy",
                     help="expert-parallel p2p transport: results go home by copy engine (copy) or by the mover kernel")
+    ap.add_argument("--ep-taper", action="store_true", help="with --ep-only: short first and last expert run")
     ap.add_argument("--ep-skip-nccl", action="store_true", help="with --ep-only: time the p2p transport only")
     ap.add_argument("--ep-only", action="store_true",
                     help="with more than one GPU: run only the expert-parallel leg and print its JSON (tuning runs)")

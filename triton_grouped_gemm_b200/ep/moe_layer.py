@@ -25,7 +25,7 @@ class Fp8MoELayer:
     def __init__(self, w13: torch.Tensor, w2: torch.Tensor, num_experts: int,
                  group: Optional[dist.ProcessGroup] = None, chunks: int = 4, comm_sms: int = 16,
                  transport: str = "nccl", capacity_factor: float = 1.5, tokens_per_rank: int = 0, top_k: int = 0,
-                 quantise_on_dispatch: bool = False, return_path: str = "copy"):
+                 quantise_on_dispatch: bool = False, return_path: str = "copy", taper: bool = False):
         """w13 [E_local, 2*I, H] (gate rows then up rows), w2 [E_local, H, I], bf16, this rank's experts.
         With more than one rank the expert GEMMs consume rows in the order the all-to-all delivers
         them (every [source rank][expert] block is a row group of its own, mapped to its expert's
@@ -44,7 +44,8 @@ class Fp8MoELayer:
         ``return_path`` (pipelined p2p only): "copy" sends every (expert, source rank) block of
         results home with one copy-engine transfer - contiguous on both sides, so the way back
         occupies no SM and the GEMMs keep all but the dispatch movers' SMs; "kernel" uses the
-        return-address mover kernel instead.
+        return-address mover kernel instead.  ``taper``: a first and a last run of experts about half
+        as long as the others.
         Call ``close()`` on every rank when done with a p2p layer."""
         assert w13.dim() == 3 and w2.dim() == 3 and w13.shape[0] == w2.shape[0]
         self.group = group
@@ -84,7 +85,8 @@ class Fp8MoELayer:
             assert self.hidden % 128 == 0, "the p2p transport moves 1x128-quantised rows: hidden must be a multiple of 128"
             cap = (int(tokens_per_rank * top_k * capacity_factor) + 255) // 256 * 256
             dev = w13.device
-            self.bounds = chunk_bounds(self.e_local, self.chunks)
+            self.bounds = chunk_bounds(self.e_local, self.chunks, taper)
+            self.chunks = len(self.bounds) - 1
             self.recv8 = PeerBuffer(cap, self.hidden, torch.uint8, dev, group)
             self.recvs = PeerBuffer(cap, self.hidden // 128, torch.float32, dev, group)
             self.ybuf = PeerBuffer(cap, self.hidden, torch.bfloat16, dev, group)

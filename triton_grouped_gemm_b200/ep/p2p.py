@@ -195,10 +195,22 @@ class PeerChunkPlan:
         return len(self.bounds) - 1
 
 
-def chunk_bounds(e_loc: int, chunks: int) -> List[int]:
-    """Boundaries of `chunks` nearly equal runs of consecutive local experts."""
+def chunk_bounds(e_loc: int, chunks: int, taper: bool = False) -> List[int]:
+    """Boundaries of `chunks` runs of consecutive local experts: nearly equal, or - ``taper`` -
+    with a first and a last run of about half the size of the others (the first dispatch and the
+    last return of a pipelined step have nothing to hide behind, so they are kept short)."""
     chunks = max(1, min(chunks, e_loc))
-    return [(c * e_loc) // chunks for c in range(chunks + 1)]
+    if not taper or chunks < 3 or e_loc < 2 * chunks:
+        return [(c * e_loc) // chunks for c in range(chunks + 1)]
+    # weights 1, 2, 2, ..., 2, 1 over the runs
+    total = 2 * (chunks - 1)
+    acc, bounds = 0, [0]
+    for c in range(chunks):
+        acc += 1 if c in (0, chunks - 1) else 2
+        b = max(bounds[-1] + 1, min(e_loc - (chunks - 1 - c), round(acc * e_loc / total)))
+        bounds.append(b)
+    bounds[-1] = e_loc
+    return bounds
 
 
 _KEY_TABLES = {}
