@@ -213,13 +213,17 @@ int b200gemm_fp8_m_grouped_masked_block(const void* a, const float* a_scale, con
  *   [n_dim/128, m_expand/128] fp32; padded_sizes [G]: padded token count of each expert (the
  *   quantiser's third output), k-blocks of group g = the running prefix / 128; out [G, m_dim, n_dim]
  *   bf16, an expert without tokens gives zeros.  m_dim, n_dim, m_expand multiples of 128.
+ *   workspace: optional device scratch of b200gemm_k_grouped_workspace_bytes(G) bytes (contents need
+ *   no initialisation); with it the tiles are handed out in order of falling token count, which
+ *   balances the CTAs when the experts' token counts differ; NULL = tiles in expert order.
  * The reference ships the quantiser that produces this layout
  * (quant/trans_per_block_quant_expand_128x.py:135-208) but no kernel that consumes it; the
  * skeleton (K-major operands, 128-token blocks, tile -> (group, m tile, n tile)) is that of its
  * per-channel kernel gemm/FP8/k_grouped_gemm_channel_expert.py:64-140. */
 int b200gemm_fp8_k_grouped_block(const void* x8, const float* x_scale, const void* y8, const float* y_scale, void* out,
                                  const void* padded_sizes, int sizes_is_i64, int num_groups, int64_t m_expand,
-                                 int m_dim, int n_dim, int num_sms, void* stream);
+                                 int m_dim, int n_dim, void* workspace, int64_t workspace_bytes, int num_sms,
+                                 void* stream);
 
 /* ---- per-block FP8 (e4m3) quantisers: bytes and fp32 scales identical to the reference's
  *      torch functions ------------------------------------------------------------------ */

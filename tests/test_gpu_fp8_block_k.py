@@ -72,8 +72,9 @@ def test_wgrad_vs_oracle(sizes, k_in, n_out, pair):
     # and close to the unquantised weight gradient (fp8 quantisation noise only)
     full = O.k_grouped_ref(a, dy, st, fp32_accumulate_explicit=True).float()
     assert O.rdiff(out.float(), full) < 0.06
-    # the convenience entry point is the same computation
+    # the convenience entry point is the same computation, and so is the unbalanced tile order
     assert torch.equal(fp8_wgrad(a.to(DEV), dy.to(DEV), st.to(DEV)).cpu(), out)
+    assert torch.equal(k_grouped_fp8_block_scaled((aq, a_s), (gq, g_s), padded, balanced=False).cpu(), out)
 
 
 def test_rejections():
@@ -83,7 +84,7 @@ def test_rejections():
     out = torch.empty(1, 128, 128, dtype=torch.bfloat16, device=DEV)
     sz = torch.tensor([128], device=DEV)
     args = lambda m_expand, m_dim, n_dim: (x.data_ptr(), s.data_ptr(), x.data_ptr(), s.data_ptr(), out.data_ptr(),  # noqa: E731
-                                           sz.data_ptr(), 1, 1, m_expand, m_dim, n_dim, -1, None)
+                                           sz.data_ptr(), 1, 1, m_expand, m_dim, n_dim, None, 0, -1, None)
     assert lib.b200gemm_fp8_k_grouped_block(*args(100, 128, 128)) == -1 and "m_expand" in _lib.last_error()
     assert lib.b200gemm_fp8_k_grouped_block(*args(128, 64, 128)) == -1 and "multiples of 128" in _lib.last_error()
 

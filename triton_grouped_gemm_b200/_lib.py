@@ -53,7 +53,7 @@ _SIGNATURES = {
     "b200gemm_fp8_m_grouped_masked_block": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                             c_int, c_int, c_int, c_int, c_void_p],
     "b200gemm_fp8_k_grouped_block": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64,
-                                     c_int, c_int, c_int, c_void_p],
+                                     c_int, c_int, c_void_p, c_int64, c_int, c_void_p],
     "b200moe_route_plan": [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     "b200moe_route_plan_mapped": [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     "b200moe_peer_plan": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int64, c_int, c_void_p,

@@ -518,6 +518,15 @@ static int launch_plan(const void* sizes, int sizes_is_i64, const int* gs, const
   return 0;
 }
 
+// for the other K-grouped translation units: validate a workspace and queue the plan kernel
+// (starts, token counts, longest-first order) on it; *out = nullptr when no workspace was given
+int k_grouped_plan_into(void* workspace, long long workspace_bytes, const void* sizes, int sizes_is_i64,
+                        int num_groups, const char* who, int** out, cudaStream_t stream) {
+  int rc = check_scratch(workspace, workspace_bytes, num_groups, who, out);
+  if (rc || !*out) return rc;
+  return launch_plan(sizes, sizes_is_i64, nullptr, nullptr, num_groups, *out, stream);
+}
+
 // tile width: 256 output columns unless that leaves SMs without a tile
 static int pick_block_n(int num_groups, int m_dim, int n_dim, int grid) {
   const long long m_tiles = static_cast<long long>(num_groups) * ((m_dim + 127) / 128);

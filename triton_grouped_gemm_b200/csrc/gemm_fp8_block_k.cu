@@ -17,6 +17,9 @@
 // alternate), the promotion warps read it with tcgen05.ld, multiply by the k-block's scalar and
 // accumulate in fp32 registers; after a group's last k-block the accumulators are rounded once
 // and stored with TMA (3-D map over [G, m_dim, n_dim], which clips the m and n tails).
+// Experts differ tenfold in tokens and a tile's cost follows its expert's token count; with a
+// workspace (the K-grouped kernels' plan: starts, token counts, longest-first order) tiles are
+// handed out round-robin in longest-first order, which gives every CTA the same mix.
 //   warp 0   TMA producer      warp 1   MMA issuer (pair: leader CTA only)      warps 2, 3  idle
 //   warps 4..11  promotion + epilogue: warp (quarter = warp % 4, half = (warp - 4) / 4) owns TMEM
 //                lanes [32 quarter, +32) and columns [128 half, +128) = one scale block of y
@@ -84,6 +87,26 @@ struct KBlockWalker {
       nkb = g < num_groups ? load(g) : 0;
     }
   }
+  // Slot `slot` of the tile order.  Without a plan the slot IS the group (walk the sizes).  With a
+  // plan (starts[G], tokens[G], order[G] written by the plan kernel) slot s is the group with the
+  // s-th most tokens: experts differ tenfold in tokens, and handing the tiles out round-robin in
+  // that order gives every CTA the same mix of long and short tiles.  Returns the group.
+  __device__ __forceinline__ int locate(int slot, const int* __restrict__ plan) {
+    if (!plan) {
+      seek(slot);
+      return slot;
+    }
+    const int* starts = plan + kPlanHeaderWords;
+    const int grp = __ldg(starts + 2 * num_groups + slot);
+    long long first = __ldg(starts + grp) >> 7;
+    long long blocks = (static_cast<long long>(__ldg(starts + num_groups + grp)) + 127) >> 7;
+    if (first > kb_total) first = kb_total;
+    if (blocks > kb_total - first) blocks = kb_total - first;
+    g = grp;
+    kb0 = first;
+    nkb = static_cast<int>(blocks);
+    return grp;
+  }
 };
 
 template <bool kPair>
@@ -91,7 +114,8 @@ __global__ void __launch_bounds__(Fp8BlockKCfg<kPair>::kThreads, 1)
 fp8_block_k_grouped_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_y,
                            const __grid_constant__ CUtensorMap tm_c, const float* __restrict__ x_scale,
                            const float* __restrict__ y_scale, const void* __restrict__ sizes, int sizes_i64,
-                           int num_groups, int m_dim, int n_dim, long long kb_total, unsigned* status) {
+                           int num_groups, int m_dim, int n_dim, long long kb_total, const int* __restrict__ plan,
+                           unsigned* status) {
   using L = Fp8BlockKCfg<kPair>;
   constexpr int kBlockN = L::kBlockN;
   constexpr int kStages = L::kStages;
@@ -158,11 +182,11 @@ fp8_block_k_grouped_kernel(const __grid_constant__ CUtensorMap tm_x, const __gri
       uint32_t phase = 0;
       bool ok = true;
       for (long long tile = first_tile; ok && tile < total_tiles; tile += tile_step) {
-        const int g = static_cast<int>(tile / tiles_per_group);
-        const int r = static_cast<int>(tile - static_cast<long long>(g) * tiles_per_group);
+        const int slot = static_cast<int>(tile / tiles_per_group);
+        const int r = static_cast<int>(tile - static_cast<long long>(slot) * tiles_per_group);
         const int mt = r / n_tiles;
         const int nt = r - mt * n_tiles;
-        w.seek(g);
+        w.locate(slot, plan);
         const int row0 = mt * kTileM + static_cast<int>(rank) * kBlockM;
         const int col0 = nt * kBlockN + static_cast<int>(rank) * L::kBRows;
         for (int kb = 0; kb < w.nkb; ++kb) {
@@ -201,7 +225,7 @@ fp8_block_k_grouped_kernel(const __grid_constant__ CUtensorMap tm_x, const __gri
       uint32_t it = 0;  // k-blocks issued so far: TMEM buffer = it & 1
       bool ok = rank == 0;
       for (long long tile = first_tile; ok && tile < total_tiles; tile += tile_step) {
-        w.seek(static_cast<int>(tile / tiles_per_group));
+        w.locate(static_cast<int>(tile / tiles_per_group), plan);
         for (int kb = 0; kb < w.nkb; ++kb, ++it) {
           const uint32_t buf = it & 1u;
           const uint32_t buf_phase = (it >> 1) & 1u;
@@ -249,11 +273,11 @@ fp8_block_k_grouped_kernel(const __grid_constant__ CUtensorMap tm_x, const __gri
     uint8_t* stage_buf = smem + L::kEpiOffset + (warp - 4) * (32 * 128);
     bool ok = true;
     for (long long tile = first_tile; ok && tile < total_tiles; tile += tile_step) {
-      const int g = static_cast<int>(tile / tiles_per_group);
-      const int r = static_cast<int>(tile - static_cast<long long>(g) * tiles_per_group);
+      const int slot = static_cast<int>(tile / tiles_per_group);
+      const int r = static_cast<int>(tile - static_cast<long long>(slot) * tiles_per_group);
       const int mt = r / n_tiles;
       const int nt = r - mt * n_tiles;
-      w.seek(g);
+      const int g = w.locate(slot, plan);
       const int row_w0 = mt * kTileM + static_cast<int>(rank) * kBlockM + quarter * 32;
       const int col_base = nt * kBlockN + half * 128;
       // the k-block's scalar: xs[row block, kb] * ys[column block, kb], the same for the whole warp
@@ -359,7 +383,7 @@ fp8_block_k_grouped_kernel(const __grid_constant__ CUtensorMap tm_x, const __gri
 template <bool kPair>
 static int launch_fp8_block_k(const CUtensorMap& tm_x, const CUtensorMap& tm_y, const CUtensorMap& tm_c,
                               const float* x_scale, const float* y_scale, const void* sizes, int sizes_is_i64,
-                              int num_groups, int m_dim, int n_dim, long long kb_total, int grid,
+                              int num_groups, int m_dim, int n_dim, long long kb_total, const int* plan, int grid,
                               cudaStream_t stream) {
   using L = Fp8BlockKCfg<kPair>;
   auto kern = fp8_block_k_grouped_kernel<kPair>;
@@ -403,10 +427,10 @@ static int launch_fp8_block_k(const CUtensorMap& tm_x, const CUtensorMap& tm_y, 
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     B200_CUDA(cudaLaunchKernelEx(&cfg, kern, tm_x, tm_y, tm_c, x_scale, y_scale, sizes, sizes_is_i64, num_groups, m_dim,
-                                 n_dim, kb_total, device_status_ptr()));
+                                 n_dim, kb_total, plan, device_status_ptr()));
   } else {
     kern<<<grid, L::kThreads, L::kDynamicBytes, stream>>>(tm_x, tm_y, tm_c, x_scale, y_scale, sizes, sizes_is_i64,
-                                                          num_groups, m_dim, n_dim, kb_total, device_status_ptr());
+                                                          num_groups, m_dim, n_dim, kb_total, plan, device_status_ptr());
   }
   B200_CUDA(cudaGetLastError());
   return 0;
@@ -418,7 +442,8 @@ extern "C" {
 
 int b200gemm_fp8_k_grouped_block(const void* x8, const float* x_scale, const void* y8, const float* y_scale, void* out,
                                  const void* padded_sizes, int sizes_is_i64, int num_groups, int64_t m_expand,
-                                 int m_dim, int n_dim, int num_sms, void* stream_v) {
+                                 int m_dim, int n_dim, void* workspace, int64_t workspace_bytes, int num_sms,
+                                 void* stream_v) {
   using namespace b200;
   const char* who = "b200gemm_fp8_k_grouped_block";
   B200_REQUIRE(num_groups >= 0 && m_expand >= 0 && m_dim >= 0 && n_dim >= 0, "%s: negative dimension", who);
@@ -468,11 +493,16 @@ int b200gemm_fp8_k_grouped_block(const void* x8, const float* x_scale, const voi
     if (rc) return rc;
   }
   const long long kb_total = m_expand / 128;
+  int* plan = nullptr;
+  {
+    int rc = k_grouped_plan_into(workspace, workspace_bytes, padded_sizes, sizes_is_i64, num_groups, who, &plan, stream);
+    if (rc) return rc;
+  }
   if (pair)
     return launch_fp8_block_k<true>(tm_x, tm_y, tm_c, x_scale, y_scale, padded_sizes, sizes_is_i64, num_groups, m_dim,
-                                    n_dim, kb_total, grid, stream);
+                                    n_dim, kb_total, plan, grid, stream);
   return launch_fp8_block_k<false>(tm_x, tm_y, tm_c, x_scale, y_scale, padded_sizes, sizes_is_i64, num_groups, m_dim,
-                                   n_dim, kb_total, grid, stream);
+                                   n_dim, kb_total, plan, grid, stream);
 }
 
 }  // extern "C"

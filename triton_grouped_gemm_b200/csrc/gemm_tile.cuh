@@ -148,6 +148,11 @@ template <bool kFp8>
 int launch_k_grouped_pair(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const CUtensorMap& tm_c, void* c,
                           int num_groups, int m_dim, int n_dim, int in_fmt, int out_fp16, const float* a_scale,
                           const float* b_scale, int* scratch, int want_ctas, cudaStream_t stream);
+// Validates a K-grouped workspace and queues the plan kernel on it: scratch[kPlanHeaderWords + ...] =
+// starts[G] (first token of each group), tokens[G], order[G] (groups by falling token count).
+// *out = nullptr when workspace is null (gemm_bf16_k.cu).
+int k_grouped_plan_into(void* workspace, long long workspace_bytes, const void* sizes, int sizes_is_i64,
+                        int num_groups, const char* who, int** out, cudaStream_t stream);
 // -1 = use the pair kernel when the problem is large enough, 0 = never, 1 = whenever possible
 extern int g_cta_pair_mode;
 int pair_kernel_grid();

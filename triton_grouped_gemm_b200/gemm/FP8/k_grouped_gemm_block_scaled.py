@@ -24,10 +24,12 @@ Pair = Tuple[Tensor, Tensor]
 
 
 def k_grouped_fp8_block_scaled(x: Pair, y: Pair, padded_sizes: Tensor, *, out: Optional[Tensor] = None,
-                               num_sms: int = -1) -> Tensor:
+                               num_sms: int = -1, balanced: bool = True) -> Tensor:
     """``padded_sizes`` [G]: each expert's token count rounded up to 128 (the quantiser's third
     output); expert g owns the k-blocks after those of the experts before it.  Returns
-    [G, M_DIM, N_DIM] bf16; an expert without tokens gives a zero matrix."""
+    [G, M_DIM, N_DIM] bf16; an expert without tokens gives a zero matrix.  ``balanced`` hands the
+    tiles out in order of falling token count (a few hundred bytes of scratch from torch's
+    stream-ordered allocator per call); without it they go out in expert order."""
     x8, xs = x
     y8, ys = y
     assert x8.dim() == 2 and y8.dim() == 2 and x8.shape[1] == y8.shape[1], "operands are [dim, M_EXPAND] with the same M_EXPAND"
@@ -44,9 +46,11 @@ def k_grouped_fp8_block_scaled(x: Pair, y: Pair, padded_sizes: Tensor, *, out: O
         out = torch.empty((g, m_dim, n_dim), device=x8.device, dtype=torch.bfloat16)
     assert out.shape == (g, m_dim, n_dim) and out.dtype == torch.bfloat16 and out.is_contiguous()
     sizes, is64 = _lib.sizes_arg(padded_sizes)
+    ws, ws_bytes = _lib.k_grouped_workspace(g, x8.device) if balanced else (None, 0)
     with torch.cuda.device(x8.device):
         rc = _lib.load().b200gemm_fp8_k_grouped_block(_lib.ptr(x8), _lib.ptr(xs), _lib.ptr(y8), _lib.ptr(ys), _lib.ptr(out),
-                                                      _lib.ptr(sizes), is64, g, m_expand, m_dim, n_dim, int(num_sms),
+                                                      _lib.ptr(sizes), is64, g, m_expand, m_dim, n_dim,
+                                                      _lib.ptr(ws) if ws is not None else None, ws_bytes, int(num_sms),
                                                       _lib.stream_ptr(x8.device))
     _lib.check(rc, "b200gemm_fp8_k_grouped_block")
     return out
