@@ -250,7 +250,7 @@ def algorithmic_work(kind, k, n, sizes):
 
 EP_CHUNKS = 8  # set from --ep-chunks
 EP_TRANSPORT = "p2p"  # set from --ep-transport
-EP_COMM_SMS = 16  # set from --ep-comm-sms
+EP_COMM_SMS = 12  # set from --ep-comm-sms
 
 
 def build_step(kind, k, n, trans_b, sizes_dev, inp):
@@ -1123,7 +1123,7 @@ def main():
                          "NCCL all-to-all (nccl)")
     ap.add_argument("--cta-pair", type=int, default=-1, choices=[-1, 0, 1],
                     help="kernel form: -1 chosen by problem size (default), 0 single-CTA tiles, 1 CTA pairs")
-    ap.add_argument("--ep-comm-sms", type=int, default=16,
+    ap.add_argument("--ep-comm-sms", type=int, default=12,
                     help="moe_ep_fp8 with more than one GPU: SMs the expert GEMMs leave to the row movers / collectives")
     ap.add_argument("--ep-quantise-on-dispatch", action="store_true",
                     help="expert-parallel p2p transport: quantise each pair's bf16 row inside the dispatch kernel")

@@ -23,7 +23,7 @@ from .dispatch import combine, dispatch, dispatch_chunk_async, make_chunked_plan
 
 class Fp8MoELayer:
     def __init__(self, w13: torch.Tensor, w2: torch.Tensor, num_experts: int,
-                 group: Optional[dist.ProcessGroup] = None, chunks: int = 4, comm_sms: int = 16,
+                 group: Optional[dist.ProcessGroup] = None, chunks: int = 4, comm_sms: int = 12,
                  transport: str = "nccl", capacity_factor: float = 1.5, tokens_per_rank: int = 0, top_k: int = 0,
                  quantise_on_dispatch: bool = False, return_path: str = "copy", taper: bool = False):
         """w13 [E_local, 2*I, H] (gate rows then up rows), w2 [E_local, H, I], bf16, this rank's experts.
