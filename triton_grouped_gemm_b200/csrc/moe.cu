@@ -42,41 +42,88 @@ gather_rows_kernel(const uint4* __restrict__ src, const long long* __restrict__ 
   }
 }
 
-// out[t, :] = bf16( sum_k w[t,k] * y[pos[t,k], :] ), fp32 accumulation in k order
+// out[t, :] = bf16( sum_k w[t,k] * y[pos[t,k], :] ), fp32 accumulation in k order.
+// kTopK > 0: top_k known at compile time - the k rows' loads of a 16-byte column chunk are all
+// issued before the first multiply-add, so a lane keeps kTopK loads in flight instead of one (the
+// kernel is bound by bytes in flight, not by arithmetic); kTopK == 0: any top_k, one load at a
+// time.  Same operations in the same order either way, so the results are identical.
+template <int kTopK>
 __global__ void __launch_bounds__(kMoeThreads)
 combine_topk_kernel(const uint4* __restrict__ y, const long long* __restrict__ pos, const float* __restrict__ w,
-                    uint4* __restrict__ out, long long tokens, int top_k, int row_vecs, long long y_rows,
+                    uint4* __restrict__ out, long long tokens, int top_k_rt, int row_vecs, long long y_rows,
                     unsigned* status) {
   const int lane = threadIdx.x & 31;
   const long long warp = (static_cast<long long>(blockIdx.x) * kMoeThreads + threadIdx.x) >> 5;
   const long long warps = (static_cast<long long>(gridDim.x) * kMoeThreads) >> 5;
+  const int top_k = kTopK > 0 ? kTopK : top_k_rt;
   for (long long t = warp; t < tokens; t += warps) {
-    for (int v = lane; v < row_vecs; v += 32) {
-      float acc[8];
+    if constexpr (kTopK > 0) {
+      long long yr[kTopK];
+      float wk[kTopK];
+      bool bad = false;
 #pragma unroll
-      for (int e = 0; e < 8; ++e) acc[e] = 0.f;
-      for (int k = 0; k < top_k; ++k) {
-        const long long yr = pos[t * top_k + k];
-        if (yr < 0 || yr >= y_rows) {  // a pair the routing plan rejected: it contributes nothing
-          if (v == lane && lane == 0 && status) atomicOr(status, kDevBadRowIndex);
-          continue;
+      for (int k = 0; k < kTopK; ++k) {
+        yr[k] = pos[t * kTopK + k];
+        wk[k] = w[t * kTopK + k];
+        if (yr[k] < 0 || yr[k] >= y_rows) {  // a pair the routing plan rejected: it contributes nothing
+          yr[k] = -1;
+          bad = true;
         }
-        const uint4 q = __ldg(y + yr * row_vecs + v);
-        const float wk = w[t * top_k + k];
-        const uint32_t p[4] = {q.x, q.y, q.z, q.w};
+      }
+      if (bad && lane == 0 && status) atomicOr(status, kDevBadRowIndex);
+      for (int v = lane; v < row_vecs; v += 32) {
+        uint4 q[kTopK];
+#pragma unroll
+        for (int k = 0; k < kTopK; ++k) q[k] = yr[k] >= 0 ? __ldg(y + yr[k] * row_vecs + v) : make_uint4(0, 0, 0, 0);
+        float acc[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+#pragma unroll
+        for (int k = 0; k < kTopK; ++k) {
+          if (yr[k] < 0) continue;
+          const uint32_t p[4] = {q[k].x, q[k].y, q[k].z, q[k].w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            acc[2 * e] = fmaf(wk[k], __uint_as_float(p[e] << 16), acc[2 * e]);
+            acc[2 * e + 1] = fmaf(wk[k], __uint_as_float(p[e] & 0xFFFF0000u), acc[2 * e + 1]);
+          }
+        }
+        uint32_t o[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          acc[2 * e] = fmaf(wk, __uint_as_float(p[e] << 16), acc[2 * e]);
-          acc[2 * e + 1] = fmaf(wk, __uint_as_float(p[e] & 0xFFFF0000u), acc[2 * e + 1]);
+          __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * e], acc[2 * e + 1]);
+          o[e] = *reinterpret_cast<uint32_t*>(&h);
         }
+        out[t * row_vecs + v] = make_uint4(o[0], o[1], o[2], o[3]);
       }
-      uint32_t o[4];
+    } else {
+      for (int v = lane; v < row_vecs; v += 32) {
+        float acc[8];
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * e], acc[2 * e + 1]);
-        o[e] = *reinterpret_cast<uint32_t*>(&h);
+        for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+        for (int k = 0; k < top_k; ++k) {
+          const long long yr = pos[t * top_k + k];
+          if (yr < 0 || yr >= y_rows) {
+            if (v == lane && lane == 0 && status) atomicOr(status, kDevBadRowIndex);
+            continue;
+          }
+          const uint4 q = __ldg(y + yr * row_vecs + v);
+          const float wk = w[t * top_k + k];
+          const uint32_t p[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            acc[2 * e] = fmaf(wk, __uint_as_float(p[e] << 16), acc[2 * e]);
+            acc[2 * e + 1] = fmaf(wk, __uint_as_float(p[e] & 0xFFFF0000u), acc[2 * e + 1]);
+          }
+        }
+        uint32_t o[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * e], acc[2 * e + 1]);
+          o[e] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        out[t * row_vecs + v] = make_uint4(o[0], o[1], o[2], o[3]);
       }
-      out[t * row_vecs + v] = make_uint4(o[0], o[1], o[2], o[3]);
     }
   }
 }
@@ -734,9 +781,19 @@ int b200moe_combine_topk(const void* y, const int64_t* pos, const float* weights
   B200_REQUIRE(sms > 0, "b200moe_combine_topk: no CUDA device");
   long long blocks = (tokens + kMoeThreads / 32 - 1) / (kMoeThreads / 32);
   if (blocks > 16ll * sms) blocks = 16ll * sms;
-  combine_topk_kernel<<<static_cast<int>(blocks), kMoeThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const uint4*>(y), reinterpret_cast<const long long*>(pos), weights, static_cast<uint4*>(out), tokens,
-      top_k, hidden / 8, y_rows, device_status_ptr());
+#define B200_COMBINE(K)                                                                                              \
+  combine_topk_kernel<K><<<static_cast<int>(blocks), kMoeThreads, 0, static_cast<cudaStream_t>(stream)>>>(           \
+      static_cast<const uint4*>(y), reinterpret_cast<const long long*>(pos), weights, static_cast<uint4*>(out), tokens, \
+      top_k, hidden / 8, y_rows, device_status_ptr())
+  switch (top_k) {
+    case 1: B200_COMBINE(1); break;
+    case 2: B200_COMBINE(2); break;
+    case 4: B200_COMBINE(4); break;
+    case 6: B200_COMBINE(6); break;
+    case 8: B200_COMBINE(8); break;
+    default: B200_COMBINE(0); break;
+  }
+#undef B200_COMBINE
   B200_CUDA(cudaGetLastError());
   return 0;
 }
