@@ -83,6 +83,9 @@ class Fp8MoELayer:
 
             assert tokens_per_rank > 0 and top_k > 0, "the p2p transport sizes its buffers from tokens_per_rank and top_k"
             assert self.hidden % 128 == 0, "the p2p transport moves 1x128-quantised rows: hidden must be a multiple of 128"
+            # the one-shot form moves the scales with the generic 16-byte-vector scatter: 4 * hidden / 128 bytes per row
+            assert self.chunks > 1 or self.hidden % 512 == 0, \
+                "transport='p2p' with chunks=1 needs hidden % 512 == 0 (scale rows of a multiple of 16 bytes); use chunks > 1"
             cap = (int(tokens_per_rank * top_k * capacity_factor) + 255) // 256 * 256
             dev = w13.device
             self.bounds = chunk_bounds(self.e_local, self.chunks, taper)
