@@ -20,7 +20,7 @@ CSRC = PKG / "csrc"
 LIB = PKG / "libb200gemm.so"
 INCLUDE = PKG.parent / "include"
 
-SOURCES = ["api.cu", "gemm_bf16.cu", "gemm_bf16_k.cu", "gemm_pair.cu", "gemm_k_pair.cu", "gemm_fp8_block.cu", "gemm_fp8_block_deep.cu", "gemm_fp8_block_k.cu", "quant.cu", "moe.cu", "layout.cu", "ipc.cu"]
+SOURCES = ["api.cu", "gemm_bf16.cu", "gemm_bf16_k.cu", "gemm_pair.cu", "gemm_k_pair.cu", "gemm_fp8_block.cu", "gemm_fp8_block_k.cu", "quant.cu", "moe.cu", "layout.cu", "ipc.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

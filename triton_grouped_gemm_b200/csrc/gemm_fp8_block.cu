@@ -27,8 +27,6 @@
 // gate half through the two warps' store-staging buffers (mbarrier handshake per tile).
 #include <cuda_bf16.h>
 
-#include <cstdlib>
-
 #include "../../include/b200gemm.h"
 #include "common.cuh"
 #include "gemm_tile.cuh"
@@ -579,11 +577,6 @@ static int launch_fp8_block(const CUtensorMap& tm_a, const CUtensorMap& tm_b, co
   return 0;
 }
 
-int launch_fp8_block_deep(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const CUtensorMap& tm_c, void* c,
-                          const float* a_scale, const float* b_scale, const void* sizes, int sizes_is_i64,
-                          int num_groups, int masked_stride, long long m_rows, int n, int k, const int* b_map, int num_b,
-                          int grid, cudaStream_t stream);
-
 static int fp8_block_common(const void* a, const float* a_scale, const void* b, const float* b_scale, void* c,
                             const void* sizes, int sizes_is_i64, int num_groups, int64_t m_rows, int masked_stride,
                             int n, int k, int num_sms, void* stream_v, const char* who, const int* b_map = nullptr,
@@ -618,9 +611,7 @@ static int fp8_block_common(const void* a, const float* a_scale, const void* b, 
   else if (g_cta_pair_mode == -1)
     pair = block_n == 256 && grid >= 2 && (m_rows / 256) * ((n + 255) / 256) >= grid / 2 &&
            m_rows / 256 >= 4ll * num_groups;
-  static const bool deep_env = getenv("B200GEMM_FP8_DEEP") != nullptr;
-  const bool deep = deep_env && pair && !swiglu;
-  const int b_box_rows = deep ? 64 : (pair ? 128 : block_n);
+  const int b_box_rows = pair ? 128 : block_n;
   CUtensorMap tm_a, tm_b;
   {
     const uint64_t dims[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(m_rows)};
@@ -653,9 +644,6 @@ static int fp8_block_common(const void* a, const float* a_scale, const void* b, 
                          CU_TENSOR_MAP_SWIZZLE_128B, "C");
     if (rc) return rc;
   }
-  if (deep)
-    return launch_fp8_block_deep(tm_a, tm_b, tm_c, c, a_scale, b_scale, sizes, sizes_is_i64, num_groups, masked_stride,
-                                 m_rows, n, k, b_map, num_b, grid, stream);
   // a_scale [m_rows, ceil(k/128)] staged by TMA when its row pitch allows (multiple of 16 bytes)
   const int num_kb = (k + 127) / 128;
   const int scales_by_tma = ((num_kb * 4) % 16 == 0 && (reinterpret_cast<uintptr_t>(a_scale) & 15) == 0) ? 1 : 0;
