@@ -216,8 +216,10 @@ fp8_block_m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
       for (int kb = 0; kb < num_kb; ++kb, ++it) {
         const uint32_t buf = it & 1u;
         const uint32_t buf_phase = (it >> 1) & 1u;
-        if (!wait_bounded(tmem_empty_bar(buf), buf_phase ^ 1u, abort_flag, status, kDevTimeoutMma) ||
-            !wait_bounded(full_bar(stage), phase, abort_flag, status, kDevTimeoutMma)) {
+        // operands first (they are nearly always there), then the drained buffer: the MMAs go out
+        // the moment the promotion warps let go of it
+        if (!wait_bounded(full_bar(stage), phase, abort_flag, status, kDevTimeoutMma) ||
+            !wait_bounded(tmem_empty_bar(buf), buf_phase ^ 1u, abort_flag, status, kDevTimeoutMma)) {
           ok = false;
           break;
         }

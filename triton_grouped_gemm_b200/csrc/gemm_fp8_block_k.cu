@@ -229,8 +229,9 @@ fp8_block_k_grouped_kernel(const __grid_constant__ CUtensorMap tm_x, const __gri
         for (int kb = 0; kb < w.nkb; ++kb, ++it) {
           const uint32_t buf = it & 1u;
           const uint32_t buf_phase = (it >> 1) & 1u;
-          if (!wait_bounded(tmem_empty_bar(buf), buf_phase ^ 1u, abort_flag, status, kDevTimeoutMma) ||
-              !wait_bounded(full_bar(stage), phase, abort_flag, status, kDevTimeoutMma)) {
+          // operands first, then the drained buffer: the MMAs go out the moment it is handed back
+          if (!wait_bounded(full_bar(stage), phase, abort_flag, status, kDevTimeoutMma) ||
+              !wait_bounded(tmem_empty_bar(buf), buf_phase ^ 1u, abort_flag, status, kDevTimeoutMma)) {
             ok = false;
             break;
           }
