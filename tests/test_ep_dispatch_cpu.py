@@ -236,7 +236,8 @@ def _peer_chunk_plan_worker(rank, world, port, results):
         mine = dict(x=x, idx=idx, token_of_pair=plan.token_of_pair, dst_rank=plan.dst_rank, dst_row=plan.dst_row,
                     recv_offsets=plan.recv_offsets, send_offsets=plan.send_offsets,
                     size_per_group=plan.size_per_group, n=int(plan.token_of_pair.numel()), pairs=t * k,
-                    blk_count=plan.blk_count, blk_start=plan.blk_start, ret_row0=plan.ret_row0)
+                    blk_count=plan.blk_count, blk_start=plan.blk_start, ret_row0=plan.ret_row0,
+                    snd_count=plan.snd_count, snd_src0=plan.snd_src0, snd_dst0=plan.snd_dst0)
         everyone = [None] * world
         dist.all_gather_object(everyone, mine)
         bufs = [torch.full((cap, h), float("nan")) for _ in range(world)]
@@ -276,6 +277,22 @@ def _peer_chunk_plan_worker(rank, world, port, results):
                     ok &= bool(torch.equal(pr["x"][int(pr["token_of_pair"][back_pos])], bufs[d][r]))
                     row_expert[d][r] = d * e_loc + l
                 start += nrows
+        # the copy-engine way out: every sender gathers its rows into send order; its pairs for
+        # expert (d, l) are then one contiguous block that lands as block (l, sender) of rank d's
+        # buffer - the same bytes at the same rows as the mover kernel's stores
+        bufs_copy = [torch.full((cap, h), float("nan")) for _ in range(world)]
+        for src, p in enumerate(everyone):
+            send = p["x"][p["token_of_pair"]]
+            ok &= p["snd_count"].shape == (world, e_loc) and int(p["snd_count"].sum()) == p["n"]
+            for c in range(chunks):
+                for d in range(world):
+                    for l in range(bounds[c], bounds[c + 1]):
+                        n_rows, s0, d0 = int(p["snd_count"][d, l]), int(p["snd_src0"][d, l]), int(p["snd_dst0"][d, l])
+                        ok &= p["send_offsets"][c] <= s0 and s0 + n_rows <= p["send_offsets"][c + 1]
+                        bufs_copy[d][d0:d0 + n_rows] = send[s0:s0 + n_rows]
+        for d, p in enumerate(everyone):
+            r_tot = p["recv_offsets"][-1]
+            ok &= bool(torch.equal(bufs_copy[d][:r_tot], bufs[d][:r_tot])) and bool(torch.isnan(bufs_copy[d][r_tot:]).all())
         # results = row * (expert + 1), pushed back through the return addresses, combined locally
         rets = [torch.zeros(p["pairs"], h) for p in everyone]
         for d in range(world):

@@ -15,7 +15,7 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _worker(rank, world, port, transport, chunks, qod, return_path, results):
+def _worker(rank, world, port, transport, chunks, qod, return_path, dispatch_path, results):
     import torch.distributed as dist
 
     from triton_grouped_gemm_b200 import _lib
@@ -33,7 +33,8 @@ def _worker(rank, world, port, transport, chunks, qod, return_path, results):
         e_loc = e // world
         layer = Fp8MoELayer(w13[rank * e_loc:(rank + 1) * e_loc].to(dev), w2[rank * e_loc:(rank + 1) * e_loc].to(dev), e,
                             dist.group.WORLD, transport=transport, chunks=chunks, tokens_per_rank=t, top_k=k,
-                            capacity_factor=2.0, quantise_on_dispatch=qod, return_path=return_path)
+                            capacity_factor=2.0, quantise_on_dispatch=qod, return_path=return_path,
+                            dispatch_path=dispatch_path)
         full = Fp8MoELayer(w13.to(dev), w2.to(dev), e, None)
         worst = 0.0
         for step in range(3):
@@ -51,10 +52,11 @@ def _worker(rank, world, port, transport, chunks, qod, return_path, results):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("transport,chunks,qod,return_path", [
-    ("p2p", 1, False, "copy"), ("p2p", 4, False, "copy"), ("p2p", 3, True, "copy"), ("p2p", 8, True, "kernel"),
-    ("p2p", 4, False, "kernel"), ("nccl", 1, False, "copy"), ("nccl", 4, False, "copy")])
-def test_two_gpu_layer_matches_single_rank(transport, chunks, qod, return_path):
+@pytest.mark.parametrize("transport,chunks,qod,return_path,dispatch_path", [
+    ("p2p", 1, False, "copy", "copy"), ("p2p", 4, False, "copy", "copy"), ("p2p", 3, False, "copy", "copy"),
+    ("p2p", 4, False, "copy", "kernel"), ("p2p", 3, True, "copy", "kernel"), ("p2p", 8, True, "kernel", "kernel"),
+    ("p2p", 4, False, "kernel", "kernel"), ("nccl", 1, False, "copy", "copy"), ("nccl", 4, False, "copy", "copy")])
+def test_two_gpu_layer_matches_single_rank(transport, chunks, qod, return_path, dispatch_path):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
@@ -65,7 +67,7 @@ def test_two_gpu_layer_matches_single_rank(transport, chunks, qod, return_path):
     ctx = mp.get_context("spawn")
     with ctx.Manager() as mgr:
         results = mgr.dict()
-        procs = [ctx.Process(target=_worker, args=(r, 2, port, transport, chunks, qod, return_path, results)) for r in range(2)]
+        procs = [ctx.Process(target=_worker, args=(r, 2, port, transport, chunks, qod, return_path, dispatch_path, results)) for r in range(2)]
         for p in procs:
             p.start()
         for p in procs:

@@ -23,9 +23,10 @@ from .dispatch import combine, dispatch, dispatch_chunk_async, make_chunked_plan
 
 class Fp8MoELayer:
     def __init__(self, w13: torch.Tensor, w2: torch.Tensor, num_experts: int,
-                 group: Optional[dist.ProcessGroup] = None, chunks: int = 4, comm_sms: int = 12,
+                 group: Optional[dist.ProcessGroup] = None, chunks: int = 4, comm_sms: Optional[int] = None,
                  transport: str = "nccl", capacity_factor: float = 1.5, tokens_per_rank: int = 0, top_k: int = 0,
-                 quantise_on_dispatch: bool = False, return_path: str = "copy", taper: bool = False):
+                 quantise_on_dispatch: bool = False, return_path: str = "copy", taper: bool = False,
+                 dispatch_path: str = "kernel"):
         """w13 [E_local, 2*I, H] (gate rows then up rows), w2 [E_local, H, I], bf16, this rank's experts.
         With more than one rank the expert GEMMs consume rows in the order the all-to-all delivers
         them (every [source rank][expert] block is a row group of its own, mapped to its expert's
@@ -44,8 +45,15 @@ class Fp8MoELayer:
         ``return_path`` (pipelined p2p only): "copy" sends every (expert, source rank) block of
         results home with one copy-engine transfer - contiguous on both sides, so the way back
         occupies no SM and the GEMMs keep all but the dispatch movers' SMs; "kernel" uses the
-        return-address mover kernel instead.  ``taper``: a first and a last run of experts about half
-        as long as the others.
+        return-address mover kernel instead.  ``dispatch_path`` (pipelined p2p only): "kernel" (default) moves the
+        rows to their experts with the mover kernels on ``comm_sms`` SMs (12 by default) beside the
+        GEMMs; "copy" gathers every chunk's rows into send order locally and ships each
+        (destination, expert) block with copy-engine transfers too, so that no mover kernel runs beside
+        the GEMMs and they keep every SM but ``comm_sms`` (then 2 by default, for the one-word flag
+        reductions).  It needs the copy return path, rows quantised beforehand and hidden % 512 == 0
+        (else "kernel" is used), and measured slower on two GPUs: the copy engines serve dispatch and
+        return at once and a chunk's dispatch stretches from 0.5 to 2.5 ms.  ``taper``: a first and a last run of
+        experts about half as long as the others.
         Call ``close()`` on every rank when done with a p2p layer."""
         assert w13.dim() == 3 and w2.dim() == 3 and w13.shape[0] == w2.shape[0]
         self.group = group
@@ -65,8 +73,7 @@ class Fp8MoELayer:
         self._w13_interleaved = None   # built by the first decode()
         world = 1 if group is None else dist.get_world_size(group)
         self.world = world
-        self.comm_sms = comm_sms
-        assert transport in ("nccl", "p2p")
+        assert transport in ("nccl", "p2p") and dispatch_path in ("copy", "kernel")
         self.transport = transport if world > 1 else "nccl"
         if self.transport == "nccl":
             while chunks > 1 and self.e_local % chunks:
@@ -76,6 +83,10 @@ class Fp8MoELayer:
         self.quantise_on_dispatch = bool(quantise_on_dispatch)
         assert return_path in ("copy", "kernel")
         self.return_path = return_path
+        self.dispatch_path = dispatch_path if (return_path == "copy" and not quantise_on_dispatch
+                                               and self.hidden % 512 == 0) else "kernel"
+        movers = not (self.transport == "p2p" and self.chunks > 1 and self.dispatch_path == "copy")
+        self.comm_sms = comm_sms if comm_sms is not None else (12 if movers else 2)
         self.trace = False
         self._marks = None
         if self.transport == "p2p":
@@ -101,6 +112,10 @@ class Fp8MoELayer:
                 self.ret = PeerBuffer(tokens_per_rank * top_k, self.hidden, torch.bfloat16, dev, group)
                 self._peer_buffers += [self.meta, self.ret]
                 self._side = (torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev))
+                if self.dispatch_path == "copy":
+                    # this rank's rows in send order, the source of the copy-engine dispatch
+                    self._send8 = torch.empty((tokens_per_rank * top_k, self.hidden), dtype=torch.uint8, device=dev)
+                    self._sends = torch.empty((tokens_per_rank * top_k, self.hidden // 128), dtype=torch.float32, device=dev)
 
     @property
     def w13_interleaved(self):
@@ -228,8 +243,8 @@ class Fp8MoELayer:
         finishes the step.  With ``self.trace`` set, CUDA events bracket every phase on its stream
         (``phase_times()`` reads them)."""
         from .. import _lib
-        from .p2p import (dispatch_quant_range, dispatch_range, make_peer_chunk_plan, return_blocks_by_copy,
-                          return_rows)
+        from .p2p import (dispatch_blocks_by_copy, dispatch_quant_range, dispatch_range, gather_send_rows,
+                          make_peer_chunk_plan, return_blocks_by_copy, return_rows)
 
         lib = _lib.load()
         dev = x.device
@@ -264,7 +279,24 @@ class Fp8MoELayer:
                 lo, hi = plan.send_offsets[c], plan.send_offsets[c + 1]
                 blocks = 0 if c == 0 else background
                 mark(f"dispatch{c}>", s_disp)
-                if self.quantise_on_dispatch:
+                if self.dispatch_path == "copy":
+                    # chunk 0's rows are gathered alone so that its copies start at once; the other
+                    # chunks' rows in one go on the (still idle) return stream, while chunk 0 is on
+                    # the wire and before the first GEMM starts
+                    if c == 0:
+                        gather_send_rows(x8, xs, plan, lo, hi, self._send8, self._sends)
+                        gathered0 = torch.cuda.Event()
+                        gathered0.record(s_disp)
+                        with torch.cuda.stream(s_ret):
+                            s_ret.wait_event(gathered0)
+                            gather_send_rows(x8, xs, plan, hi, plan.send_offsets[-1], self._send8, self._sends)
+                            gathered = torch.cuda.Event()
+                            gathered.record(s_ret)
+                    elif c == 1:
+                        s_disp.wait_event(gathered)
+                    dispatch_blocks_by_copy(self._send8, self._sends, self.recv8, self.recvs, plan,
+                                            self.bounds[c], self.bounds[c + 1])
+                elif self.quantise_on_dispatch:
                     dispatch_quant_range(x, plan, lo, hi, self.recv8, self.recvs, self.meta, blocks=blocks)
                 else:
                     dispatch_range(x8, xs, plan, lo, hi, self.recv8, self.recvs, self.meta, blocks=blocks)

@@ -189,6 +189,9 @@ class PeerChunkPlan:
     blk_count: "object" = None       # host int array [e_loc, world]: rows of block (local expert, source rank) here
     blk_start: "object" = None       # host int array [e_loc, world]: first row of that block in this rank's buffers
     ret_row0: "object" = None        # host int array [e_loc, world]: first row of that block in the SOURCE's return buffer
+    snd_count: "object" = None       # host int array [world, e_loc]: pairs this rank sends to expert l of rank d
+    snd_src0: "object" = None        # host int array [world, e_loc]: where they start in this rank's send order
+    snd_dst0: "object" = None        # host int array [world, e_loc]: first row of that block in rank d's buffers
 
     @property
     def chunks(self) -> int:
@@ -298,8 +301,14 @@ def _host_tables(ca, world, me, e_loc, num_experts, bounds, capacity_rows, key_o
     ret_row0 = send_start[:, key_of_expert_h[me * e_loc:(me + 1) * e_loc]].T.copy()   # [l, s]
     my_cbk = cbk[me]
     send_offsets = [int(my_cbk[:world * bb].sum()) for bb in bounds]
+    # the sender's view of the same blocks: its pairs for expert (d, l) are consecutive in its send
+    # order and land as block (l, me) of rank d's [expert][source] layout
+    snd_count = ca[me].copy()                                             # [d, l]
+    snd_src0 = send_start[me][key_of_expert_h].reshape(world, e_loc).copy()
+    per_dest = ca.transpose(1, 2, 0).reshape(world, e_loc * world)        # [d, (l, s)]
+    snd_dst0 = (per_dest.cumsum(axis=1) - per_dest).reshape(world, e_loc, world)[:, :, me].copy()
     return dict(send_offsets=send_offsets, recv_offsets=recv_offsets, blk_count=blk_count, blk_start=blk_start,
-                ret_row0=ret_row0)
+                ret_row0=ret_row0, snd_count=snd_count, snd_src0=snd_src0, snd_dst0=snd_dst0)
 
 
 def _make_peer_chunk_plan_cuda(flat, t, k, num_experts, group, capacity_rows, bounds, key_of_expert_h, expert_of_key,
@@ -364,6 +373,55 @@ def return_blocks_by_copy(ybuf: PeerBuffer, ret: PeerBuffer, plan: PeerChunkPlan
     with torch.cuda.device(ybuf.local.device):
         rc = _lib.load().b200ipc_copy_many_async(m, (ctypes.c_void_p * m)(*dsts), (ctypes.c_void_p * m)(*srcs),
                                                  (ctypes.c_int64 * m)(*sizes), _lib.stream_ptr(ybuf.local.device))
+    _lib.check(rc, "b200ipc_copy_many_async")
+
+
+def gather_send_rows(x8: torch.Tensor, xs: torch.Tensor, plan: PeerChunkPlan, lo: int, hi: int,
+                     send8: torch.Tensor, sends: torch.Tensor) -> None:
+    """send8[i], sends[i] = the quantised row and the scales of pair i's token, for the pairs [lo, hi) of
+    the send order: the local half of a dispatch by copy engine (two gather kernels, all of HBM's
+    bandwidth, nothing crosses NVLink)."""
+    if hi <= lo:
+        return
+    src = x8.view(torch.uint8) if x8.dtype != torch.uint8 else x8
+    lib = _lib.load()
+    idx = plan.token_of_pair[lo:hi]
+    with torch.cuda.device(src.device):
+        stream = _lib.stream_ptr(src.device)
+        rc = lib.b200moe_gather_rows(src.data_ptr(), idx.data_ptr(), send8[lo:hi].data_ptr(), hi - lo, src.shape[1],
+                                     src.shape[0], stream)
+        _lib.check(rc, "b200moe_gather_rows")
+        rc = lib.b200moe_gather_rows(xs.data_ptr(), idx.data_ptr(), sends[lo:hi].data_ptr(), hi - lo, xs.shape[1] * 4,
+                                     xs.shape[0], stream)
+        _lib.check(rc, "b200moe_gather_rows")
+
+
+def dispatch_blocks_by_copy(send8: torch.Tensor, sends: torch.Tensor, rows8: PeerBuffer, scales: PeerBuffer,
+                            plan: PeerChunkPlan, l_lo: int, l_hi: int) -> None:
+    """The gathered rows of local experts [l_lo, l_hi) of every rank to their owners by copy
+    engine: this rank's pairs for expert (d, l) are consecutive in its send order and form block
+    (l, this rank) of rank d's [expert][source] buffers, so every block is one device-to-device
+    copy of the rows and one of the scales on the current stream; no SM is involved."""
+    row_bytes, scale_bytes = send8.shape[1], sends.shape[1] * 4
+    assert send8.dtype == torch.uint8 and sends.dtype == torch.float32 and send8.is_contiguous() and sends.is_contiguous()
+    assert rows8.local.shape[1] == row_bytes and scales.local.shape[1] * 4 == scale_bytes
+    dsts, srcs, sizes = [], [], []
+    own8, owns = send8.data_ptr(), sends.data_ptr()
+    for d in range(rows8.world):
+        for l in range(l_lo, l_hi):
+            n = int(plan.snd_count[d, l])
+            if n:
+                s0, d0 = int(plan.snd_src0[d, l]), int(plan.snd_dst0[d, l])
+                assert s0 + n <= send8.shape[0] and d0 + n <= rows8.capacity
+                dsts += [rows8.bases[d] + d0 * row_bytes, scales.bases[d] + d0 * scale_bytes]
+                srcs += [own8 + s0 * row_bytes, owns + s0 * scale_bytes]
+                sizes += [n * row_bytes, n * scale_bytes]
+    if not dsts:
+        return
+    m = len(dsts)
+    with torch.cuda.device(send8.device):
+        rc = _lib.load().b200ipc_copy_many_async(m, (ctypes.c_void_p * m)(*dsts), (ctypes.c_void_p * m)(*srcs),
+                                                 (ctypes.c_int64 * m)(*sizes), _lib.stream_ptr(send8.device))
     _lib.check(rc, "b200ipc_copy_many_async")
 
 
