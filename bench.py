@@ -338,9 +338,9 @@ def build_step(kind, k, n, trans_b, sizes_dev, inp):
             x = torch.randn(tokens, k, device=dev, generator=gen, dtype=torch.bfloat16)
             idx, w = synthetic_routing(tokens, NUM_EXPERTS, TOP_K, seed=ROUTING_SEED + rank, device=dev)
             inp.update(x=x, idx=idx, w=w)
-            # kernels of this library per step on one rank: routing plan (3), activation quantiser, two row
-            # gathers, two GEMMs, SwiGLU quantiser, weighted combine (more with several ranks: per-chunk movers)
-            return (lambda: inp.__setitem__("c", layer.forward(x, idx, w))), 10
+            # kernels of this library per step on one rank: routing plan (3), quantise-and-permute, two GEMMs,
+            # SwiGLU quantiser, weighted combine (more with several ranks: per-chunk movers)
+            return (lambda: inp.__setitem__("c", layer.forward(x, idx, w))), 8
         e_loc = sizes_dev.numel()
         x = torch.randn(e_loc * DECODE_M_MAX, k, device=dev, generator=gen, dtype=torch.bfloat16)
         x8, xs = per_token_cast_to_fp8(x)

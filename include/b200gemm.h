@@ -339,6 +339,15 @@ int b200moe_dispatch_quant_rows_multi(const void* x, const int64_t* token_of_pai
                                       const int64_t* dst_row, int64_t first_pair, int64_t num_pairs, int64_t tokens,
                                       int hidden, int dtype, int world, int64_t capacity_rows, int my_rank, int blocks,
                                       void* stream);
+/* Quantise-and-permute on one GPU: row t of x [tokens, hidden] (bf16 / fp16, hidden % 128 == 0,
+ * <= 8192) is quantised 1x128 once - bytes and scales identical to b200quant_act_1x128 - and
+ * written to row pos[t * top_k + j] of dst8 [dst_rows, hidden] (e4m3 bytes) and dst_scales
+ * [dst_rows, hidden/128] for every j < top_k: the activation quantiser and the token permute
+ * (baseline counterpart of the latter: grouped_gemm/csrc/permute.cu, moe_permute_topK_kernel) in
+ * one pass.  A pos outside [0, dst_rows) - the -1 of a rejected pair - is skipped and raises
+ * B200GEMM_DEV_BAD_ROW_INDEX.  No counterpart in the reference's Triton path. */
+int b200moe_quant_scatter_rows(const void* x, int dtype, int64_t tokens, int hidden, const int64_t* pos, int top_k,
+                               void* dst8, float* dst_scales, int64_t dst_rows, void* stream);
 /* The same dispatch for rows that are already quantised: x8 [tokens, hidden] e4m3 bytes and
  * x_scales [tokens, hidden/128] fp32 (as b200quant_act_1x128 writes them) are copied to the
  * pair's row of the owner's buffers together with the return address - one launch per chunk

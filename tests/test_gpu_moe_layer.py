@@ -288,6 +288,40 @@ def test_dropped_routing_pair_is_skipped_not_followed():
     assert torch.equal(out, ref)
 
 
+@pytest.mark.parametrize("t,h,k,dtype", [(257, 512, 4, torch.bfloat16), (96, 4096, 8, torch.bfloat16),
+                                          (65, 8192, 2, torch.float16), (33, 128, 1, torch.bfloat16)])
+def test_quantise_and_permute_in_one_pass_is_bit_exact(t, h, k, dtype):
+    """b200moe_quant_scatter_rows against the quantiser followed by the gather: same bytes, same
+    scales at every row a pair owns; a dropped pair (pos = -1) is skipped and flagged."""
+    from triton_grouped_gemm_b200.ep.dispatch import dispatch, make_plan, quant_permute_rows
+
+    e = 8
+    idx, _ = synthetic_routing(t, e, k, seed=31)
+    if t > 40:
+        idx[7, 0] = -1
+    gen = torch.Generator().manual_seed(32)
+    x = (torch.randn(t, h, generator=gen) * torch.rand(t, 1, generator=gen) * 3).to(dtype).to(DEV)
+    x[3] = 0                                  # an all-zero row: scale floor
+    plan = make_plan(idx.to(DEV), e)
+    _lib.device_status()
+    r8, rs = quant_permute_rows(x, plan.pos, k)
+    status = _lib.device_status()
+    assert status == ((1 << 5) if t > 40 else 0)
+    x8, xs = per_token_cast_to_fp8(x)
+    g8, gs = dispatch(plan, x8), dispatch(plan, xs)
+    status = _lib.device_status()             # the gather skips the dropped pair's slot too
+    n_ok = int(((idx >= 0) & (idx < e)).sum())
+    assert torch.equal(r8[:n_ok].view(torch.uint8), g8[:n_ok].view(torch.uint8))
+    assert torch.equal(rs[:n_ok], gs[:n_ok])
+    # and against the oracle's quantiser at the rows of a few pairs
+    ref8, refs = O.per_token_cast_to_fp8(x.cpu())
+    pos = plan.pos.cpu()
+    for pair in (0, t * k // 2, t * k - 1):
+        if pos[pair] >= 0:
+            assert torch.equal(r8[pos[pair]].cpu().view(torch.uint8), ref8[pair // k].view(torch.uint8))
+            assert torch.equal(rs[pos[pair]].cpu(), refs[pair // k])
+
+
 def test_peer_plan_kernels_match_the_host_formulas():
     """b200moe_route_plan_mapped + b200moe_peer_plan for three pretended ranks on one GPU: counts in
     key order, the [local expert][source rank] row of every pair and the per-expert row counts equal

@@ -77,6 +77,7 @@ _SIGNATURES = {
     "b200layout_psum": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
     "b200layout_grouped_rows": [c_void_p, c_int, c_int, c_int, c_void_p, c_int64, c_void_p],
     "b200moe_gather_rows": [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p],
+    "b200moe_quant_scatter_rows": [c_void_p, c_int, c_int64, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int64, c_void_p],
     "b200moe_combine_topk": [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int64, c_void_p],
     "b200quant_act_1x128": [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_void_p],
     "b200quant_swiglu_act_1x128": [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p],

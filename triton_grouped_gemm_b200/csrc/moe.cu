@@ -329,6 +329,74 @@ dispatch_quant_rows_multi_kernel(const uint4* __restrict__ x, const long long* _
   }
 }
 
+// Quantise-and-permute on one GPU: token t's 16-bit row is quantised 1x128 ONCE and its e4m3 row
+// and scales are written to every row pos[t * top_k + j] of the expert-major buffers - the
+// activation quantiser and the permute in one pass (read T rows, write T * top_k rows; the fp8
+// copy of x is never read back).  One warp per token; the quantised row stays in registers (one
+// 8-byte chunk per lane and step; kQsMaxSteps = 16 serves hidden <= 4096, 32 hidden <= 8192)
+// between the k stores.
+template <int kQsMaxSteps>
+__global__ void __launch_bounds__(256, kQsMaxSteps <= 16 ? 2 : 1)
+quant_scatter_rows_kernel(const uint4* __restrict__ x, const long long* __restrict__ pos, uint8_t* __restrict__ dst8,
+                          float* __restrict__ dst_scales, long long tokens, int top_k, int hidden, int is_fp16,
+                          long long dst_rows, unsigned* status) {
+  const int lane = threadIdx.x & 31;
+  const long long warp = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  const int chunks = hidden >> 3;   // 8-element chunks per row (a multiple of 16: hidden % 128 == 0)
+  const int nb = hidden >> 7;       // 1x128 blocks per row (<= 64)
+  const int steps = (chunks + 31) >> 5;
+  for (long long t = warp; t < tokens; t += warps) {
+    const uint4* src = x + t * chunks;
+    uint2 q[kQsMaxSteps];
+    float s_lo = 0.f, s_hi = 0.f;  // lane L ends up holding the scales of blocks L and L + 32
+#pragma unroll
+    for (int st0 = 0; st0 < kQsMaxSteps; st0 += kDqUnroll) {
+      if (st0 < steps) {  // uniform over the warp
+        uint4 v[kDqUnroll];
+#pragma unroll
+        for (int u = 0; u < kDqUnroll; ++u) {
+          const int c = (st0 + u) * 32 + lane;
+          v[u] = (st0 + u < steps && c < chunks) ? __ldg(src + c) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int u = 0; u < kDqUnroll; ++u) {
+          const int st = st0 + u;
+          if (st < steps) {
+            float amax = abs_max8(v[u], is_fp16);
+#pragma unroll
+            for (int o = 8; o >= 1; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+            amax = fmaxf(amax, 1e-4f);
+            q[st] = quant8_e4m3(v[u], inv_scale_448(amax), is_fp16);
+            // blocks 2 st (lanes 0..15) and 2 st + 1 (lanes 16..31): lane L keeps the scale of block L mod 32
+            const float sc = __shfl_sync(0xFFFFFFFFu, __fdiv_rn(amax, 448.0f), (lane & 1) << 4);
+            if ((lane >> 1) == (st & 15)) {
+              if (st < 16) s_lo = sc;
+              else s_hi = sc;
+            }
+          }
+        }
+      }
+    }
+    for (int j = 0; j < top_k; ++j) {
+      const long long r = __ldg(pos + t * top_k + j);
+      if (r < 0 || r >= dst_rows) {
+        if (lane == 0 && status) atomicOr(status, kDevBadRowIndex);
+        continue;
+      }
+      uint2* d8 = reinterpret_cast<uint2*>(dst8 + r * hidden);
+#pragma unroll
+      for (int st = 0; st < kQsMaxSteps; ++st) {
+        const int c = st * 32 + lane;
+        if (st < steps && c < chunks) d8[c] = q[st];
+      }
+      float* ds = dst_scales + r * nb;
+      if (lane < nb) ds[lane] = s_lo;
+      if (lane + 32 < nb) ds[lane + 32] = s_hi;
+    }
+  }
+}
+
 // The same dispatch for rows that are already quantised (x8 [tokens, hidden] bytes, xs [tokens,
 // hidden/128] fp32): the pair's row, its scales and its return address in one pass - one launch
 // per chunk instead of one scatter per payload.  hidden % 16 == 0.
@@ -662,6 +730,30 @@ int b200moe_dispatch_quant_rows_multi(const void* x, const int64_t* token_of_pai
       static_cast<const uint4*>(x), reinterpret_cast<const long long*>(token_of_pair), pr, ps, pm, dst_rank,
       reinterpret_cast<const long long*>(dst_row), first_pair, num_pairs, tokens, hidden, dtype, world, capacity_rows,
       my_rank, device_status_ptr());
+  B200_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int b200moe_quant_scatter_rows(const void* x, int dtype, int64_t tokens, int hidden, const int64_t* pos, int top_k,
+                               void* dst8, float* dst_scales, int64_t dst_rows, void* stream) {
+  using namespace b200;
+  const char* who = "b200moe_quant_scatter_rows";
+  B200_REQUIRE(tokens >= 0 && dst_rows >= 0 && top_k >= 0, "%s: negative size", who);
+  B200_REQUIRE(dtype == 0 || dtype == 1, "%s: dtype must be 0 (bf16) or 1 (fp16)", who);
+  B200_REQUIRE(hidden > 0 && hidden % 128 == 0 && hidden <= 8192,
+               "%s: hidden (%d) must be a multiple of 128, at most 8192", who, hidden);
+  if (tokens == 0 || top_k == 0) return 0;
+  B200_REQUIRE(x && pos && dst8 && dst_scales, "%s: null pointer", who);
+  B200_REQUIRE((reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(dst8) & 7) == 0,
+               "%s: x must be 16-byte aligned, dst8 8-byte aligned", who);
+  const int sms = sm_count();
+  B200_REQUIRE(sms > 0, "%s: no CUDA device", who);
+  const long long want = (tokens + 7) / 8;  // 8 warps per block
+  const int blocks = static_cast<int>(want < 16ll * sms ? want : 16ll * sms);
+  auto kern = hidden <= 4096 ? quant_scatter_rows_kernel<16> : quant_scatter_rows_kernel<32>;
+  kern<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(x), reinterpret_cast<const long long*>(pos), static_cast<uint8_t*>(dst8), dst_scales,
+      tokens, top_k, hidden, dtype, dst_rows, device_status_ptr());
   B200_CUDA(cudaGetLastError());
   return 0;
 }

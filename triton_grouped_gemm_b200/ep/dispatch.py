@@ -54,6 +54,26 @@ def _gather_rows(rows: torch.Tensor, idx: torch.Tensor) -> torch.Tensor:
     return rows[idx]
 
 
+def quant_permute_rows(x: torch.Tensor, pos: torch.Tensor, top_k: int):
+    """x [T, H] bf16 / fp16 on CUDA, pos [T*k] int64 (row of pair (t, j) in expert-major order, -1 =
+    dropped): returns (rows8 [T*k, H] float8_e4m3fn, scales [T*k, H/128] fp32) with
+    rows8[pos[t*k+j]], scales[pos[t*k+j]] = the 1x128 quantisation of x[t] - what
+    ``per_token_cast_to_fp8`` followed by a gather in send order gives, in one kernel."""
+    from .. import _lib
+
+    assert x.is_cuda and x.dim() == 2 and x.is_contiguous() and x.dtype in (torch.bfloat16, torch.float16)
+    t, h = x.shape
+    assert pos.numel() == t * top_k and pos.dtype == torch.int64 and pos.is_contiguous()
+    rows8 = torch.empty((t * top_k, h), dtype=torch.float8_e4m3fn, device=x.device)
+    scales = torch.empty((t * top_k, h // 128), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        rc = _lib.load().b200moe_quant_scatter_rows(x.data_ptr(), 0 if x.dtype == torch.bfloat16 else 1, t, h,
+                                                    pos.data_ptr(), top_k, rows8.data_ptr(), scales.data_ptr(),
+                                                    t * top_k, _lib.stream_ptr(x.device))
+    _lib.check(rc, "b200moe_quant_scatter_rows")
+    return rows8, scales
+
+
 def route_plan(keys: torch.Tensor, num_keys: int):
     """Counting sort of ``keys`` (int64, values in [0, num_keys)): returns (counts int64 [num_keys],
     order int64 [n] - indices grouped by key, pos = order^-1).  On CUDA one pass of the library's

@@ -18,7 +18,7 @@ from ..gemm.FP8.m_grouped_gemm_block_scaled import (interleave_gate_up, m_groupe
                                                     m_grouped_fp8_block_scaled_masked,
                                                     m_grouped_fp8_block_scaled_swiglu)
 from ..quant.per_block_cast import per_block_cast_to_fp8, per_token_cast_to_fp8, swiglu_per_token_cast_to_fp8
-from .dispatch import combine, dispatch, dispatch_chunk_async, make_chunked_plan, make_plan
+from .dispatch import combine, dispatch, dispatch_chunk_async, make_chunked_plan, make_plan, quant_permute_rows
 
 
 class Fp8MoELayer:
@@ -183,16 +183,21 @@ class Fp8MoELayer:
         """x [T, H] bf16, topk_idx/topk_weight [T, k] -> [T, H] bf16."""
         if self.transport == "p2p" and self.chunks > 1:
             return self._forward_p2p_pipelined(x.contiguous(), topk_idx, topk_weight)  # quantises while it dispatches
-        x8, xs = per_token_cast_to_fp8(x.contiguous())
+        x = x.contiguous()
+        if self.world == 1:
+            plan = make_plan(topk_idx, self.num_experts, self.group)
+            if x.is_cuda and x.dtype in (torch.bfloat16, torch.float16) and self.hidden % 128 == 0 and self.hidden <= 8192:
+                # one rank: quantise every token once and write it straight to its k expert-major rows
+                r8, rs = quant_permute_rows(x, plan.pos, plan.top_k)
+            else:
+                x8, xs = per_token_cast_to_fp8(x)
+                r8, rs = dispatch(plan, x8, self.group).contiguous(), dispatch(plan, xs, self.group).contiguous()
+            y = self.experts(r8, rs, plan.size_per_group)
+            return combine(plan, y, topk_weight, self.group)
+        x8, xs = per_token_cast_to_fp8(x)
         if self.transport == "p2p":
             return self._forward_p2p(x8, xs, topk_idx, topk_weight)
-        if self.world > 1:
-            return self._forward_pipelined(x8, xs, topk_idx, topk_weight)
-        plan = make_plan(topk_idx, self.num_experts, self.group)
-        r8 = dispatch(plan, x8, self.group)
-        rs = dispatch(plan, xs, self.group)
-        y = self.experts(r8.contiguous(), rs.contiguous(), plan.size_per_group)
-        return combine(plan, y, topk_weight, self.group)
+        return self._forward_pipelined(x8, xs, topk_idx, topk_weight)
 
     def _forward_pipelined(self, x8, xs, topk_idx, topk_weight) -> torch.Tensor:
         """More than one rank.  Chunk c's GEMMs run while chunk c+1 is being dispatched and chunk
