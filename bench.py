@@ -64,6 +64,8 @@ WORKLOADS = {
     # masked layout: 128 slots of 4096 rows, ~1/4 of them valid (the reference's masked benchmark)
     "bf16_masked_m_grouped": ("masked", 2048, 1536, True),
     "quant_act_1x128": ("quant_act", 4096, 0, True),
+    # the one-GPU MoE layer's first step: 1x128 quantiser + token permute in one pass (rows / 8 tokens, top-8)
+    "quant_permute_1x128": ("quant_permute", 4096, 0, True),
     # transposing 128x128 quantiser with per-expert expansion: input [rows, 4096] bf16
     "quant_trans_expand_128x": ("quant_trans", 4096, 0, True),
     # expert-parallel FP8 MoE layer: K = hidden 4096, N = intermediate 1536, 128 experts, top-8,
@@ -209,6 +211,8 @@ def make_inputs(kind, k, n, trans_b, sizes, device, seed):
         return {"x": randn((m, k), 1.0), "w": randn((g, n, k), 0.02, chunk_rows=4)}
     if kind in ("quant_act", "quant_trans"):
         return {"x": randn((m, k), 1.0)}
+    if kind == "quant_permute":
+        return {"x": randn((m // TOP_K, k), 1.0)}
     if kind == "fp8_rowcol":
         a8 = (randn((m, k), 100.0).float().clamp(-400, 400)).to(torch.float8_e4m3fn)
         b8 = (randn((g, n, k), 100.0, chunk_rows=4).float().clamp(-400, 400)).to(torch.float8_e4m3fn)
@@ -239,6 +243,9 @@ def algorithmic_work(kind, k, n, sizes):
         return 2.0 * rows * n * k, "flop"  # M_DIM=k, N_DIM=n, K_total=rows
     if kind == "quant_act":
         return rows * k * 3.0 + rows * (k // 128) * 4.0, "byte"
+    if kind == "quant_permute":
+        pairs = rows // TOP_K * TOP_K   # every token's 16-bit row read once, its fp8 row and scales written top_k times
+        return pairs // TOP_K * k * 2.0 + pairs * k * 1.0 + pairs * (k // 128) * 4.0, "byte"
     if kind == "quant_trans":
         m_expand = rows + 128 * sizes.numel() - rows % 128
         return rows * k * 2.0 + k * m_expand * 1.0 + (k // 128) * (m_expand // 128) * 4.0, "byte"
@@ -284,6 +291,15 @@ def build_step(kind, k, n, trans_b, sizes_dev, inp):
 
         x = inp["x"]
         return (lambda: inp.__setitem__("c", per_token_cast_to_fp8(x))), 1
+    if kind == "quant_permute":
+        from triton_grouped_gemm_b200.ep.dispatch import make_plan, quant_permute_rows
+        from triton_grouped_gemm_b200.ep.moe_layer import synthetic_routing
+
+        x = inp["x"]
+        idx, _ = synthetic_routing(x.shape[0], NUM_EXPERTS, TOP_K, seed=ROUTING_SEED, device=x.device)
+        pos = make_plan(idx, NUM_EXPERTS).pos
+        inp["pos"] = pos
+        return (lambda: inp.__setitem__("c", quant_permute_rows(x, pos, TOP_K))), 1
     if kind == "fp8_rowcol":
         from triton_grouped_gemm_b200.gemm.FP8.m_grouped_gemm_channel_expert import gmm_fp8_act_per_channel_w_per_expert as op
 
@@ -408,6 +424,13 @@ def cpu_reference_step(kind, k, n, trans_b, sizes, budget_work, seed=7):
     elif kind == "quant_act":
         x = torch.randn(m, k, generator=gen).bfloat16()
         fn = lambda: O.per_token_cast_to_fp8(x)  # noqa: E731
+    elif kind == "quant_permute":
+        x = torch.randn(m // TOP_K, k, generator=gen).bfloat16()
+        order = torch.randperm(m // TOP_K * TOP_K, generator=gen) // TOP_K   # token of every expert-major row
+
+        def fn():
+            q, sc = O.per_token_cast_to_fp8(x)
+            return q.view(torch.uint8)[order], sc[order]
     elif kind == "quant_trans":
         x = torch.randn(m, k, generator=gen).bfloat16()
         fn = lambda: O.trans_quant_expand_ref(x, ps)  # noqa: E731
@@ -431,7 +454,7 @@ def cpu_reference_step(kind, k, n, trans_b, sizes, budget_work, seed=7):
 
 
 def unit_of(kind):
-    return ("TFLOP/s", 1e12) if kind not in ("quant_act", "quant_trans") else ("GB/s", 1e9)
+    return ("TFLOP/s", 1e12) if kind not in ("quant_act", "quant_trans", "quant_permute") else ("GB/s", 1e9)
 
 
 def use_all_host_threads():
@@ -754,6 +777,7 @@ def metric_name(kind):
             "fp8_block_k": "grouped-GEMM TFLOP/s (FP8 block-scaled K-grouped, weight gradient)",
             "masked": "grouped-GEMM TFLOP/s (BF16 masked M-grouped)",
             "quant_act": "per-block quantiser GB/s (1x128 e4m3)",
+            "quant_permute": "per-block quantiser + token permute GB/s (1x128 e4m3, top-8)",
             "quant_trans": "per-block quantiser GB/s (transposing 128x128 e4m3 with expansion)",
             "moe_ep": "expert-parallel FP8 MoE layer, grouped-GEMM TFLOP/s incl. dispatch/combine",
             "moe_decode": "FP8 MoE decode (masked layout), grouped-GEMM TFLOP/s"}[kind]
@@ -762,6 +786,7 @@ def metric_name(kind):
 def dtype_name(kind):
     return {"m_grouped": "bf16", "k_grouped": "bf16", "fp8_block": "fp8_e4m3", "fp8_rowcol": "fp8_e4m3",
             "fp8_rowcol_k": "fp8_e4m3", "fp8_block_k": "fp8_e4m3", "masked": "bf16", "quant_act": "bf16->fp8_e4m3",
+            "quant_permute": "bf16->fp8_e4m3",
             "quant_trans": "bf16->fp8_e4m3", "moe_ep": "fp8_e4m3", "moe_decode": "fp8_e4m3"}[kind]
 
 
@@ -1073,6 +1098,19 @@ def run_e2e(args, kind, k, n, trans_b, sizes, inp, dev, use_dist, _unused, work)
         def one():
             q, sc, _ = trans_per_block_quant_expand_128x(host["x"].to(dev, non_blocking=True),
                                                          host["s"].to(dev, non_blocking=True))
+            out_host.copy_(q.view(torch.uint8), non_blocking=True)
+            s_host.copy_(sc, non_blocking=True)
+        host["_extra_out"] = s_host
+    elif kind == "quant_permute":
+        from triton_grouped_gemm_b200.ep.dispatch import quant_permute_rows
+
+        host = {"x": inp["x"].cpu().pin_memory(), "pos": inp["pos"].cpu().pin_memory()}
+        q0, s0 = inp["c"]
+        out_host = torch.empty(q0.shape, dtype=torch.uint8).pin_memory()
+        s_host = torch.empty(s0.shape, dtype=torch.float32).pin_memory()
+
+        def one():
+            q, sc = quant_permute_rows(host["x"].to(dev, non_blocking=True), host["pos"].to(dev, non_blocking=True), TOP_K)
             out_host.copy_(q.view(torch.uint8), non_blocking=True)
             s_host.copy_(sc, non_blocking=True)
         host["_extra_out"] = s_host
