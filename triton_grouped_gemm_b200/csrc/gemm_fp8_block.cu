@@ -12,7 +12,12 @@
 //   warp 0              TMA producer (same ring as the 16-bit kernels; a k-block is 128 bytes
 //                       per row, so the stage layout is identical)
 //   warp 1              MMA issuer: 4 x tcgen05.mma kind::f8f6f4 (128 x BLOCK_N x 32) per k-block
-//   warps 2, 3          idle (they complete warpgroup 0, which gives its registers away)
+//   warps 2, 3          scale producers: for every 16 k-blocks they multiply a_scale[row, kb] by
+//                       b_scale[g, n-block, kb] for this CTA's 128 rows and the tile's two column
+//                       halves and leave the products in shared memory, so that a promotion thread
+//                       fetches the scales of two k-blocks with ONE shared-memory load (shared memory
+//                       is saturated by the tensor core's operand reads: a load and a shuffle per
+//                       k-block cost the promotion warps 8 % of the kernel)
 //   warps 4..4+BLOCK_N/32-1   promotion + epilogue: warp (quarter = warp%4, half = (warp-4)/4)
 //                       owns TMEM lanes [32*quarter, +32) and columns [128*half, +128), i.e.
 //                       exactly one 128-wide scale block of B per thread; these warpgroups
@@ -51,14 +56,23 @@ struct Fp8BlockCfg {
   // warpgroups rise to 224 (128*56 + 256*224 <= 64K).  256 threads (BLOCK_N = 128) already
   // get 255 each and need no re-balancing.
   static constexpr bool kRebalance = kBlockN == 256;
+  // setmaxnreg only moves registers inside the CTA's own allocation (threads x registers at launch);
+  // an increase that the decreases do not cover waits for ever
+  static constexpr int kRegsLaunch = 168, kRegsMove = 56, kRegsPromo = 224;
+  static_assert(!kRebalance || 128 * kRegsMove + (kThreads - 128) * kRegsPromo <= kThreads * kRegsLaunch,
+                "register re-balancing must fit the CTA's allocation");
   static constexpr int kABytes = kBlockM * 128;
   static constexpr int kBBytes = kBRows * 128;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kEpiOffset = kStages * kStageBytes;  // one 4 KB store-staging buffer per promotion warp
-  // two 128-row x 32-k-block tiles of a_scale (fp32, 128-byte swizzle), filled by TMA
-  static constexpr int kScaleTileBytes = kBlockM * 128;
+  // scale products: two buffers x two column halves x 8 k-block pairs x 128 rows x 8 bytes
+  // (a buffer covers kScaleChunk = 16 k-blocks; entry [pair][row] = the products of k-blocks 2 pair
+  // and 2 pair + 1, so the 32 lanes of a promotion warp read 256 consecutive bytes)
+  static constexpr int kScaleChunk = 16;
+  static constexpr int kScaleHalfBytes = (kScaleChunk / 2) * kBlockM * 8;  // 8 KB
+  static constexpr int kScaleBufBytes = 2 * kScaleHalfBytes;
   static constexpr int kScaleOffset = kEpiOffset + 8 * 32 * 128;
-  static constexpr int kBarOffset = kScaleOffset + 2 * kScaleTileBytes;
+  static constexpr int kBarOffset = kScaleOffset + 2 * kScaleBufBytes;
   // + tmem_full[2], tmem_empty[2], scale_full[2], scale_empty[2], exchange_full[4], exchange_empty[4]
   static constexpr int kNumBars = 2 * kStages + 16;
   static constexpr int kDynamicBytes = kBarOffset + kNumBars * 8 + 16 + 1024;
@@ -67,8 +81,8 @@ struct Fp8BlockCfg {
 template <int kBlockN, bool kPair, bool kSwiglu>
 __global__ void __launch_bounds__(Fp8BlockCfg<kBlockN, kPair>::kThreads, 1)
 fp8_block_m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
-                           const __grid_constant__ CUtensorMap tm_c, const __grid_constant__ CUtensorMap tm_as,
-                           int scales_by_tma, __nv_bfloat16* __restrict__ c_ptr, const float* __restrict__ a_scale,
+                           const __grid_constant__ CUtensorMap tm_c, __nv_bfloat16* __restrict__ c_ptr,
+                           const float* __restrict__ a_scale,
                            const float* __restrict__ b_scale, const void* __restrict__ sizes, int sizes_i64,
                            int num_groups, int masked_stride, long long m_rows, int n, int k,
                            const int* __restrict__ b_map, int num_b, float* __restrict__ act_scale_out,
@@ -117,7 +131,7 @@ fp8_block_m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
     for (int a = 0; a < 2; ++a) {
       mbar_init(tmem_full_bar(a), 1);
       mbar_init(tmem_empty_bar(a), L::kPromoWarps * kCtas);
-      mbar_init(scale_full_bar(a), 1);
+      mbar_init(scale_full_bar(a), 2);  // one arrival per scale-producer warp
       mbar_init(scale_empty_bar(a), L::kPromoWarps);
     }
     for (int q = 0; q < 4; ++q) {
@@ -131,7 +145,6 @@ fp8_block_m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
     prefetch_tmap(&tm_a);
     prefetch_tmap(&tm_b);
     prefetch_tmap(&tm_c);
-    if (scales_by_tma) prefetch_tmap(&tm_as);
   }
   if (warp == 1) {
     tmem_alloc<kCtas>(smem_u32(const_cast<uint32_t*>(tmem_holder)), kTmemCols);
@@ -144,14 +157,13 @@ fp8_block_m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
   const uint32_t tmem_base = *tmem_holder;
 
   if (warp < 4) {
-  if constexpr (L::kRebalance) warpgroup_reg_dec<56>();
+  if constexpr (L::kRebalance) warpgroup_reg_dec<L::kRegsMove>();
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     GroupWalker w;
     w.init(sizes, sizes_i64, num_groups, masked_stride, kTileM, m_rows);
     int stage = 0;
     uint32_t phase = 0;
-    uint32_t scale_it = 0;  // scale tiles requested so far: buffer = scale_it & 1
     bool ok = true;
     for (int tile = first_tile; ok; tile += tile_step) {
       const int mt = tile / n_tiles;
@@ -161,21 +173,6 @@ fp8_block_m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
       const int col0 = nt * kBlockN + static_cast<int>(rank) * L::kBRows;
       const int g = weight_of(w.g);
       for (int kb = 0; kb < num_kb; ++kb) {
-        if (scales_by_tma && (kb & 31) == 0) {
-          // a_scale[rows of this CTA, 32 k-blocks] -> shared memory, one tile per 32 k-blocks
-          const uint32_t sb = scale_it & 1u;
-          if (!wait_bounded(scale_empty_bar(sb), ((scale_it >> 1) & 1u) ^ 1u, abort_flag, status,
-                            kDevTimeoutProducer)) {
-            ok = false;
-            break;
-          }
-          if (lane == 0) {
-            mbar_arrive_expect_tx(scale_full_bar(sb), L::kScaleTileBytes);
-            tma_load_2d(smem_base + L::kScaleOffset + sb * L::kScaleTileBytes, &tm_as, scale_full_bar(sb), kb, row0);
-          }
-          __syncwarp();
-          ++scale_it;
-        }
         if (!wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag, status, kDevTimeoutProducer)) {
           ok = false;
           break;
@@ -249,10 +246,69 @@ fp8_block_m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
         }
       }
     }
+  } else {
+    // ------------------------------------------------------------ scale producers (warps 2, 3)
+    // Warp 2 serves rows [0, 64) of this CTA's 128, warp 3 rows [64, 128); lane l the rows l and
+    // l + 32 of that range.  Per chunk of kScaleChunk k-blocks and column half h the products
+    // a_scale[row, kb] * b_scale[weight, n-block of h, kb] go to
+    //   products[buffer][h][pair = (kb % 16) / 2][row] = {kb even, kb odd}   (8 bytes)
+    // Rows past the end of the tensors read row m_rows - 1 instead (their results are discarded);
+    // k-blocks past num_kb get zeros.
+    GroupWalker w;
+    w.init(sizes, sizes_i64, num_groups, masked_stride, kTileM, m_rows);
+    constexpr int kHalves = kBlockN / 128;
+    const int row_in_cta = (warp - 2) * 64 + lane;
+    uint32_t scale_it = 0;  // chunks produced so far: buffer = scale_it & 1
+    bool ok = true;
+    for (int tile = first_tile; ok; tile += tile_step) {
+      const int mt = tile / n_tiles;
+      const int nt = tile - mt * n_tiles;
+      if (!w.seek(mt)) break;
+      const long long row_c0 = w.tile_row0(mt) + static_cast<long long>(rank) * kBlockM + row_in_cta;
+      const int wsel = weight_of(w.g) * n_blocks;
+      int bs_off[kHalves];  // first scale of this tile's column half h: b_scale[bs_off[h] + kb]
+#pragma unroll
+      for (int h = 0; h < kHalves; ++h) {
+        int nb = (nt * kBlockN + h * 128) >> 7;
+        if (nb >= n_blocks) nb = n_blocks - 1;  // columns past n: results are discarded
+        bs_off[h] = (wsel + nb) * num_kb;
+      }
+      for (int kb0 = 0; kb0 < num_kb; kb0 += L::kScaleChunk) {
+        const uint32_t sb = scale_it & 1u;
+        if (!wait_bounded(scale_empty_bar(sb), ((scale_it >> 1) & 1u) ^ 1u, abort_flag, status, kDevTimeoutProducer)) {
+          ok = false;
+          break;
+        }
+#pragma unroll 1
+        for (int j = 0; j < 2; ++j) {
+          long long r = row_c0 + 32 * j;
+          if (r >= m_rows) r = m_rows - 1;
+          const float* ar = a_scale + r * static_cast<long long>(num_kb);
+          uint8_t* dst = smem + L::kScaleOffset + sb * L::kScaleBufBytes + (row_in_cta + 32 * j) * 8;
+#pragma unroll 2
+          for (int pr = 0; pr < L::kScaleChunk / 2; ++pr) {
+            const int kb = kb0 + 2 * pr;
+            const bool in0 = kb < num_kb, in1 = kb + 1 < num_kb;
+            const float a0 = in0 ? __ldg(ar + kb) : 0.f;
+            const float a1 = in1 ? __ldg(ar + kb + 1) : 0.f;
+#pragma unroll
+            for (int h = 0; h < kHalves; ++h) {
+              const float b0 = in0 ? __ldg(b_scale + bs_off[h] + kb) : 0.f;
+              const float b1 = in1 ? __ldg(b_scale + bs_off[h] + kb + 1) : 0.f;
+              *reinterpret_cast<float2*>(dst + h * L::kScaleHalfBytes + pr * (kBlockM * 8)) =
+                  make_float2(__fmul_rn(a0, b0), __fmul_rn(a1, b1));
+            }
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(scale_full_bar(sb));
+        ++scale_it;
+      }
+    }
   }
   } else {
     // ------------------------------------------------------------ promotion + epilogue
-    if constexpr (L::kRebalance) warpgroup_reg_inc<224>();
+    if constexpr (L::kRebalance) warpgroup_reg_inc<L::kRegsPromo>();
     GroupWalker w;
     w.init(sizes, sizes_i64, num_groups, masked_stride, kTileM, m_rows);
     const int quarter = warp & 3;
@@ -260,23 +316,16 @@ fp8_block_m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
     uint32_t it = 0;
     uint32_t scale_it = 0;
     uint32_t xchg_it = 0;  // tiles passed through the gate/up exchange (kSwiglu)
-    // this thread's row inside a staged scale tile: 128 bytes per row, 16-byte chunks XOR-ed
-    // with (row % 8) by the 128-byte swizzle
+    // this thread's entries of the scale-product buffers: [buffer][half][k-block pair][row] x 8 bytes
     const int srow = quarter * 32 + lane;
-    const uint32_t scale_tiles = smem_base + L::kScaleOffset + srow * 128;
-    // volatile: the load must be issued where it is written (a k-block ahead of its use), not
-    // sunk to the use, where its latency would sit on the promotion warps' critical path
-    auto staged_a_scale = [&](uint32_t sb, int kbl) -> float {
-      float v;
-      asm volatile("ld.shared.f32 %0, [%1];"
-                   : "=f"(v)
-                   : "r"(scale_tiles + sb * L::kScaleTileBytes + ((((kbl >> 2) ^ (srow & 7)) << 4) | ((kbl & 3) << 2))));
-      return v;
-    };
-    auto bcast_lane = [&](float v, int src) -> float {
-      float r;
-      asm volatile("shfl.sync.idx.b32 %0, %1, %2, 0x1f, 0xffffffff;" : "=f"(r) : "f"(v), "r"(src));
-      return r;
+    const uint32_t scale_prod = smem_base + L::kScaleOffset + half * L::kScaleHalfBytes + srow * 8;
+    // volatile: the load must be issued where it is written (a pair of k-blocks ahead of its
+    // use), neither sunk to the use, where its latency would sit on the promotion warps' critical
+    // path, nor hoisted above the TMEM load wait
+    auto load_scale_pair = [&](uint32_t sb, int kb, float& s0, float& s1) {
+      asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];"
+                   : "=f"(s0), "=f"(s1)
+                   : "r"(scale_prod + sb * L::kScaleBufBytes + ((kb & (L::kScaleChunk - 1)) >> 1) * (kBlockM * 8)));
     };
     bool ok = true;
     for (int tile = first_tile; ok; tile += tile_step) {
@@ -287,11 +336,6 @@ fp8_block_m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
       const long long row = row_w0 + lane;
       const bool row_ok = row < w.group_row_end();
       const int col_base = nt * kBlockN + half * 128;
-      // scales of this thread: its row of A, and the one 128-wide block of B it covers
-      const float* as_row = a_scale + (row_ok ? row : 0) * static_cast<long long>(num_kb);
-      int nb = col_base >> 7;
-      if (nb >= n_blocks) nb = n_blocks - 1;  // columns past n: results are discarded
-      const float* bs_blk = b_scale + (static_cast<long long>(weight_of(w.g)) * n_blocks + nb) * num_kb;
       // 128 fp32 accumulators as 64 packed pairs (fma.rn.f32x2: two lanes per instruction)
       unsigned long long acc2[64];
 #pragma unroll
@@ -302,53 +346,46 @@ fp8_block_m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
       // k-block kb+1 is requested as soon as its buffer is full, before the loop comes around.
       uint32_t t[64];
       const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + half * 128;
-      // scale of k-block kb: a_scale[row, kb] * b_scale[g, nb, kb].  With staged scales the a
-      // part comes from shared memory and the b part (uniform over the warp) from a register
-      // of lane kb % 32; otherwise both are read from global memory.
-      float bs_reg = 0.f;
+      // scale of k-block kb = a_scale[row, kb] * b_scale[g, n-block, kb], multiplied by the scale
+      // producers; s_even / s_odd hold the current pair of k-blocks, p_even / p_odd the next pair
+      // (requested at the start of the current one)
       uint32_t sb = 0;
-      auto begin_segment = [&](int kb0) -> bool {
+      auto begin_chunk = [&]() -> bool {
         sb = scale_it & 1u;
-        bs_reg = (kb0 + lane < num_kb) ? __ldg(bs_blk + kb0 + lane) : 0.f;
         if (!wait_bounded(scale_full_bar(sb), (scale_it >> 1) & 1u, abort_flag, status, kDevTimeoutPromote))
           return false;
         ++scale_it;
         return true;
       };
-      // the two factors of k-block kb's scale; multiplied when the k-block is reached
-      auto scale_parts = [&](int kb, float& fa, float& fb) {
-        if (scales_by_tma) {
-          fa = staged_a_scale(sb, kb & 31);
-          fb = bcast_lane(bs_reg, kb & 31);
-        } else {
-          fa = __ldg(as_row + kb);
-          fb = __ldg(bs_blk + kb);
-        }
-      };
-      if (scales_by_tma && !begin_segment(0)) break;
-      float fa_next, fb_next;
-      scale_parts(0, fa_next, fb_next);
+      if (!begin_chunk()) break;
+      float s_even, s_odd, p_even = 0.f, p_odd = 0.f;
+      load_scale_pair(sb, 0, s_even, s_odd);
       if (!wait_bounded(tmem_full_bar(it & 1u), (it >> 1) & 1u, abort_flag, status, kDevTimeoutPromote)) break;
       tc_fence_after_sync();
       tmem_ld_32x32b_x64(t_lane + (it & 1u) * kBlockN, t);
       for (int kb = 0; kb < num_kb; ++kb, ++it) {
-        const float s_cur = fa_next * fb_next;
+        const bool odd = (kb & 1) != 0;
+        const float s_cur = odd ? s_odd : s_even;
         const unsigned long long s2 = pack_f32x2(__float_as_uint(s_cur), __float_as_uint(s_cur));
         const bool more = kb + 1 < num_kb;
-        if (more && scales_by_tma && ((kb + 1) & 31) == 0) {
-          // last use of this scale tile is behind us: hand it back, move to the next one
-          __syncwarp();
-          if (lane == 0) mbar_arrive(scale_empty_bar(sb));
-          if (!begin_segment(kb + 1)) {
-            ok = false;
-            break;
-          }
-        }
         const uint32_t buf = it & 1u;
         const uint32_t t_addr = t_lane + buf * kBlockN;
         tmem_ld_wait();
-        // request the next k-block's scale factors now; this k-block's FMAs cover their latency
-        if (more) scale_parts(kb + 1, fa_next, fb_next);
+        // The next pair's products are requested HERE, behind the wait: the same load issued at the
+        // top of the loop, while the first TMEM load is in flight, cost 12 % of the kernel
+        if (!odd && kb + 2 < num_kb) {
+          if (((kb + 2) & (L::kScaleChunk - 1)) == 0) {
+            // the next pair opens a new chunk; everything this buffer had to give is in s_even /
+            // s_odd already: hand it back to the scale producers
+            __syncwarp();
+            if (lane == 0) mbar_arrive(scale_empty_bar(sb));
+            if (!begin_chunk()) {
+              ok = false;
+              break;
+            }
+          }
+          load_scale_pair(sb, kb + 2, p_even, p_odd);
+        }
 #pragma unroll
         for (int j = 0; j < 32; ++j) fma_f32x2(acc2[j], s2, pack_f32x2(t[2 * j], t[2 * j + 1]));
         tmem_ld_32x32b_x64(t_addr + 64, t);
@@ -370,13 +407,16 @@ fp8_block_m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
           }
           tc_fence_after_sync();
           tmem_ld_32x32b_x64(t_lane + (nit & 1u) * kBlockN, t);
+          if (odd) {
+            // end of a pair: the next pair's products arrived long ago
+            s_even = p_even;
+            s_odd = p_odd;
+          }
         }
       }
       if (!ok) break;
-      if (scales_by_tma) {
-        __syncwarp();
-        if (lane == 0) mbar_arrive(scale_empty_bar(sb));
-      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(scale_empty_bar(sb));
       float acc[128];
 #pragma unroll
       for (int j = 0; j < 64; ++j) unpack_f32x2(acc2[j], acc[2 * j], acc[2 * j + 1]);
@@ -521,7 +561,7 @@ fp8_block_m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
 
 template <int kBlockN, bool kPair, bool kSwiglu = false>
 static int launch_fp8_block(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const CUtensorMap& tm_c,
-                            const CUtensorMap& tm_as, int scales_by_tma, void* c, const float* a_scale, const float* b_scale, const void* sizes, int sizes_is_i64,
+                            void* c, const float* a_scale, const float* b_scale, const void* sizes, int sizes_is_i64,
                             int num_groups, int masked_stride, long long m_rows, int n, int k, const int* b_map, int num_b,
                             int grid, cudaStream_t stream, float* act_scale_out = nullptr) {
   using L = Fp8BlockCfg<kBlockN, kPair>;
@@ -566,11 +606,11 @@ static int launch_fp8_block(const CUtensorMap& tm_a, const CUtensorMap& tm_b, co
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    B200_CUDA(cudaLaunchKernelEx(&cfg, kern, tm_a, tm_b, tm_c, tm_as, scales_by_tma, static_cast<__nv_bfloat16*>(c), a_scale, b_scale, sizes,
+    B200_CUDA(cudaLaunchKernelEx(&cfg, kern, tm_a, tm_b, tm_c, static_cast<__nv_bfloat16*>(c), a_scale, b_scale, sizes,
                                  sizes_is_i64, num_groups, masked_stride, m_rows, n, k, b_map, num_b, act_scale_out,
                                  device_status_ptr()));
   } else {
-    kern<<<grid, L::kThreads, L::kDynamicBytes, stream>>>(tm_a, tm_b, tm_c, tm_as, scales_by_tma,
+    kern<<<grid, L::kThreads, L::kDynamicBytes, stream>>>(tm_a, tm_b, tm_c,
                                                           static_cast<__nv_bfloat16*>(c), a_scale,
                                                           b_scale, sizes, sizes_is_i64, num_groups, masked_stride, m_rows,
                                                           n, k, b_map, num_b, act_scale_out, device_status_ptr());
@@ -646,34 +686,22 @@ static int fp8_block_common(const void* a, const float* a_scale, const void* b, 
                          CU_TENSOR_MAP_SWIZZLE_128B, "C");
     if (rc) return rc;
   }
-  // a_scale [m_rows, ceil(k/128)] staged by TMA when its row pitch allows (multiple of 16 bytes)
-  const int num_kb = (k + 127) / 128;
-  const int scales_by_tma = ((num_kb * 4) % 16 == 0 && (reinterpret_cast<uintptr_t>(a_scale) & 15) == 0) ? 1 : 0;
-  CUtensorMap tm_as = tm_c;  // placeholder when unused
-  if (scales_by_tma) {
-    const uint64_t dims[2] = {static_cast<uint64_t>(num_kb), static_cast<uint64_t>(m_rows)};
-    const uint64_t strides[1] = {static_cast<uint64_t>(num_kb) * 4};
-    const uint32_t box[2] = {32, kBlockM};
-    int rc = encode_tmap(&tm_as, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, a_scale, dims, strides, box,
-                         CU_TENSOR_MAP_SWIZZLE_128B, "a_scale");
-    if (rc) return rc;
-  }
   if (swiglu) {
     if (pair)
-      return launch_fp8_block<256, true, true>(tm_a, tm_b, tm_c, tm_as, scales_by_tma, c, a_scale, b_scale, sizes,
+      return launch_fp8_block<256, true, true>(tm_a, tm_b, tm_c, c, a_scale, b_scale, sizes,
                                                sizes_is_i64, num_groups, masked_stride, m_rows, n, k, b_map, num_b, grid,
                                                stream, act_scale_out);
-    return launch_fp8_block<256, false, true>(tm_a, tm_b, tm_c, tm_as, scales_by_tma, c, a_scale, b_scale, sizes,
+    return launch_fp8_block<256, false, true>(tm_a, tm_b, tm_c, c, a_scale, b_scale, sizes,
                                               sizes_is_i64, num_groups, masked_stride, m_rows, n, k, b_map, num_b, grid,
                                               stream, act_scale_out);
   }
   if (pair)
-    return launch_fp8_block<256, true>(tm_a, tm_b, tm_c, tm_as, scales_by_tma, c, a_scale, b_scale, sizes, sizes_is_i64, num_groups,
+    return launch_fp8_block<256, true>(tm_a, tm_b, tm_c, c, a_scale, b_scale, sizes, sizes_is_i64, num_groups,
                                        masked_stride, m_rows, n, k, b_map, num_b, grid, stream);
   if (block_n == 256)
-    return launch_fp8_block<256, false>(tm_a, tm_b, tm_c, tm_as, scales_by_tma, c, a_scale, b_scale, sizes, sizes_is_i64, num_groups,
+    return launch_fp8_block<256, false>(tm_a, tm_b, tm_c, c, a_scale, b_scale, sizes, sizes_is_i64, num_groups,
                                         masked_stride, m_rows, n, k, b_map, num_b, grid, stream);
-  return launch_fp8_block<128, false>(tm_a, tm_b, tm_c, tm_as, scales_by_tma, c, a_scale, b_scale, sizes, sizes_is_i64, num_groups,
+  return launch_fp8_block<128, false>(tm_a, tm_b, tm_c, c, a_scale, b_scale, sizes, sizes_is_i64, num_groups,
                                       masked_stride, m_rows, n, k, b_map, num_b, grid, stream);
 }
 
