@@ -137,6 +137,14 @@ fp8_block_k_grouped_kernel(const __grid_constant__ CUtensorMap tm_x, const __gri
   const uint32_t rank = kPair ? cluster_ctarank() : 0u;
   const int first_tile = kPair ? (blockIdx.x >> 1) : blockIdx.x;
   const int tile_step = kPair ? (gridDim.x >> 1) : gridDim.x;
+  // Tiles are handed out in rounds of tile_step, alternately forwards and backwards (round r gives
+  // this CTA tile r * tile_step + first_tile, or ... + tile_step - 1 - first_tile when r is odd):
+  // with the experts in order of falling token count a plain round-robin gives the first CTAs the
+  // longer tile of every round, and the excess adds up to the difference between the longest and
+  // the shortest tile.  Every role computes the same sequence.
+  auto tile_of_round = [&](long long r) -> long long {
+    return r * tile_step + ((r & 1) ? (tile_step - 1 - first_tile) : first_tile);
+  };
   const int m_tiles = (m_dim + kTileM - 1) / kTileM;
   const int n_tiles = (n_dim + kBlockN - 1) / kBlockN;
   const int tiles_per_group = m_tiles * n_tiles;
@@ -181,7 +189,7 @@ fp8_block_k_grouped_kernel(const __grid_constant__ CUtensorMap tm_x, const __gri
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (long long tile = first_tile; ok && tile < total_tiles; tile += tile_step) {
+      for (long long round = 0, tile = tile_of_round(0); ok && tile < total_tiles; tile = tile_of_round(++round)) {
         const int slot = static_cast<int>(tile / tiles_per_group);
         const int r = static_cast<int>(tile - static_cast<long long>(slot) * tiles_per_group);
         const int mt = r / n_tiles;
@@ -224,7 +232,7 @@ fp8_block_k_grouped_kernel(const __grid_constant__ CUtensorMap tm_x, const __gri
       uint32_t phase = 0;
       uint32_t it = 0;  // k-blocks issued so far: TMEM buffer = it & 1
       bool ok = rank == 0;
-      for (long long tile = first_tile; ok && tile < total_tiles; tile += tile_step) {
+      for (long long round = 0, tile = tile_of_round(0); ok && tile < total_tiles; tile = tile_of_round(++round)) {
         w.locate(static_cast<int>(tile / tiles_per_group), plan);
         for (int kb = 0; kb < w.nkb; ++kb, ++it) {
           const uint32_t buf = it & 1u;
@@ -273,7 +281,7 @@ fp8_block_k_grouped_kernel(const __grid_constant__ CUtensorMap tm_x, const __gri
     const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + half * 128;
     uint8_t* stage_buf = smem + L::kEpiOffset + (warp - 4) * (32 * 128);
     bool ok = true;
-    for (long long tile = first_tile; ok && tile < total_tiles; tile += tile_step) {
+    for (long long round = 0, tile = tile_of_round(0); ok && tile < total_tiles; tile = tile_of_round(++round)) {
       const int slot = static_cast<int>(tile / tiles_per_group);
       const int r = static_cast<int>(tile - static_cast<long long>(slot) * tiles_per_group);
       const int mt = r / n_tiles;
