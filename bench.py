@@ -621,7 +621,7 @@ def summarise_phases(marks, chunks):
 
 
 def ep_leg(dev, rank, world, steps, warmup, chunks, comm_sms, qod=False, return_path="copy", transports=("p2p", "nccl"),
-           taper=False, dispatch_path="kernel"):
+           taper=False, dispatch_path="kernel", ret_streams=4):
     """The expert-parallel FP8 MoE layer of the benchmark configuration on this process group:
     128 experts split over the ranks, 81 920 tokens x hidden 4096 per rank, top-8, intermediate
     1536; dispatch and combine over NVLink inside every step.  Both transports are timed (max over
@@ -658,7 +658,8 @@ def ep_leg(dev, rank, world, steps, warmup, chunks, comm_sms, qod=False, return_
     for transport, ch in [tc for tc in (("p2p", min(chunks, sl)), ("nccl", min(4, sl))) if tc[0] in transports]:
         lay = Fp8MoELayer(sw13[rank * sl:(rank + 1) * sl].to(dev), sw2[rank * sl:(rank + 1) * sl].to(dev), se, group,
                           transport=transport, chunks=ch, tokens_per_rank=st, top_k=sk, capacity_factor=2.0,
-                          quantise_on_dispatch=qod, return_path=return_path, dispatch_path=dispatch_path)
+                          quantise_on_dispatch=qod, return_path=return_path, dispatch_path=dispatch_path,
+                          ret_streams=ret_streams)
         out = lay.forward(sx, sidx, sw)
         small_rdiff[transport] = max_over_ranks(((out.float() - ref.float()).abs().sum() / ref.float().abs().sum()).item())
         lay.close()
@@ -680,13 +681,14 @@ def ep_leg(dev, rank, world, steps, warmup, chunks, comm_sms, qod=False, return_
     for transport, ch in [tc for tc in (("p2p", chunks), ("nccl", 4)) if tc[0] in transports]:
         layer = Fp8MoELayer(w13, w2, NUM_EXPERTS, group, chunks=ch, comm_sms=comm_sms, transport=transport,
                             tokens_per_rank=tokens, top_k=TOP_K, quantise_on_dispatch=qod, return_path=return_path, taper=taper,
-                            dispatch_path=dispatch_path)
+                            dispatch_path=dispatch_path, ret_streams=ret_streams)
         dist.barrier()
         per = timed_steps(lambda: layer.forward(x, idx, w), steps, max(warmup, 3))
         ms = max_over_ranks(statistics.mean(per))
         entry = {"chunks": layer.chunks, "comm_sms": layer.comm_sms, "quantise_on_dispatch": bool(qod and transport == "p2p"),
                  "return_path": return_path if transport == "p2p" else "all_to_all",
                  "dispatch_path": layer.dispatch_path if transport == "p2p" else "all_to_all",
+                 "return_queues": 1 + len(getattr(layer, "_ret_extra", [])) if transport == "p2p" else 0,
                  "ms_per_step": ms,
                  "tflops": work_rank * world / (ms * 1e-3) / 1e12, "rdiff_vs_single_rank": small_rdiff[transport]}
         if transport == "p2p":
@@ -825,7 +827,7 @@ def run_b200(args):
     if args.ep_only and use_dist:
         ep = ep_leg(dev, rank, world, min(args.steps, 8), 3, args.ep_chunks, args.ep_comm_sms, args.ep_quantise_on_dispatch, args.ep_return_path,
                     transports=("p2p",) if args.ep_skip_nccl else ("p2p", "nccl"), taper=args.ep_taper,
-                    dispatch_path=args.ep_dispatch_path)
+                    dispatch_path=args.ep_dispatch_path, ret_streams=args.ep_ret_streams)
         if rank == 0:
             print(json.dumps({"ep_only": True, "n_gpus": world, "ep": ep}), flush=True)
         dist.barrier()
@@ -997,7 +999,8 @@ def run_b200(args):
         if use_dist:
             dist.barrier()
             ep = ep_leg(dev, rank, world, min(args.steps, 8), 3, args.ep_chunks, args.ep_comm_sms,
-                        args.ep_quantise_on_dispatch, args.ep_return_path, dispatch_path=args.ep_dispatch_path)
+                        args.ep_quantise_on_dispatch, args.ep_return_path, dispatch_path=args.ep_dispatch_path,
+                        ret_streams=args.ep_ret_streams)
     if rank == 0:
         if also is not None:
             line["also"] = also
@@ -1167,6 +1170,8 @@ def main():
     ap.add_argument("--ep-comm-sms", type=int, default=None,
                     help="moe_ep_fp8 with more than one GPU: SMs the expert GEMMs leave to the row movers / collectives "
                          "(default: the layer's own, 12 with mover kernels, 2 when both ways go by copy engine)")
+    ap.add_argument("--ep-ret-streams", type=int, default=4,
+                    help="expert-parallel leg, peer memory: stream queues the copy-engine return is spread over")
     ap.add_argument("--ep-dispatch-path", choices=["copy", "kernel"], default="kernel",
                     help="expert-parallel leg, peer memory: rows travel to the experts by copy engine after a local gather, "
                          "or by the mover kernels beside the GEMMs")

@@ -26,7 +26,7 @@ class Fp8MoELayer:
                  group: Optional[dist.ProcessGroup] = None, chunks: int = 4, comm_sms: Optional[int] = None,
                  transport: str = "nccl", capacity_factor: float = 1.5, tokens_per_rank: int = 0, top_k: int = 0,
                  quantise_on_dispatch: bool = False, return_path: str = "copy", taper: bool = False,
-                 dispatch_path: str = "kernel"):
+                 dispatch_path: str = "kernel", ret_streams: int = 4):
         """w13 [E_local, 2*I, H] (gate rows then up rows), w2 [E_local, H, I], bf16, this rank's experts.
         With more than one rank the expert GEMMs consume rows in the order the all-to-all delivers
         them (every [source rank][expert] block is a row group of its own, mapped to its expert's
@@ -53,7 +53,9 @@ class Fp8MoELayer:
         reductions).  It needs the copy return path, rows quantised beforehand and hidden % 512 == 0
         (else "kernel" is used), and measured slower on two GPUs: the copy engines serve dispatch and
         return at once and a chunk's dispatch stretches from 0.5 to 2.5 ms.  ``taper``: a first and a last run of
-        experts about half as long as the others.
+        experts about half as long as the others.  ``ret_streams``: stream queues the copy-engine
+        return is spread over (by destination rank); one queue keeps one copy engine busy, and at 8
+        ranks a single engine (~270 GB/s) cannot keep up with the GEMMs.
         Call ``close()`` on every rank when done with a p2p layer."""
         assert w13.dim() == 3 and w2.dim() == 3 and w13.shape[0] == w2.shape[0]
         self.group = group
@@ -112,6 +114,8 @@ class Fp8MoELayer:
                 self.ret = PeerBuffer(tokens_per_rank * top_k, self.hidden, torch.bfloat16, dev, group)
                 self._peer_buffers += [self.meta, self.ret]
                 self._side = (torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev))
+                # further queues for the copy-engine return: one queue feeds one copy engine (~270 GB/s)
+                self._ret_extra = [torch.cuda.Stream(device=dev) for _ in range(max(0, min(ret_streams, world) - 1))]
                 if self.dispatch_path == "copy":
                     # this rank's rows in send order, the source of the copy-engine dispatch
                     self._send8 = torch.empty((tokens_per_rank * top_k, self.hidden), dtype=torch.uint8, device=dev)
@@ -322,7 +326,13 @@ class Fp8MoELayer:
                 s_ret.wait_event(computed[c])
                 mark(f"return{c}>", s_ret)
                 if self.return_path == "copy":
-                    return_blocks_by_copy(self.ybuf, self.ret, plan, self.bounds[c], self.bounds[c + 1])
+                    queues = [s_ret] + self._ret_extra
+                    return_blocks_by_copy(self.ybuf, self.ret, plan, self.bounds[c], self.bounds[c + 1],
+                                          streams=queues, after=computed[c])
+                    for q in self._ret_extra:      # s_ret stands for the whole chunk again
+                        joined = torch.cuda.Event()
+                        joined.record(q)
+                        s_ret.wait_event(joined)
                 else:
                     return_rows(self.ybuf.local[lo:hi], self.meta.local[lo:hi], self.ret,
                                 blocks=0 if c == chunks - 1 else background)
