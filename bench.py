@@ -621,7 +621,7 @@ def summarise_phases(marks, chunks):
 
 
 def ep_leg(dev, rank, world, steps, warmup, chunks, comm_sms, qod=False, return_path="copy", transports=("p2p", "nccl"),
-           taper=False, dispatch_path="kernel", ret_streams=4):
+           taper=False, dispatch_path="kernel", ret_streams=2):
     """The expert-parallel FP8 MoE layer of the benchmark configuration on this process group:
     128 experts split over the ranks, 81 920 tokens x hidden 4096 per rank, top-8, intermediate
     1536; dispatch and combine over NVLink inside every step.  Both transports are timed (max over
@@ -1160,8 +1160,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--rows", type=int, default=TOTAL_ROWS, help="routed rows per GPU (default: the benchmark's 655360)")
     ap.add_argument("--experts", type=int, default=NUM_EXPERTS, help="experts over all GPUs (default 128)")
-    ap.add_argument("--ep-chunks", type=int, default=8,
-                    help="moe_ep_fp8 with more than one GPU: groups of local experts whose exchange overlaps the GEMMs")
+    ap.add_argument("--ep-chunks", type=int, default=None,
+                    help="moe_ep_fp8 with more than one GPU: groups of local experts whose exchange overlaps the GEMMs "
+                         "(default: 8, and 16 from 8 GPUs on, where the shorter last chunk shortens the exposed tail)")
     ap.add_argument("--ep-transport", choices=["p2p", "nccl"], default="p2p",
                     help="moe_ep_fp8 with more than one GPU: rows move by kernels over peer memory (p2p) or by "
                          "NCCL all-to-all (nccl)")
@@ -1170,7 +1171,7 @@ def main():
     ap.add_argument("--ep-comm-sms", type=int, default=None,
                     help="moe_ep_fp8 with more than one GPU: SMs the expert GEMMs leave to the row movers / collectives "
                          "(default: the layer's own, 12 with mover kernels, 2 when both ways go by copy engine)")
-    ap.add_argument("--ep-ret-streams", type=int, default=4,
+    ap.add_argument("--ep-ret-streams", type=int, default=2,
                     help="expert-parallel leg, peer memory: stream queues the copy-engine return is spread over")
     ap.add_argument("--ep-dispatch-path", choices=["copy", "kernel"], default="kernel",
                     help="expert-parallel leg, peer memory: rows travel to the experts by copy engine after a local gather, "
@@ -1190,6 +1191,8 @@ def main():
     ap.add_argument("--profile", action="store_true",
                     help="for ncu captures: honour --warmup as given, skip the host-buffer and CPU legs")
     args = ap.parse_args()
+    if args.ep_chunks is None:
+        args.ep_chunks = 16 if int(os.environ.get("WORLD_SIZE", "1")) >= 8 else 8
     ROWS_USED[0] = args.rows
     if args.impl == "reference":
         run_reference(args)

@@ -26,7 +26,7 @@ class Fp8MoELayer:
                  group: Optional[dist.ProcessGroup] = None, chunks: int = 4, comm_sms: Optional[int] = None,
                  transport: str = "nccl", capacity_factor: float = 1.5, tokens_per_rank: int = 0, top_k: int = 0,
                  quantise_on_dispatch: bool = False, return_path: str = "copy", taper: bool = False,
-                 dispatch_path: str = "kernel", ret_streams: int = 4):
+                 dispatch_path: str = "kernel", ret_streams: int = 2):
         """w13 [E_local, 2*I, H] (gate rows then up rows), w2 [E_local, H, I], bf16, this rank's experts.
         With more than one rank the expert GEMMs consume rows in the order the all-to-all delivers
         them (every [source rank][expert] block is a row group of its own, mapped to its expert's
