@@ -11,10 +11,15 @@
 // Warp roles (one persistent CTA per SM):
 //   warp 0              TMA producer (same ring as the 16-bit kernels; a k-block is 128 bytes
 //                       per row, so the stage layout is identical)
-//   warp 1              MMA issuer: 4 x tcgen05.mma kind::f8f6f4 (128 x BLOCK_N x 32) per k-block
-//   warps 2, 3          scale producers: for every 16 k-blocks they multiply a_scale[row, kb] by
+//   warps 1, 2          MMA issuers: 4 x tcgen05.mma kind::f8f6f4 (128 x BLOCK_N x 32) per k-block;
+//                       warp 1 issues the k-blocks that go to TMEM buffer 0, warp 2 those of buffer 1.
+//                       A warp sits in its blocked tcgen05.mma instructions for ~40 % of a k-block's
+//                       time, and the promotion warps that share its scheduler fall that far behind
+//                       the others; with two issuers on two schedulers each pair of promotion warps
+//                       is held up only every other k-block (+2 %)
+//   warp 3              scale producer: for every 16 k-blocks it multiplies a_scale[row, kb] by
 //                       b_scale[g, n-block, kb] for this CTA's 128 rows and the tile's two column
-//                       halves and leave the products in shared memory, so that a promotion thread
+//                       halves and leaves the products in shared memory, so that a promotion thread
 //                       fetches the scales of two k-blocks with ONE shared-memory load (shared memory
 //                       is saturated by the tensor core's operand reads: a load and a shuffle per
 //                       k-block cost the promotion warps 8 % of the kernel)
@@ -131,7 +136,7 @@ fp8_block_m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
     for (int a = 0; a < 2; ++a) {
       mbar_init(tmem_full_bar(a), 1);
       mbar_init(tmem_empty_bar(a), L::kPromoWarps * kCtas);
-      mbar_init(scale_full_bar(a), 2);  // one arrival per scale-producer warp
+      mbar_init(scale_full_bar(a), 1);  // one arrival of the scale-producer warp
       mbar_init(scale_empty_bar(a), L::kPromoWarps);
     }
     for (int q = 0; q < 4; ++q) {
@@ -198,8 +203,8 @@ fp8_block_m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
         }
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer (pair: leader only)
+  } else if (warp == 1 || warp == 2) {
+    // ------------------------------------------------------------ MMA issuers (pair: leader only); warp 1: TMEM buffer 0, warp 2: buffer 1
     GroupWalker w;
     w.init(sizes, sizes_i64, num_groups, masked_stride, kTileM, m_rows);
     const uint32_t idesc = make_instr_desc(0u, 0u, 0u, 0u, kTileM, kBlockN);  // e4m3 x e4m3 -> f32
@@ -213,6 +218,13 @@ fp8_block_m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
       for (int kb = 0; kb < num_kb; ++kb, ++it) {
         const uint32_t buf = it & 1u;
         const uint32_t buf_phase = (it >> 1) & 1u;
+        if (buf != static_cast<uint32_t>(warp - 1)) {  // the other issuer's k-block
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+          continue;
+        }
         // operands first (they are nearly always there), then the drained buffer: the MMAs go out
         // the moment the promotion warps let go of it
         if (!wait_bounded(full_bar(stage), phase, abort_flag, status, kDevTimeoutMma) ||
@@ -247,9 +259,8 @@ fp8_block_m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
       }
     }
   } else {
-    // ------------------------------------------------------------ scale producers (warps 2, 3)
-    // Warp 2 serves rows [0, 64) of this CTA's 128, warp 3 rows [64, 128); lane l the rows l and
-    // l + 32 of that range.  Per chunk of kScaleChunk k-blocks and column half h the products
+    // ------------------------------------------------------------ scale producer (warp 3)
+    // Lane l serves rows l, l + 32, l + 64 and l + 96 of this CTA's 128.  Per chunk of kScaleChunk k-blocks and column half h the products
     // a_scale[row, kb] * b_scale[weight, n-block of h, kb] go to
     //   products[buffer][h][pair = (kb % 16) / 2][row] = {kb even, kb odd}   (8 bytes)
     // Rows past the end of the tensors read row m_rows - 1 instead (their results are discarded);
@@ -257,7 +268,7 @@ fp8_block_m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
     GroupWalker w;
     w.init(sizes, sizes_i64, num_groups, masked_stride, kTileM, m_rows);
     constexpr int kHalves = kBlockN / 128;
-    const int row_in_cta = (warp - 2) * 64 + lane;
+    const int row_in_cta = lane;
     uint32_t scale_it = 0;  // chunks produced so far: buffer = scale_it & 1
     bool ok = true;
     for (int tile = first_tile; ok; tile += tile_step) {
@@ -280,7 +291,7 @@ fp8_block_m_grouped_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
           break;
         }
 #pragma unroll 1
-        for (int j = 0; j < 2; ++j) {
+        for (int j = 0; j < 4; ++j) {
           long long r = row_c0 + 32 * j;
           if (r >= m_rows) r = m_rows - 1;
           const float* ar = a_scale + r * static_cast<long long>(num_kb);

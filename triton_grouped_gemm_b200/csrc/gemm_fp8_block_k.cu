@@ -20,7 +20,7 @@
 // Experts differ tenfold in tokens and a tile's cost follows its expert's token count; with a
 // workspace (the K-grouped kernels' plan: starts, token counts, longest-first order) tiles are
 // handed out round-robin in longest-first order, which gives every CTA the same mix.
-//   warp 0   TMA producer      warp 1   MMA issuer (pair: leader CTA only)      warps 2, 3  idle
+//   warp 0   TMA producer      warps 1, 2   MMA issuers (pair: leader CTA only; warp 1 owns TMEM buffer 0, warp 2 buffer 1)      warp 3  idle
 //   warps 4..11  promotion + epilogue: warp (quarter = warp % 4, half = (warp - 4) / 4) owns TMEM
 //                lanes [32 quarter, +32) and columns [128 half, +128) = one scale block of y
 // kPair: two CTAs on two SMs share a 256 x 256 tile (tcgen05 cta_group::2), CTA r holding rows
@@ -223,8 +223,11 @@ fp8_block_k_grouped_kernel(const __grid_constant__ CUtensorMap tm_x, const __gri
           }
         }
       }
-    } else if (warp == 1) {
-      // ------------------------------------------------------------ MMA issuer (pair: leader only)
+    } else if (warp == 1 || warp == 2) {
+      // ------------------------------------------------------------ MMA issuers (pair: leader only).  Warp 1 issues
+      // the k-blocks of TMEM buffer 0, warp 2 those of buffer 1: a warp is blocked in its
+      // tcgen05.mma instructions for a good part of a k-block and holds up the promotion warps
+      // on its scheduler; two issuers on two schedulers halve that for each of them.
       KBlockWalker w;
       w.init(sizes, sizes_i64, num_groups, kb_total);
       const uint32_t idesc = make_instr_desc(0u, 0u, 0u, 0u, kTileM, kBlockN);  // e4m3 x e4m3 -> f32
@@ -237,6 +240,13 @@ fp8_block_k_grouped_kernel(const __grid_constant__ CUtensorMap tm_x, const __gri
         for (int kb = 0; kb < w.nkb; ++kb, ++it) {
           const uint32_t buf = it & 1u;
           const uint32_t buf_phase = (it >> 1) & 1u;
+          if (buf != static_cast<uint32_t>(warp - 1)) {  // the other issuer's k-block
+            if (++stage == kStages) {
+              stage = 0;
+              phase ^= 1u;
+            }
+            continue;
+          }
           // operands first, then the drained buffer: the MMAs go out the moment it is handed back
           if (!wait_bounded(full_bar(stage), phase, abort_flag, status, kDevTimeoutMma) ||
               !wait_bounded(tmem_empty_bar(buf), buf_phase ^ 1u, abort_flag, status, kDevTimeoutMma)) {
