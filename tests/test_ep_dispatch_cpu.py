@@ -358,3 +358,48 @@ def test_layer_module_finds_every_helper_it_imports_lazily():
             mod = p2p if node.module == "p2p" else dispatch
             for alias in node.names:
                 assert hasattr(mod, alias.name), f"{node.module}.{alias.name} is imported by moe_layer but not defined"
+
+
+@pytest.mark.parametrize("world,e_loc,chunks", [(2, 6, 4), (4, 3, 2), (8, 2, 2), (8, 16, 16), (3, 5, 3)])
+def test_host_tables_agree_between_sender_and_receiver(world, e_loc, chunks):
+    """The block tables every rank derives from the gathered counts (no process group needed): what
+    rank s believes about the blocks it sends to rank d must be what rank d believes about the
+    blocks it receives from s - the copy-engine dispatch and return rely on exactly that."""
+    import numpy as np
+
+    from triton_grouped_gemm_b200.ep.p2p import _host_tables, _key_tables, chunk_bounds
+
+    rng = np.random.default_rng(world * 100 + e_loc)
+    e = world * e_loc
+    ca = rng.integers(0, 40, size=(world, world, e_loc))            # [source, destination, local expert]
+    ca[rng.random(ca.shape) < 0.15] = 0
+    bounds = chunk_bounds(e_loc, chunks)
+    key_h, inv_h, _, _ = _key_tables(world, e_loc, tuple(bounds), "cpu")
+    assert sorted(key_h.tolist()) == list(range(e)) and (inv_h[key_h] == np.arange(e)).all()
+    tabs = [_host_tables(ca, world, me, e_loc, e, bounds, 10 ** 9, key_h, inv_h) for me in range(world)]
+    for d in range(world):
+        t = tabs[d]
+        # receive side: blocks [expert][source] packed without gaps, chunk ranges on expert boundaries
+        flat = t["blk_count"].reshape(-1)
+        assert (t["blk_start"].reshape(-1) == np.cumsum(flat) - flat).all()
+        assert t["recv_offsets"][0] == 0 and t["recv_offsets"][-1] == int(ca[:, d, :].sum())
+        for c in range(len(bounds) - 1):
+            assert t["recv_offsets"][c] == int(t["blk_count"][:bounds[c]].sum())
+        for s in range(world):
+            for l in range(e_loc):
+                assert t["blk_count"][l, s] == ca[s, d, l]
+                # the sender's view of the same block
+                assert tabs[s]["snd_count"][d, l] == t["blk_count"][l, s]
+                assert tabs[s]["snd_dst0"][d, l] == t["blk_start"][l, s]
+                assert tabs[s]["snd_src0"][d, l] == t["ret_row0"][l, s]
+    for s in range(world):
+        t = tabs[s]
+        # send order: chunk-major, then destination, then expert; blocks packed without gaps
+        order = [(d, l) for c in range(len(bounds) - 1) for d in range(world) for l in range(bounds[c], bounds[c + 1])]
+        pos = 0
+        for d, l in order:
+            assert t["snd_src0"][d, l] == pos
+            pos += int(ca[s, d, l])
+        assert t["send_offsets"][-1] == pos == int(ca[s].sum())
+        for c in range(len(bounds) - 1):
+            assert t["send_offsets"][c] == sum(int(ca[s, d, l]) for d in range(world) for l in range(bounds[c]))
